@@ -1,0 +1,386 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload `c2_m1`: the Q4_K 14336x4096 decode GEMV with one bf16 activation row (the shape
+the headline metric "weight-GB/s at M=1" is quoted on).  One STEP is four passes over a stack of 32
+distinct weight matrices of that shape (1.06 GB, far larger than the 126 MB L2, so every launch
+streams its weights from HBM); the 128 launches of a step are replayed from one CUDA graph.
+
+Printed JSON (one line, rank 0):
+  value      whole-job weight-GB/s with everything resident in HBM (CUDA events, max over ranks)
+  e2e        the same metric through the public GcuDevice API: activations copied from host memory
+             and the result copied back and synchronised inside every step
+  roofline   algorithmic weight+activation+output bytes of one launch / average launch duration
+             inside the timed region, against the measured HBM copy bandwidth
+  cpu_baseline   the CPU restatement of the same dequant-dot on this box's host cores (bounded sample)
+
+`--impl reference` times that CPU path alone (the reference's own kernels need the vendor toolchain
+and device, so the CPU restatement is the only reference arm that can run).
+
+Other workloads (c1, c2_m4, c2_m16, c3, c4, c5_m1, c5_m512) print the same line for the other
+configurations; c4 and c5 shard over the ranks (expert / tensor parallel) with NCCL all-reduces.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+Q4K_ROW_BYTES = lambda K: K // 256 * 144  # noqa: E731
+Q8_ROW_BYTES = lambda K: K // 32 * 34  # noqa: E731
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+class CpuArm:
+    """The CPU restatement (oracle/ub_oracle.c, OpenMP over weight rows) on this workload's matrix:
+    the same block-wise dequantise-and-dot, f32 accumulation, all host threads."""
+
+    def __init__(self, workload: dict):
+        from oracle import oracle as o
+
+        self.o, self.wl = o, workload
+        N, K, M, is_q4k = workload["N"], workload["K"], workload["M"], workload["is_q4k"]
+        rng = np.random.default_rng(workload["seed"])
+        self.w = (o.gen_q4k_weight if is_q4k else o.gen_q8_0_weight)(rng, N, K)
+        self.Ms = min(M, workload.get("cpu_rows", M))
+        self.x = o.gen_activation(rng, self.Ms, K, workload["x_bf16"])
+        self.y = np.empty((self.Ms, N), dtype=np.float32)
+        self.fn = o.clib().ub_oracle_qmatmul_f32
+        self.cores = os.cpu_count()
+        self.call()  # warm-up: page-in and thread pool
+
+    def call(self):
+        o, wl = self.o, self.wl
+        self.fn(o._p(self.x), o._p(self.w), o._p(self.y), self.Ms, wl["N"], wl["K"], int(wl["is_q4k"]))
+
+    def run(self, budget_s: float):
+        """Repeats the matmul for about budget_s seconds; returns (value in the metric's unit, sample text)."""
+        wl = self.wl
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            self.call()
+            reps += 1
+            el = time.perf_counter() - t0
+            if el >= budget_s:
+                break
+        per_call = el / reps
+        if wl["unit"] == "GB/s":
+            value = self.w.nbytes / per_call / 1e9
+        else:
+            value = 2.0 * self.Ms * wl["N"] * wl["K"] / per_call / 1e12
+        sample = "%d x [%dx%d %s] . x[%d rows] in %.2f s" % (reps, wl["N"], wl["K"], "Q4_K" if wl["is_q4k"] else "Q8_0",
+                                                          self.Ms, el)
+        return value, sample
+
+
+# ----------------------------------------------------------------------------- workloads
+WORKLOADS = {
+    # name: N, K, M, format, activation type, metric unit, seed, number of distinct weight copies per step
+    "c1": dict(N=4096, K=4096, M=1, is_q4k=False, x_bf16=False, unit="GB/s", seed=1001, copies=64,
+               desc="Q8_0 4096x4096 decode GEMV, f32 activations"),
+    "c2_m1": dict(N=14336, K=4096, M=1, is_q4k=True, x_bf16=True, unit="GB/s", seed=1002, copies=32, passes=4,
+                  desc="Q4_K 14336x4096 decode GEMV, bf16 activations, M=1"),
+    "c2_m4": dict(N=14336, K=4096, M=4, is_q4k=True, x_bf16=True, unit="GB/s", seed=1002, copies=32,
+                  desc="Q4_K 14336x4096 small-batch decode, M=4"),
+    "c2_m16": dict(N=14336, K=4096, M=16, is_q4k=True, x_bf16=True, unit="GB/s", seed=1002, copies=32,
+                   desc="Q4_K 14336x4096 small-batch decode, M=16"),
+    "c3": dict(N=14336, K=4096, M=2048, is_q4k=True, x_bf16=True, unit="TFLOP/s", seed=1002, copies=2, cpu_rows=64,
+               desc="Q4_K 14336x4096 prefill GEMM, M=2048"),
+}
+
+
+def run_linear(args, wl, rank, world, torch, dist):
+    """Replicated (data-parallel, weak scaling) linear workloads: every rank streams its own copies."""
+    import ubridge_b200 as ub
+    from oracle import oracle as o  # input generation only; nothing of it is timed here
+    from ubridge_b200 import ops
+
+    dev_index = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(dev_index)
+    N, K, M, is_q4k = wl["N"], wl["K"], wl["M"], wl["is_q4k"]
+    rng = np.random.default_rng(wl["seed"] + rank)
+    w_host = (o.gen_q4k_weight if is_q4k else o.gen_q8_0_weight)(rng, N, K).reshape(-1)
+    w_bytes = w_host.nbytes
+    copies = wl["copies"]
+    x_dtype = ub.DTYPE_BF16 if wl["x_bf16"] else ub.DTYPE_F32
+    y_dtype = ub.DTYPE_BF16 if wl["x_bf16"] else ub.DTYPE_F32
+    xs = o.gen_activation(rng, M, K, wl["x_bf16"])
+    x_host = o.f32_to_bf16_bits(xs).reshape(M, K) if wl["x_bf16"] else xs
+    esz = 2 if wl["x_bf16"] else 4
+
+    # distinct weight buffers resident in HBM (same bytes at different addresses: what matters is that
+    # their total size exceeds L2, so every launch streams from DRAM)
+    w_dev = torch.empty((copies, w_bytes), dtype=torch.uint8, device="cuda")
+    base = torch.from_numpy(w_host).cuda()
+    for c in range(copies):
+        w_dev[c].copy_(base)
+    del base
+    x_dev = torch.from_numpy(x_host.view(np.uint8).reshape(-1).copy()).cuda()
+    y_dev = torch.empty((M * N * esz,), dtype=torch.uint8, device="cuda")
+    ws_bytes = ops.qmatmul_workspace_bytes(M, N, K, is_q4k)
+    ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device="cuda")
+
+    stream = torch.cuda.Stream()
+    sp = ctypes.c_void_p(stream.cuda_stream)
+
+    passes = wl.get("passes", 1)
+
+    def one_step():
+        for _p in range(passes):
+            for c in range(copies):
+                ops.qmatmul(y_dev.data_ptr(), x_dev.data_ptr(), w_dev[c].data_ptr(), M, N, K, is_q4k=is_q4k,
+                            x_dtype=x_dtype, out_dtype=y_dtype, workspace=ws.data_ptr(), ws_bytes=ws_bytes, stream=sp)
+
+    with torch.cuda.stream(stream):
+        one_step()  # first call resolves symbols and attributes outside any capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_step()
+        for _ in range(args.warmup):
+            graph.replay()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(dev_index)
+        if rank == 0:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        ev1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if rank == 0 else None
+    ms_total = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+
+    # decode kernel: M rows are processed 4/2/1 at a time, one launch each
+    def decode_launches(m):
+        n = 0
+        while m > 0:
+            t_ = 4 if m >= 4 else (2 if m >= 2 else 1)
+            m -= t_
+            n += 1
+        return n
+    launches_per_call = decode_launches(M) if (M <= 16 or not is_q4k) else 1
+    launches = args.steps * copies * passes * launches_per_call
+
+    calls = copies * passes * world
+    if wl["unit"] == "GB/s":
+        value = calls * w_bytes / (ms_step * 1e-3) / 1e9
+    else:
+        value = calls * 2.0 * M * N * K / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public device API: host activations in, host result out, every step
+    e2e = None
+    if rank == 0 or world > 1:
+        dev = ub.GcuDevice(dev_index)
+        w_e2e = [dev.alloc(w_bytes) for _ in range(copies)]
+        for c in range(copies):
+            ub.lib().ub_memcpy_dtod(dev._handle, ctypes.c_void_p(w_e2e[c].ptr), ctypes.c_void_p(w_dev[c].data_ptr()),
+                                    w_bytes)
+        dev.synchronize()
+        del w_dev
+        torch.cuda.empty_cache()
+        host_x = torch.from_numpy(x_host.view(np.uint8).reshape(-1).copy()).pin_memory()
+        host_y = torch.empty((M * N * esz,), dtype=torch.uint8).pin_memory()
+        d_x, d_y = dev.alloc(host_x.numel()), dev.alloc(host_y.numel())
+        d_ws = dev.alloc(max(ws_bytes, 256))
+        lib = ub.lib()
+
+        def e2e_step():
+            lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), ctypes.c_void_p(host_x.data_ptr()), host_x.numel())
+            for _p in range(passes):
+                for c in range(copies):
+                    ops.qmatmul(d_y, d_x, w_e2e[c], M, N, K, is_q4k=is_q4k, x_dtype=x_dtype, out_dtype=y_dtype,
+                                workspace=d_ws, ws_bytes=ws_bytes, stream=dev.stream)
+            lib.ub_memcpy_dtoh(dev._handle, ctypes.c_void_p(host_y.data_ptr()), ctypes.c_void_p(d_y.ptr), host_y.numel())
+            dev.synchronize()
+
+        for _ in range(max(3, args.warmup)):
+            e2e_step()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        el = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([el], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            el = float(t.item())
+        s_step = el / args.steps
+        ev = calls * w_bytes / s_step / 1e9 if wl["unit"] == "GB/s" else calls * 2.0 * M * N * K / s_step / 1e12
+        e2e = {"value": ev, "unit": wl["unit"], "h2d_bytes_per_step": int(host_x.numel()),
+               "d2h_bytes_per_step": int(host_y.numel())}
+
+    peaks = measured_peaks()
+    algo_bytes = w_bytes + M * K * esz + M * N * esz
+    avg_launch_s = ms_total * 1e-3 / (args.steps * copies * passes)  # per matmul call (all of its launches)
+    if wl["unit"] == "GB/s":
+        achieved = algo_bytes / avg_launch_s / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "algorithmic_bytes_per_launch": algo_bytes, "avg_launch_us": avg_launch_s * 1e6}
+    else:
+        achieved = 2.0 * M * N * K / avg_launch_s / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["source"],
+                "algorithmic_flops_per_launch": 2.0 * M * N * K, "avg_launch_us": avg_launch_s * 1e6}
+    return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
+                dtype="u4+f16 scales -> f32 accumulate" if is_q4k else "i8+f16 scales -> f32 accumulate")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2_m1", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    wl = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    metric = "weight_GBps" if wl["unit"] == "GB/s" else "TFLOPS"
+    config = {"workload": "%s: %s; one step = %d matmuls over %d distinct weight copies (%.0f MB, larger than L2)" % (
+        args.workload, wl["desc"], wl["copies"] * wl.get("passes", 1), wl["copies"],
+        wl["copies"] * wl["N"] * (Q4K_ROW_BYTES(wl["K"]) if wl["is_q4k"] else Q8_ROW_BYTES(wl["K"])) / 1e6),
+        "N": wl["N"], "K": wl["K"], "M": wl["M"], "format": "Q4_K" if wl["is_q4k"] else "Q8_0",
+        "l2_policy": "inputs larger than L2", "parallelism": "replicas x%d" % args.gpus}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        vals = []
+        sample = ""
+        arm = CpuArm(wl)
+        cores = arm.cores
+        per = max(0.25, min(args.cpu_seconds, 60.0 / max(1, args.steps + args.warmup)))
+        for i in range(args.warmup + args.steps):
+            v, sample = arm.run(per)
+            if i >= args.warmup:
+                vals.append(v)
+        value = statistics.mean(vals)
+        line = {"impl": "reference", "metric": metric, "value": value, "unit": wl["unit"], "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": value, "unit": wl["unit"], "cores": cores, "kind": "port",
+                                 "sample": "each step: " + sample},
+                "e2e": {"value": value, "unit": wl["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl")
+    try:
+        res = run_linear(args, wl, rank, world, torch, dist)
+        if rank == 0:
+            cpu = None
+            if world == 1:
+                arm = CpuArm(wl)
+                v, sample = arm.run(args.cpu_seconds)
+                cpu = {"value": v, "unit": wl["unit"], "cores": arm.cores, "kind": "port", "sample": sample}
+            line = {"metric": metric, "value": res["value"], "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
+                    "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+                    "scaling": "weak", "vs_baseline": None, "dtype": res["dtype"], "data": "synthetic",
+                    "config": config, "roofline": res["roofline"], "cpu_baseline": cpu, "e2e": res["e2e"],
+                    "gpu_launches": res["launches"], "clocks": res["clocks"]}
+            print(json.dumps(line))
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,234 @@
+/*
+ * ubridge_b200 — C-ABI of the B200 (sm_100a) quantized-linear + fused-MoE path.
+ *
+ * Plain C: pointers, sizes and ints only.  Every pointer is caller-owned DEVICE memory
+ * unless a comment says "host".  Every call enqueues on the CUDA stream passed as the
+ * trailing `void* stream` (a cudaStream_t; NULL = the legacy default stream) and returns
+ * without synchronising, exactly like the reference's host launchers.  Outputs and
+ * workspaces are pre-allocated by the caller; the library allocates nothing on these
+ * paths and keeps no pointer after a call returns.
+ *
+ * Each declaration cites the reference interface it replaces as  file:line  (paths
+ * inside the reference project).  Exports that keep a reference name keep its argument
+ * order, meaning and `void` return; status of the last such call on the calling thread
+ * is readable through ub_last_status().  New exports return an int status.
+ */
+#ifndef UBRIDGE_B200_H_
+#define UBRIDGE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ status codes */
+enum {
+  UB_OK = 0,
+  UB_ERR_INVALID_ARG = 1,   /* bad shape, null pointer, unsupported dtype            */
+  UB_ERR_UNSUPPORTED = 2,   /* name not in the registry / path not built             */
+  UB_ERR_WORKSPACE = 3,     /* workspace missing or too small                        */
+  UB_ERR_CUDA = 4,          /* a CUDA runtime call failed (see ub_last_cuda_error)   */
+  UB_ERR_BAD_INDEX = 5,     /* device saw an expert id / slot outside its range      */
+  UB_ERR_TIMEOUT = 6,       /* a bounded device-side wait ran out                    */
+  UB_ERR_NCCL = 7,          /* NCCL missing or a collective call failed              */
+  UB_ERR_TOO_LARGE = 8      /* size beyond a fixed limit of the entry point          */
+};
+
+/* element type codes: the reference's DATATYPE enum, src/lib.rs:87-106 (kernels/utils/utils.h:31-49) */
+enum { UB_DTYPE_I8 = 0, UB_DTYPE_U8 = 1, UB_DTYPE_F16 = 4, UB_DTYPE_BF16 = 5, UB_DTYPE_I32 = 6, UB_DTYPE_F32 = 8, UB_DTYPE_I4 = 15 };
+
+/* opcodes of the shim: src/device_opcode.rs:16-46 keeps an (unused) opcode enum; the
+ * quantized path's operations are numbered here in the same spirit. */
+enum {
+  UB_OP_DEQUANT_Q8_0 = 100,
+  UB_OP_DEQUANT_Q4K = 101,
+  UB_OP_QUANTIZE_Q8_0 = 102,
+  UB_OP_QMATMUL_Q8_0 = 110,
+  UB_OP_QMATMUL_Q4K = 111,
+  UB_OP_TOPK_SOFTMAX = 120,
+  UB_OP_MOE_ALIGN = 121,
+  UB_OP_FUSED_MOE = 122,
+  UB_OP_MOE_COMBINE = 123,
+  UB_OP_INDEXED_MOE = 124,
+  UB_OP_FUSED_MOE_Q4K = 125
+};
+
+int ub_version(void);
+const char* ub_status_string(int status);
+/* status of the most recent call made by the calling thread (void exports included) */
+int ub_last_status(void);
+/* last cudaError_t seen by the calling thread, as an int */
+int ub_last_cuda_error(void);
+/* Reads (and clears) the per-device error word that kernels set instead of trapping:
+ * the reference traps the device on a bad expert id (kernels/utils/moe_kernel_compat.h:21-28,
+ * kernels/moe_align_host.cpp:101-163).  Synchronises `stream`.  Returns UB_OK,
+ * UB_ERR_BAD_INDEX or UB_ERR_TIMEOUT. */
+int ub_device_status(void* stream);
+
+/* ------------------------------------------------------------------ device, memory, stream
+ * Mirrors GcuDevice (src/gcu_device.rs:61-635): one device + one non-blocking stream,
+ * stream-ordered alloc/free, H2D / D2H / D2D copies, synchronize. */
+typedef struct ub_device ub_device;
+int ub_device_count(void);                                         /* gcu_device.rs: GcuDevice::count */
+int ub_device_new(int ordinal, ub_device** out);                   /* gcu_device.rs:108-139 */
+void ub_device_free(ub_device* dev);
+int ub_device_ordinal(const ub_device* dev);
+void* ub_device_stream(const ub_device* dev);                      /* the device's cudaStream_t */
+int ub_device_bind(const ub_device* dev);                          /* gcu_device.rs:144-147 (select device) */
+int ub_alloc(ub_device* dev, size_t bytes, void** out);            /* gcu_device.rs:216-260 */
+int ub_alloc_zeros(ub_device* dev, size_t bytes, void** out);      /* gcu_device.rs:262-324 */
+int ub_free(ub_device* dev, void* ptr);                            /* gcu_slice.rs:62-101 (stream-ordered free) */
+int ub_memcpy_htod(ub_device* dev, void* dst, const void* host_src, size_t bytes); /* gcu_device.rs:337-420 */
+int ub_memcpy_dtoh(ub_device* dev, void* host_dst, const void* src, size_t bytes); /* gcu_device.rs:500-588 */
+int ub_memcpy_dtod(ub_device* dev, void* dst, const void* src, size_t bytes);      /* gcu_device.rs:422-498 */
+/* strided rows: `height` rows of `width_bytes`, source/destination pitches in bytes */
+int ub_memcpy_dtod_2d(ub_device* dev, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t height); /* gcu_device.rs:422-498 */
+int ub_synchronize(ub_device* dev);                                /* gcu_device.rs:610-618 */
+
+/* ------------------------------------------------------------------ name -> launcher registry
+ * Mirrors DeviceExecutor.function_map + GcuDevice::get_or_load_func + GcuFunction::launch
+ * (src/device_executor.rs:57-61,295-308,361-376; src/gcu_device.rs:160-183;
+ * src/gcu_launch.rs:183-328).  `params` is the same void*[] the reference hands to
+ * topsModuleLaunchKernel: params[i] points at the i-th kernel argument.  Grid, block and
+ * shared-memory fields are accepted for source compatibility and ignored: each launcher
+ * sizes its own grid.  Unlike the reference (silent no-op handle, gcu_device.rs:176-182)
+ * an unknown name returns NULL and launching NULL returns UB_ERR_UNSUPPORTED. */
+typedef struct ub_function ub_function;
+typedef struct {
+  unsigned grid_dim[3];
+  unsigned block_dim[3];
+  unsigned shared_mem_bytes;
+  int is_cooperative_launch;
+} ub_launch_config;                                                /* src/gcu_launch.rs:40-90 */
+
+const ub_function* ub_get_function(const char* module_name, const char* func_name);
+int ub_has_function(const char* module_name, const char* func_name); /* device_executor.rs:533-538 */
+int ub_function_count(void);
+const char* ub_function_name(int index);                           /* "module::name" */
+int ub_function_opcode(const ub_function* f);
+int ub_launch(const ub_function* f, const ub_launch_config* cfg, void** params, void* stream);
+
+/* Kernels reachable by name, module "quant" (kernels/quant.cpp:257-268,341-353,477-488):
+ *   dequantize_block_q8_0_{f16,bf16,f32}(int8_t* in, T* out, size_t numel)
+ *   dequantize_block_q4_k_{f16,bf16,f32}(int8_t* in, T* out, size_t numel)
+ *   quantize_block_q8_0_{f16,bf16,f32}(T* in, int8_t* out, size_t in_bytes, size_t out_bytes)
+ * `in`/`out` use the reference's de-interleaved device layout: all block headers first,
+ * then all quants (kernels/quant.cpp:219-220,300-301,441-442).  quantize_block_q4_k_* is
+ * absent on purpose: the reference's own is a stub whose body is commented out
+ * (kernels/quant.cpp:639-640). */
+
+/* ------------------------------------------------------------------ GGUF block (de)quantisation
+ * New entry points on INTERLEAVED GGUF blocks (34-byte Q8_0, 144-byte Q4_K; formats at
+ * kernels/quant.cpp:98-104,145-150,356-363).  `numel` counts weights, a multiple of the
+ * block size.  Output is bit-exact: the f32 value d*q (Q8_0) or (d*sc)*q - dmin*m (Q4_K),
+ * rounded once (nearest-even) to out_dtype.  Replaces kernels/quant.cpp:188-268,372-488. */
+int ub_dequant_q8_0(void* out, const void* blocks, size_t numel, int out_dtype, void* stream);
+int ub_dequant_q4k(void* out, const void* blocks, size_t numel, int out_dtype, void* stream);
+/* x (in_dtype) -> interleaved Q8_0 blocks; replaces kernels/quant.cpp:270-353. */
+int ub_quantize_q8_0(void* blocks, const void* x, size_t numel, int in_dtype, void* stream);
+/* interleaved <-> the reference's split device layout (kernels/quant.cpp:219-220,441-442) */
+int ub_repack_to_split(void* split, const void* interleaved, size_t nblocks, int is_q4k, void* stream);
+int ub_repack_to_interleaved(void* interleaved, const void* split, size_t nblocks, int is_q4k, void* stream);
+
+/* ------------------------------------------------------------------ fused quantized matmul
+ * y[M,N] = x[M,K] . W^T, W given as N rows of K/32 (Q8_0) or K/256 (Q4_K) interleaved GGUF
+ * blocks; f32 accumulation.  The reference reaches the same result with two kernels and a
+ * dense temporary: dequantize_block_* (kernels/quant.cpp:257-268,477-488) followed by
+ * matmul_* (kernels/matmul.cpp:1143-1184; small-M shape in
+ * kernels/third_party/matmul_decoding.h:12-570).  The suffix names the activation type;
+ * out_dtype is UB_DTYPE_F32 / UB_DTYPE_BF16 / UB_DTYPE_F16.  M <= 16 runs the
+ * bandwidth-bound decode kernel, larger M the tensor-core kernel (Q4_K) — see
+ * ub_qmatmul_workspace_bytes for the scratch each needs (0 for the decode kernel). */
+size_t ub_qmatmul_workspace_bytes(int M, int N, int K, int is_q4k);
+int ub_qmatmul_q8_0_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
+int ub_qmatmul_q8_0_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
+int ub_qmatmul_q4k_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
+int ub_qmatmul_q4k_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------ MoE: reference-named host launchers */
+/* src/ffi.rs:205-236, kernels/topk_softmax_host.cpp:178-208 */
+void topk_softmax_f32(float* input, float* output, int* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
+void topk_softmax_f16(void* input, void* output, int* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
+void topk_softmax_bf16(void* input, void* output, int* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
+
+/* src/ffi.rs:149-161, kernels/moe_align_host.cpp:923-935.  sorted_ids holds
+ * token_num*topk + num_experts*(block_size-1) ints, experts_ids that count / block_size.
+ * real_token_num and expert_map may be NULL.  A bad expert id sets the device error word
+ * (ub_device_status) instead of trapping. */
+void moe_align_block_size(int32_t* sorted_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t* topk_ids, int32_t* real_token_num, int32_t* expert_map, int32_t num_experts, int32_t block_size, int32_t token_num, int32_t topk, void* stream);
+
+/* src/ffi.rs:163-203, kernels/fused_moe_host.cpp:504-536.  Dense expert weights B[E,N,K]. */
+void invoke_fused_moe_f16(void* C, void* A, void* B, void* bias, float* topk_weights, int32_t* sorted_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t M, int32_t K, int32_t N, int32_t E, int32_t topk_ids_size, int32_t top_k, int32_t block_size, int32_t mul_routed_weight, int32_t bias_flag, void* stream);
+void invoke_fused_moe_bf16(void* C, void* A, void* B, void* bias, float* topk_weights, int32_t* sorted_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t M, int32_t K, int32_t N, int32_t E, int32_t topk_ids_size, int32_t top_k, int32_t block_size, int32_t mul_routed_weight, int32_t bias_flag, void* stream);
+
+/* src/ffi.rs:44-68, kernels/moe_host.cpp:83-94: y[idx[k],:] += e_out[k,:] * w[idx[k]*topk + top[k]] */
+void moe_f16(void* y, void* e_out, float* w, uint32_t* idx, uint32_t* top, int N, int K, int M, int topk, void* stream);
+void moe_bf16(void* y, void* e_out, float* w, uint32_t* idx, uint32_t* top, int N, int K, int M, int topk, void* stream);
+
+/* src/ffi.rs:121-147, kernels/moe_host.cpp:278-293: out[b,t,:] = in[b,(M==1?0:t),:] . w[indices[b,t]]^T */
+void indexed_moe_f16(void* in, void* w, void* out, uint32_t* indices, int N, int K, int M, int batch, int topk, int num_experts, void* stream);
+void indexed_moe_bf16(void* in, void* w, void* out, uint32_t* indices, int N, int K, int M, int batch, int topk, int num_experts, void* stream);
+
+/* status-returning twins: src/ffi.rs:671-713, kernels/topsaten_moe_wrapper.cpp:80-213 */
+int topsaten_topk_softmax_f32(float* gating_output, float* topk_weights, int32_t* topk_indices, int32_t* token_expert_indices, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
+int topsaten_moe_align_block_size(int32_t* sorted_token_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t* topk_ids, int32_t num_experts, int32_t block_size, int32_t num_tokens, int32_t topk, void* stream);
+int topsaten_fused_moe_gemm(void* c, void* a, void* b, float* topk_weights, int32_t* topk_ids, int32_t* sorted_token_ids, int32_t* expert_ids, int32_t* num_tokens_post_padded, int32_t mul_routed_weight, int32_t topk, int32_t block_size, int32_t num_tokens, int32_t hidden_dim, int32_t inter_dim, int32_t num_experts, int32_t dtype_code, void* stream);
+void topsaten_release_graph_workspace_pool(void* stream);
+
+/* ------------------------------------------------------------------ MoE: new fused entry points */
+/* out[t, :D] = silu(in[t, :D]) * in[t, D:2D]  (kernels/topsaten_ops_wrapper.cpp:375-391) */
+int ub_silu_and_mul(void* out, const void* in, int rows, int D, int dtype, void* stream);
+/* out[t,:] = sum_j in[t,j,:]  (the reference's caller uses topsaten_sum, src/ffi.rs:841-849) */
+int ub_topk_sum(void* out, const void* in, int T, int topk, int H, int dtype, void* stream);
+
+/* Grouped GEMM over aligned blocks with Q4_K expert weights Bq[E][N rows of K/256
+ * super-blocks]: same contract as invoke_fused_moe_bf16 (kernels/fused_moe_host.cpp:43-250)
+ * with A and C bf16.  act_silu_mul != 0 treats B as [gate rows; up rows] (N = 2*D) and
+ * writes C[slot, :D] = silu(gate)*up (the SiLU.up step the reference's caller runs between
+ * its two GEMMs, kernels/topsaten_ops_wrapper.cpp:375-391), C row stride D. */
+int ub_fused_moe_q4k_gemm(void* C, const void* A, const void* Bq, const float* topk_weights, const int32_t* sorted_ids, const int32_t* experts_ids, const int32_t* num_tokens_post_pad, int M, int K, int N, int E, int topk_ids_size, int top_k, int block_size, int mul_routed_weight, int act_silu_mul, void* workspace, size_t ws_bytes, void* stream);
+
+/* Whole expert layer: router logits -> out[T,H].  topk_softmax -> moe_align_block_size ->
+ * grouped Q4_K GEMM (w13, SiLU.up) -> grouped Q4_K GEMM (w2, routed weight) -> sum over
+ * top-k; the sequence of src/ffi.rs calls the reference's caller issues (five to six
+ * launches), on one stream with one caller-provided workspace.  expert_map may be NULL
+ * (expert-parallel ranks pass local ids / -1, kernels/moe_align_host.cpp:298,535-543). */
+size_t ub_moe_layer_q4k_workspace_bytes(int T, int H, int I, int E, int top_k, int block_size);
+int ub_moe_layer_q4k(void* out, const void* hidden, const void* router_logits, const void* w13q, const void* w2q, const int32_t* expert_map, int T, int H, int I, int E, int top_k, int block_size, int norm_topk_prob, void* workspace, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------ collectives
+ * ECCL-shaped surface (src/eccllib.rs:7-169, src/eccl.rs:14-426) forwarding to NCCL over
+ * NVLink.  Types and enum values below are ECCL's names with NCCL's layout.  The NCCL
+ * library is opened at first use (dlopen "libnccl.so.2"); without it every call returns
+ * UB-side failure code ecclSystemError. */
+typedef struct ecclComm* ecclComm_t;
+typedef struct { char internal[128]; } ecclUniqueId;               /* src/eccl.rs:24-43 */
+typedef enum { ecclSuccess = 0, ecclUnhandledCudaError = 1, ecclSystemError = 2, ecclInternalError = 3, ecclInvalidArgument = 4, ecclInvalidUsage = 5, ecclRemoteError = 6, ecclInProgress = 7 } ecclResult_t;
+typedef enum { ecclSum = 0, ecclProd = 1, ecclMax = 2, ecclMin = 3, ecclAvg = 4 } ecclRedOp_t;             /* src/eccl.rs:45-61 */
+typedef enum { ecclInt8 = 0, ecclUint8 = 1, ecclInt32 = 2, ecclUint32 = 3, ecclInt64 = 4, ecclUint64 = 5, ecclFloat16 = 6, ecclFloat32 = 7, ecclFloat64 = 8, ecclBfloat16 = 9 } ecclDataType_t; /* src/eccl.rs:86-96 */
+
+ecclResult_t ecclGetVersion(int* version);                                                              /* eccllib.rs:15-21 */
+ecclResult_t ecclGetUniqueId(ecclUniqueId* id);                                                         /* eccllib.rs:23-29 */
+ecclResult_t ecclCommInitRank(ecclComm_t* comm, int nranks, ecclUniqueId id, int rank);                 /* eccllib.rs:31-38 */
+ecclResult_t ecclCommInitAll(ecclComm_t* comms, int ndev, const int* devlist);                          /* eccllib.rs:40-46 */
+ecclResult_t ecclCommDestroy(ecclComm_t comm);                                                          /* eccllib.rs:7-9  */
+ecclResult_t ecclCommAbort(ecclComm_t comm);                                                            /* eccllib.rs:11-13 */
+ecclResult_t ecclCommCount(ecclComm_t comm, int* count);                                                /* eccllib.rs:48-52 */
+ecclResult_t ecclCommDevice(ecclComm_t comm, int* device);                                              /* eccllib.rs:54-58 */
+ecclResult_t ecclCommUserRank(ecclComm_t comm, int* rank);                                              /* eccllib.rs:60-64 */
+ecclResult_t ecclReduce(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t dt, ecclRedOp_t op, int root, ecclComm_t comm, void* stream);          /* eccllib.rs:67-80 */
+ecclResult_t ecclBroadcast(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t dt, int root, ecclComm_t comm, void* stream);                      /* eccllib.rs:82-94 */
+ecclResult_t ecclAllReduce(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t dt, ecclRedOp_t op, ecclComm_t comm, void* stream);                /* eccllib.rs:96-108 */
+ecclResult_t ecclReduceScatter(const void* sendbuff, void* recvbuff, size_t recvcount, ecclDataType_t dt, ecclRedOp_t op, ecclComm_t comm, void* stream);        /* eccllib.rs:110-122 */
+ecclResult_t ecclAllGather(const void* sendbuff, void* recvbuff, size_t sendcount, ecclDataType_t dt, ecclComm_t comm, void* stream);                            /* eccllib.rs:124-135 */
+ecclResult_t ecclSend(const void* sendbuff, size_t count, ecclDataType_t dt, int peer, ecclComm_t comm, void* stream);                                           /* eccllib.rs:137-148 */
+ecclResult_t ecclRecv(void* recvbuff, size_t count, ecclDataType_t dt, int peer, ecclComm_t comm, void* stream);                                                 /* eccllib.rs:150-161 */
+ecclResult_t ecclGroupStart(void);                                                                      /* eccllib.rs:167-169 */
+ecclResult_t ecclGroupEnd(void);                                                                        /* eccllib.rs:163-165 */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UBRIDGE_B200_H_ */

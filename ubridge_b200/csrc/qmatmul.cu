@@ -1,0 +1,121 @@
+// Entry points of the fused quantized matmul and the M-bucket dispatch behind them.
+//
+// The reference picks a matmul variant per shape with AtenGemmTuner (src/gemm_tuner.rs:326-359,
+// small-M special cases :502-514) and kernels/matmul.cpp:1197-1208 (LHS-resident decode kernel when it
+// fits, batched kernel otherwise).  The same idea here is a three-way split on M:
+//   M <= 16           bandwidth-bound decode GEMV (qgemv.cu), f32 or bf16 activations, no workspace;
+//   M  > 16, Q4_K     tensor-core GEMM with in-kernel dequantisation (bf16 activations and output;
+//                     other types are converted through the caller's workspace);
+//   M  > 16, Q8_0     the decode kernel in passes of four rows.
+#include "common.cuh"
+
+namespace ub {
+template <typename XT>
+int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, cudaStream_t s);
+int q4k_gemm_mma(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
+}  // namespace ub
+
+namespace {
+
+constexpr int kDecodeMaxM = 16;
+
+__global__ void convert_f32_to_bf16_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ in, size_t n) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    out[i] = __float2bfloat16_rn(in[i]);
+}
+
+template <typename T>
+__global__ void convert_bf16_to_kernel(T* __restrict__ out, const __nv_bfloat16* __restrict__ in, size_t n) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    out[i] = ub::from_f32<T>(__bfloat162float(in[i]));
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+inline int conv_grid(size_t n) {
+  size_t b = (n + 255) / 256;
+  const size_t cap = static_cast<size_t>(ub::num_sms()) * 8;
+  return static_cast<int>(b > cap ? cap : (b ? b : 1));
+}
+
+// x_dtype: UB_DTYPE_F32 or UB_DTYPE_BF16
+int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype,
+            void* workspace, size_t ws_bytes, void* stream) {
+  if (M == 0 || N == 0) return ub::fail(UB_OK);
+  if (!y || !x || !wq || M < 0 || N < 0 || K <= 0) return ub::fail(UB_ERR_INVALID_ARG);
+  if (K % (is_q4k ? UB_QK_K : UB_QK8_0)) return ub::fail(UB_ERR_INVALID_ARG);
+  if (out_dtype != UB_DTYPE_F32 && out_dtype != UB_DTYPE_BF16 && out_dtype != UB_DTYPE_F16)
+    return ub::fail(UB_ERR_INVALID_ARG);
+  // 16-byte loads on activations and (Q4_K) weight rows
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (is_q4k && (reinterpret_cast<uintptr_t>(wq) & 15)) ||
+      (!is_q4k && (reinterpret_cast<uintptr_t>(wq) & 1)) || (x_dtype == UB_DTYPE_BF16 && (K % 8)) ||
+      (x_dtype == UB_DTYPE_F32 && (K % 4)))
+    return ub::fail(UB_ERR_INVALID_ARG);
+  cudaStream_t s = ub::as_stream(stream);
+
+  if (M <= kDecodeMaxM || !is_q4k) {
+    if (x_dtype == UB_DTYPE_F32)
+      return ub::qgemv<float>(is_q4k, y, static_cast<const float*>(x), wq, M, N, K, out_dtype, s);
+    return ub::qgemv<__nv_bfloat16>(is_q4k, y, static_cast<const __nv_bfloat16*>(x), wq, M, N, K, out_dtype, s);
+  }
+
+  // tensor-core path: bf16 in, bf16 out; convert around it when the caller's types differ
+  const size_t need = ub_qmatmul_workspace_bytes(M, N, K, 1);
+  const bool conv_in = x_dtype != UB_DTYPE_BF16, conv_out = out_dtype != UB_DTYPE_BF16;
+  if ((conv_in || conv_out) && (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)))
+    return ub::fail(UB_ERR_WORKSPACE);
+  char* ws = static_cast<char*>(workspace);
+  const void* xin = x;
+  void* yout = y;
+  if (conv_in) {
+    __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>(ws);
+    const size_t n = static_cast<size_t>(M) * K;
+    convert_f32_to_bf16_kernel<<<conv_grid(n), 256, 0, s>>>(xb, static_cast<const float*>(x), n);
+    xin = xb;
+  }
+  if (conv_out) yout = ws + align_up(static_cast<size_t>(M) * K * 2, 256);
+  int st = ub::q4k_gemm_mma(yout, xin, wq, M, N, K, s);
+  if (st != UB_OK) return st;
+  if (conv_out) {
+    const size_t n = static_cast<size_t>(M) * N;
+    if (out_dtype == UB_DTYPE_F32)
+      convert_bf16_to_kernel<float><<<conv_grid(n), 256, 0, s>>>(static_cast<float*>(y),
+                                                                static_cast<const __nv_bfloat16*>(yout), n);
+    else
+      convert_bf16_to_kernel<__half><<<conv_grid(n), 256, 0, s>>>(static_cast<__half*>(y),
+                                                                 static_cast<const __nv_bfloat16*>(yout), n);
+  }
+  return ub::check_launch();
+}
+
+}  // namespace
+
+extern "C" {
+
+// Scratch for the tensor-core path when the caller's activation or output type is not bf16:
+// a bf16 copy of x and a bf16 staging copy of y.  0 for the decode kernel and for Q8_0.
+size_t ub_qmatmul_workspace_bytes(int M, int N, int K, int is_q4k) {
+  if (M <= kDecodeMaxM || !is_q4k || M <= 0 || N <= 0 || K <= 0) return 0;
+  return align_up(static_cast<size_t>(M) * K * 2, 256) + align_up(static_cast<size_t>(M) * N * 2, 256);
+}
+
+int ub_qmatmul_q8_0_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace,
+                        size_t ws_bytes, void* stream) {
+  return qmatmul(false, UB_DTYPE_F32, y, x, wq, M, N, K, out_dtype, workspace, ws_bytes, stream);
+}
+int ub_qmatmul_q8_0_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace,
+                         size_t ws_bytes, void* stream) {
+  return qmatmul(false, UB_DTYPE_BF16, y, x, wq, M, N, K, out_dtype, workspace, ws_bytes, stream);
+}
+int ub_qmatmul_q4k_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace,
+                       size_t ws_bytes, void* stream) {
+  return qmatmul(true, UB_DTYPE_F32, y, x, wq, M, N, K, out_dtype, workspace, ws_bytes, stream);
+}
+int ub_qmatmul_q4k_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace,
+                        size_t ws_bytes, void* stream) {
+  return qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, out_dtype, workspace, ws_bytes, stream);
+}
+
+}  // extern "C"

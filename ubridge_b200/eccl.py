@@ -1,0 +1,149 @@
+"""Collectives with the reference's eccl surface (src/eccl.rs:14-426) over the NCCL-backed C-ABI.
+
+``Id`` is the 128-byte unique id shipped out of band (src/eccl.rs:24-43); ``Comm.from_rank`` is one rank
+per process or thread (src/eccl.rs:181-206); every collective enqueues on the stream given (the
+device's single stream in the reference, src/eccl.rs:209-413).
+"""
+from __future__ import annotations
+
+import ctypes
+
+from . import _lib
+from ._lib import EcclUniqueId, lib
+
+
+class EcclError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__("eccl: %s failed with result %d" % (what, code))
+        self.code = code
+
+
+class ReduceOp:
+    Sum, Prod, Max, Min, Avg = 0, 1, 2, 3, 4  # src/eccl.rs:45-61
+
+
+# ecclDataType_t (src/eccl.rs:86-96)
+Int8, Uint8, Int32, Uint32, Int64, Uint64, Float16, Float32, Float64, Bfloat16 = range(10)
+
+_FROM_UB_DTYPE = {_lib.DTYPE_F32: Float32, _lib.DTYPE_F16: Float16, _lib.DTYPE_BF16: Bfloat16,
+                  _lib.DTYPE_I32: Int32, _lib.DTYPE_I8: Int8, _lib.DTYPE_U8: Uint8}
+
+
+def eccl_dtype(ub_dtype: int) -> int:
+    return _FROM_UB_DTYPE[ub_dtype]
+
+
+def _ok(rc: int, what: str) -> None:
+    if rc != 0:
+        raise EcclError(rc, what)
+
+
+def _p(buf):
+    if buf is None:
+        return None
+    if hasattr(buf, "ptr"):
+        return ctypes.c_void_p(buf.ptr)
+    if isinstance(buf, ctypes.c_void_p):
+        return buf
+    return ctypes.c_void_p(int(buf))
+
+
+def get_version() -> int:
+    v = ctypes.c_int()
+    _ok(lib().ecclGetVersion(ctypes.byref(v)), "ecclGetVersion")
+    return v.value
+
+
+class Id:
+    def __init__(self, raw: bytes | None = None):
+        self._id = EcclUniqueId()
+        if raw is None:
+            _ok(lib().ecclGetUniqueId(ctypes.byref(self._id)), "ecclGetUniqueId")
+        else:
+            if len(raw) != 128:
+                raise ValueError("unique id is 128 bytes")
+            ctypes.memmove(ctypes.byref(self._id), raw, 128)
+
+    @classmethod
+    def uninit(cls, internal: bytes) -> "Id":  # src/eccl.rs:35-38
+        return cls(internal)
+
+    def internal(self) -> bytes:
+        return ctypes.string_at(ctypes.byref(self._id), 128)
+
+
+def group_start() -> None:
+    _ok(lib().ecclGroupStart(), "ecclGroupStart")
+
+
+def group_end() -> None:
+    _ok(lib().ecclGroupEnd(), "ecclGroupEnd")
+
+
+class Comm:
+    def __init__(self, handle, rank: int, world_size: int):
+        self._comm = handle
+        self.rank = rank
+        self.world_size = world_size
+
+    @classmethod
+    def from_rank(cls, rank: int, world_size: int, uid: Id) -> "Comm":
+        """The calling thread's current CUDA device becomes this rank's device."""
+        h = ctypes.c_void_p()
+        _ok(lib().ecclCommInitRank(ctypes.byref(h), world_size, uid._id, rank), "ecclCommInitRank")
+        return cls(h, rank, world_size)
+
+    @classmethod
+    def from_devices(cls, ordinals) -> list["Comm"]:  # src/eccl.rs:120-141
+        n = len(ordinals)
+        arr = (ctypes.c_void_p * n)()
+        devs = (ctypes.c_int * n)(*ordinals)
+        _ok(lib().ecclCommInitAll(arr, n, devs), "ecclCommInitAll")
+        return [cls(ctypes.c_void_p(arr[i]), i, n) for i in range(n)]
+
+    def count(self) -> int:
+        v = ctypes.c_int()
+        _ok(lib().ecclCommCount(self._comm, ctypes.byref(v)), "ecclCommCount")
+        return v.value
+
+    def device(self) -> int:
+        v = ctypes.c_int()
+        _ok(lib().ecclCommDevice(self._comm, ctypes.byref(v)), "ecclCommDevice")
+        return v.value
+
+    def user_rank(self) -> int:
+        v = ctypes.c_int()
+        _ok(lib().ecclCommUserRank(self._comm, ctypes.byref(v)), "ecclCommUserRank")
+        return v.value
+
+    def all_reduce(self, send, recv, count: int, dtype: int, op: int = ReduceOp.Sum, stream=None) -> None:
+        _ok(lib().ecclAllReduce(_p(send), _p(recv), count, dtype, op, self._comm, _p(stream)), "ecclAllReduce")
+
+    def reduce(self, send, recv, count: int, dtype: int, op: int, root: int, stream=None) -> None:
+        _ok(lib().ecclReduce(_p(send), _p(recv), count, dtype, op, root, self._comm, _p(stream)), "ecclReduce")
+
+    def broadcast(self, send, recv, count: int, dtype: int, root: int, stream=None) -> None:
+        _ok(lib().ecclBroadcast(_p(send), _p(recv), count, dtype, root, self._comm, _p(stream)), "ecclBroadcast")
+
+    def all_gather(self, send, recv, sendcount: int, dtype: int, stream=None) -> None:
+        _ok(lib().ecclAllGather(_p(send), _p(recv), sendcount, dtype, self._comm, _p(stream)), "ecclAllGather")
+
+    def reduce_scatter(self, send, recv, recvcount: int, dtype: int, op: int = ReduceOp.Sum, stream=None) -> None:
+        _ok(lib().ecclReduceScatter(_p(send), _p(recv), recvcount, dtype, op, self._comm, _p(stream)),
+            "ecclReduceScatter")
+
+    def send(self, buf, count: int, dtype: int, peer: int, stream=None) -> None:
+        _ok(lib().ecclSend(_p(buf), count, dtype, peer, self._comm, _p(stream)), "ecclSend")
+
+    def recv(self, buf, count: int, dtype: int, peer: int, stream=None) -> None:
+        _ok(lib().ecclRecv(_p(buf), count, dtype, peer, self._comm, _p(stream)), "ecclRecv")
+
+    def destroy(self) -> None:
+        if self._comm:
+            lib().ecclCommDestroy(self._comm)
+            self._comm = None
+
+    def abort(self) -> None:  # the reference's Drop aborts the communicator (src/eccl.rs:63-70)
+        if self._comm:
+            lib().ecclCommAbort(self._comm)
+            self._comm = None

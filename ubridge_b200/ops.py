@@ -1,0 +1,141 @@
+"""Python entry points of the quantized-linear + fused-MoE path: one function per C-ABI export.
+
+Buffers are device pointers: a :class:`~ubridge_b200.device.GcuSlice`, an int address (for example
+``tensor.data_ptr()``), or None.  ``stream`` is a ``cudaStream_t`` as int / ``c_void_p`` (None = default
+stream).  Every call enqueues and returns; nothing here synchronises.
+"""
+from __future__ import annotations
+
+import ctypes
+
+from . import _lib
+from ._lib import DTYPE_BF16, DTYPE_F16, DTYPE_F32, check, check_last, lib
+
+_SUFFIX = {DTYPE_F32: "f32", DTYPE_F16: "f16", DTYPE_BF16: "bf16"}
+
+
+def _p(buf):
+    if buf is None:
+        return None
+    if hasattr(buf, "ptr"):
+        return ctypes.c_void_p(buf.ptr)
+    if isinstance(buf, ctypes.c_void_p):
+        return buf
+    return ctypes.c_void_p(int(buf))
+
+
+def _s(stream):
+    if stream is None or isinstance(stream, ctypes.c_void_p):
+        return stream
+    return ctypes.c_void_p(int(stream))
+
+
+# ----------------------------------------------------------------------------- GGUF blocks
+def dequantize_q8_0(out, blocks, numel: int, out_dtype: int, stream=None) -> None:
+    check(lib().ub_dequant_q8_0(_p(out), _p(blocks), numel, out_dtype, _s(stream)), "ub_dequant_q8_0")
+
+
+def dequantize_q4k(out, blocks, numel: int, out_dtype: int, stream=None) -> None:
+    check(lib().ub_dequant_q4k(_p(out), _p(blocks), numel, out_dtype, _s(stream)), "ub_dequant_q4k")
+
+
+def quantize_q8_0(blocks, x, numel: int, in_dtype: int, stream=None) -> None:
+    check(lib().ub_quantize_q8_0(_p(blocks), _p(x), numel, in_dtype, _s(stream)), "ub_quantize_q8_0")
+
+
+def repack_to_split(split, interleaved, nblocks: int, is_q4k: bool, stream=None) -> None:
+    check(lib().ub_repack_to_split(_p(split), _p(interleaved), nblocks, int(is_q4k), _s(stream)), "ub_repack_to_split")
+
+
+def repack_to_interleaved(interleaved, split, nblocks: int, is_q4k: bool, stream=None) -> None:
+    check(lib().ub_repack_to_interleaved(_p(interleaved), _p(split), nblocks, int(is_q4k), _s(stream)),
+          "ub_repack_to_interleaved")
+
+
+# ----------------------------------------------------------------------------- quantized matmul
+def qmatmul_workspace_bytes(M: int, N: int, K: int, is_q4k: bool) -> int:
+    return lib().ub_qmatmul_workspace_bytes(M, N, K, int(is_q4k))
+
+
+def qmatmul(y, x, wq, M: int, N: int, K: int, *, is_q4k: bool, x_dtype: int, out_dtype: int, workspace=None,
+            ws_bytes: int = 0, stream=None) -> None:
+    """y[M,N] = x[M,K] . W^T with W given as interleaved GGUF blocks (Q4_K when is_q4k else Q8_0)."""
+    if x_dtype not in (DTYPE_F32, DTYPE_BF16):
+        raise _lib.UbridgeError(_lib.UB_ERR_INVALID_ARG, "qmatmul: activations must be f32 or bf16")
+    name = "ub_qmatmul_%s_%s" % ("q4k" if is_q4k else "q8_0", _SUFFIX[x_dtype])
+    check(getattr(lib(), name)(_p(y), _p(x), _p(wq), M, N, K, out_dtype, _p(workspace), ws_bytes, _s(stream)), name)
+
+
+# ----------------------------------------------------------------------------- MoE (reference names)
+def topk_softmax(logits, weights, indices, num_tokens: int, num_experts: int, topk: int, norm_topk_prob: bool,
+                 dtype: int, stream=None) -> None:
+    name = "topk_softmax_" + _SUFFIX[dtype]
+    getattr(lib(), name)(_p(logits), _p(weights), _p(indices), num_tokens, num_experts, topk, int(norm_topk_prob),
+                         _s(stream))
+    check_last(name)
+
+
+def moe_align_block_size(sorted_ids, experts_ids, num_tokens_post_pad, topk_ids, num_experts: int, block_size: int,
+                         token_num: int, topk: int, real_token_num=None, expert_map=None, stream=None) -> None:
+    lib().moe_align_block_size(_p(sorted_ids), _p(experts_ids), _p(num_tokens_post_pad), _p(topk_ids),
+                               _p(real_token_num), _p(expert_map), num_experts, block_size, token_num, topk,
+                               _s(stream))
+    check_last("moe_align_block_size")
+
+
+def moe_align_sizes(token_num: int, topk: int, num_experts: int, block_size: int):
+    """(len(sorted_ids), len(experts_ids)) the caller must allocate (kernels/moe_align_host.cpp:56-58)."""
+    max_padded = token_num * topk + num_experts * (block_size - 1)
+    return max_padded, max_padded // block_size
+
+
+def invoke_fused_moe(C, A, B, bias, topk_weights, sorted_ids, experts_ids, num_tokens_post_pad, M: int, K: int, N: int,
+                     E: int, topk_ids_size: int, top_k: int, block_size: int, mul_routed_weight: bool,
+                     bias_flag: bool, dtype: int, stream=None) -> None:
+    name = "invoke_fused_moe_" + _SUFFIX[dtype]
+    getattr(lib(), name)(_p(C), _p(A), _p(B), _p(bias), _p(topk_weights), _p(sorted_ids), _p(experts_ids),
+                         _p(num_tokens_post_pad), M, K, N, E, topk_ids_size, top_k, block_size,
+                         int(mul_routed_weight), int(bias_flag), _s(stream))
+    check_last(name)
+
+
+def moe_combine(y, e_out, w, idx, top, N: int, K: int, M: int, topk: int, dtype: int, stream=None) -> None:
+    name = "moe_" + _SUFFIX[dtype]
+    getattr(lib(), name)(_p(y), _p(e_out), _p(w), _p(idx), _p(top), N, K, M, topk, _s(stream))
+    check_last(name)
+
+
+def indexed_moe(inp, w, out, indices, N: int, K: int, M: int, batch: int, topk: int, num_experts: int, dtype: int,
+                stream=None) -> None:
+    name = "indexed_moe_" + _SUFFIX[dtype]
+    getattr(lib(), name)(_p(inp), _p(w), _p(out), _p(indices), N, K, M, batch, topk, num_experts, _s(stream))
+    check_last(name)
+
+
+# ----------------------------------------------------------------------------- MoE (fused Q4_K)
+def silu_and_mul(out, inp, rows: int, D: int, dtype: int, stream=None) -> None:
+    check(lib().ub_silu_and_mul(_p(out), _p(inp), rows, D, dtype, _s(stream)), "ub_silu_and_mul")
+
+
+def topk_sum(out, inp, T: int, topk: int, H: int, dtype: int, stream=None) -> None:
+    check(lib().ub_topk_sum(_p(out), _p(inp), T, topk, H, dtype, _s(stream)), "ub_topk_sum")
+
+
+def fused_moe_q4k_gemm(C, A, Bq, topk_weights, sorted_ids, experts_ids, num_tokens_post_pad, M: int, K: int, N: int,
+                       E: int, topk_ids_size: int, top_k: int, block_size: int, mul_routed_weight: bool,
+                       act_silu_mul: bool, workspace=None, ws_bytes: int = 0, stream=None) -> None:
+    check(lib().ub_fused_moe_q4k_gemm(_p(C), _p(A), _p(Bq), _p(topk_weights), _p(sorted_ids), _p(experts_ids),
+                                      _p(num_tokens_post_pad), M, K, N, E, topk_ids_size, top_k, block_size,
+                                      int(mul_routed_weight), int(act_silu_mul), _p(workspace), ws_bytes, _s(stream)),
+          "ub_fused_moe_q4k_gemm")
+
+
+def moe_layer_q4k_workspace_bytes(T: int, H: int, I: int, E: int, top_k: int, block_size: int) -> int:
+    return lib().ub_moe_layer_q4k_workspace_bytes(T, H, I, E, top_k, block_size)
+
+
+def moe_layer_q4k(out, hidden, router_logits, w13q, w2q, T: int, H: int, I: int, E: int, top_k: int, block_size: int,
+                  norm_topk_prob: bool, workspace, ws_bytes: int, expert_map=None, stream=None) -> None:
+    check(lib().ub_moe_layer_q4k(_p(out), _p(hidden), _p(router_logits), _p(w13q), _p(w2q), _p(expert_map), T, H, I, E,
+                                 top_k, block_size, int(norm_topk_prob), _p(workspace), ws_bytes, _s(stream)),
+          "ub_moe_layer_q4k")
