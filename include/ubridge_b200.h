@@ -146,6 +146,16 @@ int ub_qmatmul_q8_0_f32(void* y, const void* x, const void* wq, int M, int N, in
 int ub_qmatmul_q8_0_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 int ub_qmatmul_q4k_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 int ub_qmatmul_q4k_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
+/* No counterpart in the reference.  ub_qmatmul_q4k_f32 without a workspace argument, for hosts that
+ * cannot give the library device memory of their own: a plugin that only receives input and output
+ * pointers from its framework, or a serving loop whose memory pool is closed after start-up, where a
+ * cudaMalloc would either fail or stall every stream.  The scratch of the M > 16 path is a fixed
+ * 8 MiB array in the library's device image (held by every GPU that loads the library until the
+ * process exits); the call allocates nothing.  Limit: ub_qmatmul_workspace_bytes(M,N,K,1) <= 8 MiB,
+ * i.e. about M*(K+N) <= 4M elements; beyond it the call returns UB_ERR_TOO_LARGE.  The first call on a
+ * device looks up the array's address and should come before any stream capture.  Calls share the
+ * array: do not let two of them overlap on one GPU. */
+int ub_qmatmul_q4k_f32_static(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* stream);
 
 /* ------------------------------------------------------------------ MoE: reference-named host launchers */
 /* src/ffi.rs:205-236, kernels/topk_softmax_host.cpp:178-208 */

@@ -7,6 +7,8 @@
 //   M  > 16, Q4_K     tensor-core GEMM with in-kernel dequantisation (bf16 activations and output;
 //                     other types are converted through the caller's workspace);
 //   M  > 16, Q8_0     the decode kernel in passes of four rows.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ub {
@@ -90,6 +92,36 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
   return ub::check_launch();
 }
 
+// ---- scratch of ub_qmatmul_q4k_f32_static: lives in the library's device image, one copy per GPU ----
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(8) << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a kernel may use.
+// The device address is looked up once per device (with that device current) and cached here.
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {nullptr};
+
+int static_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      ub::set_cuda_error(e);
+      return ub::fail(UB_ERR_CUDA);
+    }
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return UB_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -116,6 +148,24 @@ int ub_qmatmul_q4k_f32(void* y, const void* x, const void* wq, int M, int N, int
 int ub_qmatmul_q4k_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace,
                         size_t ws_bytes, void* stream) {
   return qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, out_dtype, workspace, ws_bytes, stream);
+}
+
+// ub_qmatmul_q4k_f32 for callers that have no way to hand over a workspace: the type-conversion
+// scratch of the M > 16 path sits in a fixed 8 MiB array inside the library's device image instead of
+// a caller buffer, and this function never allocates (no cudaMalloc / cudaFree, no allocating library
+// call).  Shapes whose scratch need (ub_qmatmul_workspace_bytes) exceeds 8 MiB get UB_ERR_TOO_LARGE.
+// The first call on each device resolves the array's device address; make that call outside any
+// stream capture.  All calls on a device share the one array, so two calls that can overlap on the
+// GPU (different streams) race on it; nothing in it has to start at zero, every byte that is read is
+// written earlier in the same call.
+int ub_qmatmul_q4k_f32_static(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype,
+                              void* stream) {
+  const size_t need = ub_qmatmul_workspace_bytes(M, N, K, 1);
+  if (need > kStaticScratchBytes) return ub::fail(UB_ERR_TOO_LARGE);
+  void* scratch = nullptr;
+  const int st = static_scratch(&scratch);
+  if (st != UB_OK) return st;
+  return qmatmul(true, UB_DTYPE_F32, y, x, wq, M, N, K, out_dtype, scratch, kStaticScratchBytes, stream);
 }
 
 }  // extern "C"

@@ -66,6 +66,14 @@ def qmatmul(y, x, wq, M: int, N: int, K: int, *, is_q4k: bool, x_dtype: int, out
     check(getattr(lib(), name)(_p(y), _p(x), _p(wq), M, N, K, out_dtype, _p(workspace), ws_bytes, _s(stream)), name)
 
 
+def qmatmul_q4k_f32_static(y, x, wq, M: int, N: int, K: int, out_dtype: int, stream=None) -> None:
+    """Q4_K matmul with f32 activations that takes no workspace and allocates nothing: its scratch is a
+    fixed 8 MiB array inside the library (so roughly M*(K+N) <= 4M elements, else UB_ERR_TOO_LARGE).
+    For hosts that cannot provide device memory themselves.  Calls on one GPU must not overlap."""
+    check(lib().ub_qmatmul_q4k_f32_static(_p(y), _p(x), _p(wq), M, N, K, out_dtype, _s(stream)),
+          "ub_qmatmul_q4k_f32_static")
+
+
 # ----------------------------------------------------------------------------- MoE (reference names)
 def topk_softmax(logits, weights, indices, num_tokens: int, num_experts: int, topk: int, norm_topk_prob: bool,
                  dtype: int, stream=None) -> None:
