@@ -39,6 +39,10 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# dram__bytes_read + dram__bytes_write of ONE launch of the workload's dominant kernel, from the ncu
+# captures summarised under profiles/ (null where no capture has been taken yet)
+NCU_TRAFFIC_BYTES = {"c2_m1": 33103104}
+
 Q4K_ROW_BYTES = lambda K: K // 256 * 144  # noqa: E731
 Q8_ROW_BYTES = lambda K: K // 32 * 34  # noqa: E731
 
@@ -309,6 +313,7 @@ def run_linear(args, wl, rank, world, torch, dist):
         roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["source"],
                 "algorithmic_flops_per_launch": 2.0 * M * N * K, "avg_launch_us": avg_launch_s * 1e6}
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
     return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
                 dtype="u4+f16 scales -> f32 accumulate" if is_q4k else "i8+f16 scales -> f32 accumulate")
 
