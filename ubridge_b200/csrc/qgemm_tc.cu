@@ -1,0 +1,354 @@
+// Prefill GEMM for Q4_K weights on the 5th-generation tensor cores (tcgen05 / TMEM), with the
+// dequantisation fused into the main loop.
+//
+//   y[M,N] (bf16) = x[M,K] (bf16) . dequant(Wq[N rows of K/256 super-blocks])^T,   f32 accumulation.
+//
+// Replaces the reference's two-kernel sequence dequantize_block_q4_k_* (kernels/quant.cpp:477-488) +
+// matmul_bf16 (kernels/matmul.cpp:1143-1184), whose W4 flavour dequantises a weight tile in on-chip memory
+// and then calls the matrix engine (kernels/matmul.cpp:1039-1109).
+//
+// Tile and roles.  One persistent CTA per SM walks over (128 weight rows) x (TOK tokens) output tiles.
+// The weight tile is the UMMA "A" operand (M = 128), the token tile the "B" operand (N = TOK <= 256), both
+// K-major bf16 in the 128-byte-swizzled canonical layout; the accumulator D[128 lanes x TOK columns] lives
+// in tensor memory, double buffered (2 x 256 columns) so the epilogue of one tile overlaps the main loop
+// of the next.  K is consumed 64 values per stage (one 64-value Q4_K group), four UMMA K=16 steps each.
+//
+//   warp 0        allocates TMEM, then one elected lane issues tcgen05.mma and tcgen05.commit
+//   warps 1-4     epilogue: tcgen05.ld -> bf16 -> global (lane = weight row, columns = tokens)
+//   warps 5-12    producers: copy the token tile (plain 16-byte loads; rows may later be gathered) and
+//                 dequantise the weight tile straight into the swizzled layout: nibbles become bf16
+//                 (128 + q) with one byte permute per pair, minus 128 (exact), times d*sc minus dmin*m
+//                 with packed bf16 FMAs; then fence.proxy.async + mbarrier arrive
+//
+// Every mbarrier wait is bounded; on expiry the CTA sets a shared abort flag, records UB_ERR_TIMEOUT in
+// the device error word, all roles leave their loops, and TMEM is freed before the kernel returns.
+#include "common.cuh"
+
+namespace {
+
+using namespace ub;
+
+constexpr int kTcThreads = 13 * 32;
+constexpr int kTcProducerWarps = 8;
+constexpr int kTcBK = 64;
+constexpr uint32_t kTcWaitLimit = 2000000;
+
+__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait that also gives up when another role has raised the abort flag.
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kTcWaitLimit; i++) {
+    if (tc_mbar_try(bar, parity)) return true;
+    if ((i & 1023) == 1023 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
+  // K-major, 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), LBO unused (1), descriptor version 1
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+      "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// Two nibbles (bytes A and B of a word masked with 0x0F0F0F0F) -> packed bf16 (dsc*qA - dm, dsc*qB - dm)
+template <int SEL>
+__device__ __forceinline__ uint32_t deq_pair(uint32_t w4, __nv_bfloat162 dsc, __nv_bfloat162 ndm) {
+  const uint32_t biased = __byte_perm(w4, 0x43434343u, SEL);  // bf16 (128 + q) in each half
+  const uint32_t c128 = 0x43004300u;
+  const __nv_bfloat162 q = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&biased),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&c128));
+  return bf162_bits(__hfma2(q, dsc, ndm));
+}
+
+struct TcShared {
+  unsigned long long full[4], empty[4], tmem_full[2], tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// TOK: tokens per tile (UMMA N): 64, 128 or 256.  STAGES: ring depth.
+template <int TOK, int STAGES>
+__global__ void __launch_bounds__(kTcThreads, 1)
+qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
+                    int M, int N, int K, int* err_word) {
+  extern __shared__ __align__(1024) unsigned char tc_smem[];
+  __shared__ TcShared sh;
+  constexpr uint32_t kABytes = 128 * 128;        // 128 weight rows x 64 bf16
+  constexpr uint32_t kBBytes = TOK * 128;        // TOK token rows x 64 bf16
+  constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this round-up
+  const uint32_t smem_raw = static_cast<uint32_t>(__cvta_generic_to_shared(tc_smem));
+  const uint32_t smem_base = (smem_raw + 1023u) & ~1023u;
+  unsigned char* const tiles = tc_smem + (smem_base - smem_raw);
+  const uint32_t bars = static_cast<uint32_t>(__cvta_generic_to_shared(&sh));
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 32u + 8u * s; };
+  auto tfull_bar = [&](int b) { return bars + 64u + 8u * b; };
+  auto tempty_bar = [&](int b) { return bars + 80u + 8u * b; };
+  volatile int* abort_flag = &sh.abort_flag;
+
+  const int w_tiles = (N + 127) / 128, t_tiles = (M + TOK - 1) / TOK;
+  const int ntiles = w_tiles * t_tiles;
+  const int ksteps = K / kTcBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      tc_mbar_init(full_bar(s), kTcProducerWarps);
+      tc_mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      tc_mbar_init(tfull_bar(b), 1);
+      tc_mbar_init(tempty_bar(b), 4);
+    }
+    sh.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(&sh.tmem_base));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D = f32, A = B = bf16, both K-major, N = TOK, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TOK >> 3) << 17) | (8u << 24);
+      int s = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      int buf = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        ok = tc_wait(tempty_bar(buf), acc_phase ^ 1, abort_flag);  // epilogue has drained this accumulator
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * 256u;
+        for (int ks = 0; ks < ksteps; ks++) {
+          ok = tc_wait(full_bar(s), phase, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_base + s * kStageBytes, b_addr = a_addr + kABytes;
+          const uint64_t a_desc = make_sw128_desc(a_addr), b_desc = make_sw128_desc(b_addr);
+#pragma unroll
+          for (int j = 0; j < 4; j++)  // K = 16 per instruction: 32 bytes further inside the 128-byte swizzle row
+            umma_bf16(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+          umma_commit(empty_bar(s));  // stage is free once these MMAs have read it
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(buf));  // accumulator complete
+        if (++buf == 2) {
+          buf = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else if (warp <= 4) {
+    // ------------------------------------------------------------ epilogue (TMEM lanes 32*(warp%4) ..)
+    const int lane_base = 32 * (warp & 3);
+    uint32_t acc_phase = 0;
+    int buf = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      const int wt = tile / t_tiles, tt = tile - wt * t_tiles;
+      ok = __all_sync(0xFFFFFFFFu, tc_wait(tfull_bar(buf), acc_phase, abort_flag));  // warp-uniform
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int n = wt * 128 + lane_base + lane;  // weight row = output column
+      const int m0 = tt * TOK;
+#pragma unroll 1
+      for (int c = 0; c < TOK; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + static_cast<uint32_t>(buf * 256 + c), v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int m = m0 + c + j;
+            if (m < M) y[static_cast<size_t>(m) * N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) tc_mbar_arrive(tempty_bar(buf));
+      if (++buf == 2) {
+        buf = 0;
+        acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ producers (256 threads)
+    const int p = threadIdx.x - 5 * 32;        // 0..255
+    const int wrow = p & 127, half = p >> 7;   // weight row inside the tile; 0 = low nibbles, 1 = high nibbles
+    const int nsb = K >> 8;
+    const size_t row_bytes = static_cast<size_t>(nsb) * UB_Q4K_BYTES;
+    int s = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      const int wt = tile / t_tiles, tt = tile - wt * t_tiles;
+      const int n = wt * 128 + wrow;
+      const bool n_ok = n < N;
+      const uint8_t* wrow_ptr = wq + static_cast<size_t>(n_ok ? n : 0) * row_bytes;
+      const int m0 = tt * TOK;
+      float d = 0.f, dmin = 0.f;
+      uint32_t scw[2] = {0, 0}, mnw[2] = {0, 0};
+      for (int ks = 0; ks < ksteps; ks++) {
+        const int sb = ks >> 2, G = ks & 3;
+        // global loads first, so that they are in flight while waiting for the stage
+        const uint8_t* blk = wrow_ptr + static_cast<size_t>(sb) * UB_Q4K_BYTES;
+        if (G == 0) {
+          const uint4 h = __ldg(reinterpret_cast<const uint4*>(blk));
+          d = half_bits_to_f32(h.x);
+          dmin = half_bits_to_f32(h.x >> 16);
+          q4k_unpack_scales(h.y, h.z, h.w, scw[0], scw[1], mnw[0], mnw[1]);
+        }
+        const uint4 qa = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * G));
+        const uint4 qb = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * G));
+        uint4 xv[(TOK * 8 + 255) / 256];
+#pragma unroll
+        for (int i = 0; i < (TOK * 8 + 255) / 256; i++) {
+          const int idx = p + 256 * i;             // chunk index over TOK rows x 8 chunks
+          const int r = idx >> 3, c = idx & 7;
+          const int m = m0 + r;
+          xv[i] = (idx < TOK * 8 && m < M)
+                      ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * K + ks * kTcBK + 8 * c))
+                      : make_uint4(0, 0, 0, 0);
+        }
+        ok = __all_sync(0xFFFFFFFFu, tc_wait(empty_bar(s), phase ^ 1, abort_flag));  // warp-uniform
+        if (!ok) break;
+        unsigned char* a_tile = tiles + static_cast<size_t>(s) * kStageBytes;
+        unsigned char* b_tile = a_tile + kABytes;
+        // token tile: row r, 16-byte chunk c -> position c ^ (r & 7)
+#pragma unroll
+        for (int i = 0; i < (TOK * 8 + 255) / 256; i++) {
+          const int idx = p + 256 * i;
+          const int r = idx >> 3, c = idx & 7;
+          if (idx < TOK * 8) *reinterpret_cast<uint4*>(b_tile + r * 128 + ((c ^ (r & 7)) << 4)) = xv[i];
+        }
+        // weight tile: this thread's 32 values are sub-block 2G + half of its row
+        {
+          const int j = 2 * G + half;
+          const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
+          const float dscf = n_ok ? d * static_cast<float>(sc) : 0.f, dmf = n_ok ? dmin * static_cast<float>(mn) : 0.f;
+          const __nv_bfloat162 dsc = __float2bfloat162_rn(dscf), ndm = __float2bfloat162_rn(-dmf);
+          const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+          for (int cc = 0; cc < 4; cc++) {  // 8 values = bytes 8cc .. 8cc+7
+            const uint32_t w0 = half ? (w[2 * cc] >> 4) & 0x0F0F0F0Fu : w[2 * cc] & 0x0F0F0F0Fu;
+            const uint32_t w1 = half ? (w[2 * cc + 1] >> 4) & 0x0F0F0F0Fu : w[2 * cc + 1] & 0x0F0F0F0Fu;
+            uint4 o;
+            o.x = deq_pair<0x4140>(w0, dsc, ndm);
+            o.y = deq_pair<0x4342>(w0, dsc, ndm);
+            o.z = deq_pair<0x4140>(w1, dsc, ndm);
+            o.w = deq_pair<0x4342>(w1, dsc, ndm);
+            const int c = 4 * half + cc;
+            *reinterpret_cast<uint4*>(a_tile + wrow * 128 + ((c ^ (wrow & 7)) << 4)) = o;
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+        __syncwarp();
+        if (lane == 0) tc_mbar_arrive(full_bar(s));
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  }
+
+  // ---- teardown: every role arrives here, whether it finished or gave up ----
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (threadIdx.x == 0 && sh.abort_flag) report_device_error(err_word, UB_ERR_TIMEOUT);
+  if (warp == 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+template <int TOK, int STAGES>
+int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(STAGES) * (128 * 128 + TOK * 128) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(qgemm_q4k_tc_kernel<TOK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  const int tiles = ((N + 127) / 128) * ((M + TOK - 1) / TOK);
+  const int sms = ub::num_sms();
+  const int grid = tiles < sms ? tiles : sms;
+  qgemm_q4k_tc_kernel<TOK, STAGES><<<grid, kTcThreads, smem, s>>>(
+      static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq), M, N, K,
+      ub::device_error_word());
+  return ub::check_launch();
+}
+
+}  // namespace
+
+namespace ub {
+
+// y (bf16) [M,N] = x (bf16) [M,K] . dequant(Wq)^T on tcgen05; K % 256 == 0, pointers 16-byte aligned.
+int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
+  if (M <= 64) return launch_tc<64, 4>(y, x, wq, M, N, K, s);
+  if (M <= 128) return launch_tc<128, 4>(y, x, wq, M, N, K, s);
+  return launch_tc<256, 4>(y, x, wq, M, N, K, s);
+}
+
+}  // namespace ub

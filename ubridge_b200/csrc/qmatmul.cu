@@ -4,7 +4,7 @@
 // small-M special cases :502-514) and kernels/matmul.cpp:1197-1208 (LHS-resident decode kernel when it
 // fits, batched kernel otherwise).  The same idea here is a three-way split on M:
 //   M <= 16           bandwidth-bound decode GEMV (qgemv.cu), f32 or bf16 activations, no workspace;
-//   M  > 16, Q4_K     tensor-core GEMM with in-kernel dequantisation (bf16 activations and output;
+//   M  > 16, Q4_K     tcgen05 tensor-core GEMM with in-kernel dequantisation (bf16 activations and output;
 //                     other types are converted through the caller's workspace);
 //   M  > 16, Q8_0     the decode kernel in passes of four rows.
 #include <mutex>
@@ -15,6 +15,7 @@ namespace ub {
 template <typename XT>
 int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, cudaStream_t s);
 int q4k_gemm_mma(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
+int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
 }  // namespace ub
 
 namespace {
@@ -78,7 +79,7 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
     xin = xb;
   }
   if (conv_out) yout = ws + align_up(static_cast<size_t>(M) * K * 2, 256);
-  int st = ub::q4k_gemm_mma(yout, xin, wq, M, N, K, s);
+  int st = ub::q4k_gemm_tc(yout, xin, wq, M, N, K, s);
   if (st != UB_OK) return st;
   if (conv_out) {
     const size_t n = static_cast<size_t>(M) * N;
