@@ -233,61 +233,109 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
     }
   } else {
     // ------------------------------------------------------------ producers (256 threads)
+    // One flat loop over (tile, super-block), four K steps (the super-block's four 64-value groups) per
+    // iteration.  Latency is hidden by distance, not by occupancy:
+    //  * token tiles travel as 16-byte asynchronous copies straight to their swizzled position, issued
+    //    TWO steps ahead of the step being dequantised;
+    //  * a thread keeps the 4 x 32 bytes of nibbles of its row's current super-block in registers and
+    //    refills each 32-byte piece with the next super-block's right after using it (four steps ahead);
+    //    the 16-byte header is fetched one super-block ahead.
     const int p = threadIdx.x - 5 * 32;        // 0..255
     const int wrow = p & 127, half = p >> 7;   // weight row inside the tile; 0 = low nibbles, 1 = high nibbles
     const int nsb = K >> 8;
     const size_t row_bytes = static_cast<size_t>(nsb) * UB_Q4K_BYTES;
-    int s = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      const int wt = tile / t_tiles, tt = tile - wt * t_tiles;
-      const int n = wt * 128 + wrow;
-      const bool n_ok = n < N;
-      const uint8_t* wrow_ptr = wq + static_cast<size_t>(n_ok ? n : 0) * row_bytes;
+    const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int total_sb = my_tiles * nsb;      // super-block iterations
+    const int total = total_sb * 4;           // K steps
+    constexpr int kXChunks = (TOK * 8 + 255) / 256;  // 16-byte token-tile chunks per thread and step
+
+    // token tile of step `it` -> `stage`, asynchronously
+    auto issue_x = [&](int it, int stage) {
+      const int ti = it / ksteps, ks = it - ti * ksteps;
+      const int tile = blockIdx.x + ti * gridDim.x;
+      const int tt = tile % t_tiles;
       const int m0 = tt * TOK;
-      float d = 0.f, dmin = 0.f;
-      uint32_t scw[2] = {0, 0}, mnw[2] = {0, 0};
-      for (int ks = 0; ks < ksteps; ks++) {
-        const int sb = ks >> 2, G = ks & 3;
-        // global loads first, so that they are in flight while waiting for the stage
-        const uint8_t* blk = wrow_ptr + static_cast<size_t>(sb) * UB_Q4K_BYTES;
-        if (G == 0) {
-          const uint4 h = __ldg(reinterpret_cast<const uint4*>(blk));
-          d = half_bits_to_f32(h.x);
-          dmin = half_bits_to_f32(h.x >> 16);
-          q4k_unpack_scales(h.y, h.z, h.w, scw[0], scw[1], mnw[0], mnw[1]);
-        }
-        const uint4 qa = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * G));
-        const uint4 qb = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * G));
-        uint4 xv[(TOK * 8 + 255) / 256];
+      const uint32_t b_tile = smem_base + stage * kStageBytes + kABytes;
 #pragma unroll
-        for (int i = 0; i < (TOK * 8 + 255) / 256; i++) {
-          const int idx = p + 256 * i;             // chunk index over TOK rows x 8 chunks
-          const int r = idx >> 3, c = idx & 7;
+      for (int i = 0; i < kXChunks; i++) {
+        const int idx = p + 256 * i;  // chunk index over TOK rows x 8 chunks
+        const int r = idx >> 3, c = idx & 7;
+        if (idx < TOK * 8) {
           const int m = m0 + r;
-          xv[i] = (idx < TOK * 8 && m < M)
-                      ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * K + ks * kTcBK + 8 * c))
-                      : make_uint4(0, 0, 0, 0);
+          const bool in = m < M;
+          const __nv_bfloat16* src = x + static_cast<size_t>(in ? m : 0) * K + ks * kTcBK + 8 * c;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(b_tile + r * 128 + ((c ^ (r & 7)) << 4)),
+                       "l"(src), "r"(in ? 16 : 0)
+                       : "memory");
         }
-        ok = __all_sync(0xFFFFFFFFu, tc_wait(empty_bar(s), phase ^ 1, abort_flag));  // warp-uniform
+      }
+    };
+    // address of this thread's row's super-block for flat super-block index q (clamped to valid memory)
+    auto sb_ptr = [&](int q) {
+      const int ti = q / nsb, sb = q - ti * nsb;
+      const int tile = blockIdx.x + ti * gridDim.x;
+      const int n = (tile / t_tiles) * 128 + wrow;
+      return wq + static_cast<size_t>(n < N ? n : 0) * row_bytes + static_cast<size_t>(sb) * UB_Q4K_BYTES;
+    };
+
+    int s = 0;             // stage of the step being dequantised
+    uint32_t phase = 0;
+    int sx = 0;            // stage the next token tile goes to (runs two steps ahead)
+    uint32_t phase_x = 0;
+    int it_x = 0;          // next step whose token tile has not been issued yet
+    bool ok = true;
+    auto advance_x = [&]() {
+      // issue the token tile of step it_x (if any) once its stage is free; always commits one group
+      if (it_x < total && ok) {
+        ok = __all_sync(0xFFFFFFFFu, tc_wait(empty_bar(sx), phase_x ^ 1, abort_flag));
+        if (ok) {
+          issue_x(it_x, sx);
+          it_x++;
+          if (++sx == STAGES) {
+            sx = 0;
+            phase_x ^= 1;
+          }
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    uint4 hdr = make_uint4(0, 0, 0, 0), qa[4], qb[4];
+    if (total_sb > 0) {
+      const uint8_t* blk = sb_ptr(0);
+      hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+#pragma unroll
+      for (int G = 0; G < 4; G++) {
+        qa[G] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * G));
+        qb[G] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * G));
+      }
+      advance_x();
+      advance_x();
+    }
+    for (int q = 0; q < total_sb && ok; q++) {
+      const int ti = q / nsb;
+      const int tile = blockIdx.x + ti * gridDim.x;
+      const bool n_ok = (tile / t_tiles) * 128 + wrow < N;
+      const float d = half_bits_to_f32(hdr.x), dmin = half_bits_to_f32(hdr.x >> 16);
+      uint32_t scw[2], mnw[2];
+      q4k_unpack_scales(hdr.y, hdr.z, hdr.w, scw[0], scw[1], mnw[0], mnw[1]);
+      const bool more = q + 1 < total_sb;
+      const uint8_t* nblk = sb_ptr(more ? q + 1 : q);
+      hdr = __ldg(reinterpret_cast<const uint4*>(nblk));  // next super-block's header, used four steps from now
+#pragma unroll
+      for (int G = 0; G < 4; G++) {
+        advance_x();  // token tile two steps ahead
         if (!ok) break;
         unsigned char* a_tile = tiles + static_cast<size_t>(s) * kStageBytes;
-        unsigned char* b_tile = a_tile + kABytes;
-        // token tile: row r, 16-byte chunk c -> position c ^ (r & 7)
-#pragma unroll
-        for (int i = 0; i < (TOK * 8 + 255) / 256; i++) {
-          const int idx = p + 256 * i;
-          const int r = idx >> 3, c = idx & 7;
-          if (idx < TOK * 8) *reinterpret_cast<uint4*>(b_tile + r * 128 + ((c ^ (r & 7)) << 4)) = xv[i];
-        }
-        // weight tile: this thread's 32 values are sub-block 2G + half of its row
         {
           const int j = 2 * G + half;
           const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
           const float dscf = n_ok ? d * static_cast<float>(sc) : 0.f, dmf = n_ok ? dmin * static_cast<float>(mn) : 0.f;
           const __nv_bfloat162 dsc = __float2bfloat162_rn(dscf), ndm = __float2bfloat162_rn(-dmf);
-          const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+          const uint32_t w[8] = {qa[G].x, qa[G].y, qa[G].z, qa[G].w, qb[G].x, qb[G].y, qb[G].z, qb[G].w};
+          // refill this piece with the next super-block's (same group): four steps of distance
+          qa[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 16 + 32 * G));
+          qb[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 32 + 32 * G));
 #pragma unroll
           for (int cc = 0; cc < 4; cc++) {  // 8 values = bytes 8cc .. 8cc+7
             const uint32_t w0 = half ? (w[2 * cc] >> 4) & 0x0F0F0F0Fu : w[2 * cc] & 0x0F0F0F0Fu;
@@ -301,6 +349,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
             *reinterpret_cast<uint4*>(a_tile + wrow * 128 + ((c ^ (wrow & 7)) << 4)) = o;
           }
         }
+        asm volatile("cp.async.wait_group 2;" ::: "memory");        // this step's token tile has landed
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
         __syncwarp();
         if (lane == 0) tc_mbar_arrive(full_bar(s));
@@ -310,6 +359,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
         }
       }
     }
+    (void)phase;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
 
   // ---- teardown: every role arrives here, whether it finished or gave up ----
