@@ -22,6 +22,12 @@
 //
 // Every mbarrier wait is bounded; on expiry the CTA sets a shared abort flag, records UB_ERR_TIMEOUT in
 // the device error word, all roles leave their loops, and TMEM is freed before the kernel returns.
+#include <cuda.h>  // CUtensorMap type and enums only; the encoder is resolved at run time
+
+#include <string.h>
+
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -50,9 +56,11 @@ __device__ __forceinline__ bool tc_mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait that also gives up when another role has raised the abort flag.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (tc_mbar_try(bar, parity)) return true;
   for (uint32_t i = 0; i < kTcWaitLimit; i++) {
     if (tc_mbar_try(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
+    if (i > 16) __nanosleep(i > 256 ? 256 : 32);  // back off: spinning warps share issue slots with the producers
+    if ((i & 255) == 255 && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
@@ -112,10 +120,12 @@ struct TcShared {
 };
 
 // TOK: tokens per tile (UMMA N): 64, 128 or 256.  STAGES: ring depth.
-template <int TOK, int STAGES>
+// TMA_X: the token tile arrives through a 2-D tensor-map copy (one instruction per stage, hardware swizzle,
+// rows beyond M filled with zeros); otherwise producers copy it with 16-byte asynchronous copies.
+template <int TOK, int STAGES, bool TMA_X>
 __global__ void __launch_bounds__(kTcThreads, 1)
 qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
-                    int M, int N, int K, int* err_word) {
+                    int M, int N, int K, int* err_word, const __grid_constant__ CUtensorMap x_map) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   __shared__ TcShared sh;
   constexpr uint32_t kABytes = 128 * 128;        // 128 weight rows x 64 bf16
@@ -139,7 +149,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
-      tc_mbar_init(full_bar(s), kTcProducerWarps);
+      tc_mbar_init(full_bar(s), kTcProducerWarps + (TMA_X ? 1 : 0));
       tc_mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; b++) {
@@ -249,25 +259,40 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
     const int total = total_sb * 4;           // K steps
     constexpr int kXChunks = (TOK * 8 + 255) / 256;  // 16-byte token-tile chunks per thread and step
 
-    // token tile of step `it` -> `stage`, asynchronously
-    auto issue_x = [&](int it, int stage) {
-      const int ti = it / ksteps, ks = it - ti * ksteps;
-      const int tile = blockIdx.x + ti * gridDim.x;
-      const int tt = tile % t_tiles;
-      const int m0 = tt * TOK;
-      const uint32_t b_tile = smem_base + stage * kStageBytes + kABytes;
-#pragma unroll
-      for (int i = 0; i < kXChunks; i++) {
-        const int idx = p + 256 * i;  // chunk index over TOK rows x 8 chunks
-        const int r = idx >> 3, c = idx & 7;
-        if (idx < TOK * 8) {
-          const int m = m0 + r;
-          const bool in = m < M;
-          const __nv_bfloat16* src = x + static_cast<size_t>(in ? m : 0) * K + ks * kTcBK + 8 * c;
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(b_tile + r * 128 + ((c ^ (r & 7)) << 4)),
-                       "l"(src), "r"(in ? 16 : 0)
-                       : "memory");
+    // token tile of one step -> `stage`, asynchronously.  A thread always copies the same column chunk
+    // c = p & 7 of rows (p >> 3) + 32 i, so source and destination are one base plus a constant stride.
+    const int xr = p >> 3, xc = p & 7;
+    const uint32_t x_dst_off = kABytes + xr * 128 + ((xc ^ (xr & 7)) << 4);
+    int x_ti = 0, x_ks = 0;                    // (tile index of this CTA, K step) of the next token tile
+    int x_m0 = ((blockIdx.x % t_tiles)) * TOK;
+    auto issue_x = [&](int stage) {
+      if (TMA_X) {
+        if (p == 0) {
+          const uint32_t bar = full_bar(stage);
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kBBytes) : "memory");
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+                  "r"(smem_base + stage * kStageBytes + kABytes),
+              "l"(reinterpret_cast<uint64_t>(&x_map)), "r"(bar), "r"(x_ks * kTcBK), "r"(x_m0)
+              : "memory");
         }
+      } else {
+        const uint32_t dst = smem_base + stage * kStageBytes + x_dst_off;
+        const __nv_bfloat16* src = x + static_cast<size_t>(x_m0 + xr) * K + x_ks * kTcBK + 8 * xc;
+#pragma unroll
+        for (int i = 0; i < kXChunks; i++) {
+          if (xr + 32 * i < TOK) {
+            const bool in = x_m0 + xr + 32 * i < M;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + i * 4096),
+                         "l"(in ? src + static_cast<size_t>(32 * i) * K : x), "r"(in ? 16 : 0)
+                         : "memory");
+          }
+        }
+      }
+      if (++x_ks == ksteps) {
+        x_ks = 0;
+        x_ti++;
+        x_m0 = ((blockIdx.x + x_ti * gridDim.x) % t_tiles) * TOK;
       }
     };
     // address of this thread's row's super-block for flat super-block index q (clamped to valid memory)
@@ -289,7 +314,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
       if (it_x < total && ok) {
         ok = __all_sync(0xFFFFFFFFu, tc_wait(empty_bar(sx), phase_x ^ 1, abort_flag));
         if (ok) {
-          issue_x(it_x, sx);
+          issue_x(sx);
           it_x++;
           if (++sx == STAGES) {
             sx = 0;
@@ -349,7 +374,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
             *reinterpret_cast<uint4*>(a_tile + wrow * 128 + ((c ^ (wrow & 7)) << 4)) = o;
           }
         }
-        asm volatile("cp.async.wait_group 2;" ::: "memory");        // this step's token tile has landed
+        if (!TMA_X) asm volatile("cp.async.wait_group 2;" ::: "memory");  // this step's token tile has landed
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
         __syncwarp();
         if (lane == 0) tc_mbar_arrive(full_bar(s));
@@ -373,22 +398,57 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
   }
 }
 
+// cuTensorMapEncodeTiled, resolved once through the runtime (no link-time dependency on libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
 template <int TOK, int STAGES>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(STAGES) * (128 * 128 + TOK * 128) + 1024;
-  cudaError_t e = cudaFuncSetAttribute(qgemm_q4k_tc_kernel<TOK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
-  if (e != cudaSuccess) {
-    ub::set_cuda_error(e);
-    return ub::fail(UB_ERR_CUDA);
-  }
   const int tiles = ((N + 127) / 128) * ((M + TOK - 1) / TOK);
   const int sms = ub::num_sms();
   const int grid = tiles < sms ? tiles : sms;
-  qgemm_q4k_tc_kernel<TOK, STAGES><<<grid, kTcThreads, smem, s>>>(
-      static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq), M, N, K,
-      ub::device_error_word());
-  return ub::check_launch();
+  // token matrix as a 2-D tensor map: inner dimension K (bf16), outer M; box = 64 x TOK, 128-byte swizzle
+  CUtensorMap map;
+  EncodeTiledFn enc = encode_tiled_fn();
+  bool use_tma = enc != nullptr;
+  if (use_tma) {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(TOK)};
+    const cuuint32_t estr[2] = {1, 1};
+    use_tma = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  if (!use_tma) memset(&map, 0, sizeof(map));
+  auto launch = [&](auto kernel) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) {
+      ub::set_cuda_error(e);
+      return ub::fail(UB_ERR_CUDA);
+    }
+    kernel<<<grid, kTcThreads, smem, s>>>(static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x),
+                                          static_cast<const uint8_t*>(wq), M, N, K, ub::device_error_word(), map);
+    return ub::check_launch();
+  };
+  return use_tma ? launch(qgemm_q4k_tc_kernel<TOK, STAGES, true>) : launch(qgemm_q4k_tc_kernel<TOK, STAGES, false>);
 }
 
 }  // namespace
