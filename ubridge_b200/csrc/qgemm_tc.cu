@@ -27,6 +27,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -337,11 +338,19 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
       advance_x();
       advance_x();
     }
-    for (int q = 0; q < total_sb && ok; q++) {
+    // swizzled store offsets of this thread's four 16-byte chunks inside a weight tile (constant)
+    uint32_t a_off[4];
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) a_off[cc] = wrow * 128 + (((4 * half + cc) ^ (wrow & 7)) << 4);
+
+    // one super-block (four K steps); HALF is a compile-time copy of `half` so that nibble selection and
+    // the scale bytes' positions are immediate operands
+    auto super_block = [&](auto half_c, int q) {
+      constexpr int HALF = decltype(half_c)::value;
       const int ti = q / nsb;
       const int tile = blockIdx.x + ti * gridDim.x;
       const bool n_ok = (tile / t_tiles) * 128 + wrow < N;
-      const float d = half_bits_to_f32(hdr.x), dmin = half_bits_to_f32(hdr.x >> 16);
+      const float d = n_ok ? half_bits_to_f32(hdr.x) : 0.f, dmin = n_ok ? half_bits_to_f32(hdr.x >> 16) : 0.f;
       uint32_t scw[2], mnw[2];
       q4k_unpack_scales(hdr.y, hdr.z, hdr.w, scw[0], scw[1], mnw[0], mnw[1]);
       const bool more = q + 1 < total_sb;
@@ -352,27 +361,24 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
         advance_x();  // token tile two steps ahead
         if (!ok) break;
         unsigned char* a_tile = tiles + static_cast<size_t>(s) * kStageBytes;
-        {
-          const int j = 2 * G + half;
-          const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
-          const float dscf = n_ok ? d * static_cast<float>(sc) : 0.f, dmf = n_ok ? dmin * static_cast<float>(mn) : 0.f;
-          const __nv_bfloat162 dsc = __float2bfloat162_rn(dscf), ndm = __float2bfloat162_rn(-dmf);
-          const uint32_t w[8] = {qa[G].x, qa[G].y, qa[G].z, qa[G].w, qb[G].x, qb[G].y, qb[G].z, qb[G].w};
-          // refill this piece with the next super-block's (same group): four steps of distance
-          qa[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 16 + 32 * G));
-          qb[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 32 + 32 * G));
+        const int j = 2 * G + HALF;
+        const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
+        const __nv_bfloat162 dsc = __float2bfloat162_rn(d * static_cast<float>(sc));
+        const __nv_bfloat162 ndm = __float2bfloat162_rn(-dmin * static_cast<float>(mn));
+        const uint32_t w[8] = {qa[G].x, qa[G].y, qa[G].z, qa[G].w, qb[G].x, qb[G].y, qb[G].z, qb[G].w};
+        // refill this piece with the next super-block's (same group): four steps of distance
+        qa[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 16 + 32 * G));
+        qb[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 32 + 32 * G));
 #pragma unroll
-          for (int cc = 0; cc < 4; cc++) {  // 8 values = bytes 8cc .. 8cc+7
-            const uint32_t w0 = half ? (w[2 * cc] >> 4) & 0x0F0F0F0Fu : w[2 * cc] & 0x0F0F0F0Fu;
-            const uint32_t w1 = half ? (w[2 * cc + 1] >> 4) & 0x0F0F0F0Fu : w[2 * cc + 1] & 0x0F0F0F0Fu;
-            uint4 o;
-            o.x = deq_pair<0x4140>(w0, dsc, ndm);
-            o.y = deq_pair<0x4342>(w0, dsc, ndm);
-            o.z = deq_pair<0x4140>(w1, dsc, ndm);
-            o.w = deq_pair<0x4342>(w1, dsc, ndm);
-            const int c = 4 * half + cc;
-            *reinterpret_cast<uint4*>(a_tile + wrow * 128 + ((c ^ (wrow & 7)) << 4)) = o;
-          }
+        for (int cc = 0; cc < 4; cc++) {  // 8 values = bytes 8cc .. 8cc+7
+          const uint32_t w0 = HALF ? (w[2 * cc] >> 4) & 0x0F0F0F0Fu : w[2 * cc] & 0x0F0F0F0Fu;
+          const uint32_t w1 = HALF ? (w[2 * cc + 1] >> 4) & 0x0F0F0F0Fu : w[2 * cc + 1] & 0x0F0F0F0Fu;
+          uint4 o;
+          o.x = deq_pair<0x4140>(w0, dsc, ndm);
+          o.y = deq_pair<0x4342>(w0, dsc, ndm);
+          o.z = deq_pair<0x4140>(w1, dsc, ndm);
+          o.w = deq_pair<0x4342>(w1, dsc, ndm);
+          *reinterpret_cast<uint4*>(a_tile + a_off[cc]) = o;
         }
         if (!TMA_X) asm volatile("cp.async.wait_group 2;" ::: "memory");  // this step's token tile has landed
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
@@ -383,6 +389,11 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
           phase ^= 1;
         }
       }
+    };
+    if (half) {
+      for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 1>{}, q);
+    } else {
+      for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 0>{}, q);
     }
     (void)phase;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
