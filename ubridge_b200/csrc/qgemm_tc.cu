@@ -8,17 +8,21 @@
 // and then calls the matrix engine (kernels/matmul.cpp:1039-1109).
 //
 // Tile and roles.  One persistent CTA per SM walks over (128 weight rows) x (TOK tokens) output tiles.
-// The weight tile is the UMMA "A" operand (M = 128), the token tile the "B" operand (N = TOK <= 256), both
-// K-major bf16 in the 128-byte-swizzled canonical layout; the accumulator D[128 lanes x TOK columns] lives
-// in tensor memory, double buffered (2 x 256 columns) so the epilogue of one tile overlaps the main loop
-// of the next.  K is consumed 64 values per stage (one 64-value Q4_K group), four UMMA K=16 steps each.
+// The weight tile is the UMMA "A" operand (M = 128) and is read by the MMA from TENSOR MEMORY: producers
+// dequantise straight from registers into TMEM with tcgen05.st, so weights never touch shared memory.
+// The token tile is the "B" operand (N = TOK <= 256, trimmed to the valid tokens of a ragged last tile),
+// K-major bf16 in the 128-byte-swizzled canonical layout, written to shared memory by 2-D tensor-map
+// copies.  The accumulator D[128 lanes x TOK columns] lives in tensor memory next to the weight stages
+// (columns 0..255 accumulators, 256.. weight stages of 32 columns each).  K is consumed 64 values per
+// stage (one 64-value Q4_K group), four UMMA K=16 steps each.
 //
 //   warp 0        allocates TMEM, then one elected lane issues tcgen05.mma and tcgen05.commit
-//   warps 1-4     epilogue: tcgen05.ld -> bf16 -> global (lane = weight row, columns = tokens)
-//   warps 5-12    producers: copy the token tile (plain 16-byte loads; rows may later be gathered) and
-//                 dequantise the weight tile straight into the swizzled layout: nibbles become bf16
-//                 (128 + q) with one byte permute per pair, minus 128 (exact), times d*sc minus dmin*m
-//                 with packed bf16 FMAs; then fence.proxy.async + mbarrier arrive
+//   warps 1-4     epilogue: tcgen05.ld -> bf16 -> staging tile in shared memory (accumulator released
+//                 here) -> 16-byte coalesced stores to y, overlapping the next tile's main loop
+//   warps 5-12    weight producers: nibbles become bf16 (128 + q) with one byte permute per pair, minus 128
+//                 (exact), times d*sc minus dmin*m with packed bf16 FMAs; tcgen05.st, tcgen05.wait::st,
+//                 mbarrier arrive.  Packed weights are fetched four K steps ahead into registers.
+//   warp 13       one lane streams token tiles with cp.async.bulk.tensor as far ahead as the ring allows
 //
 // Every mbarrier wait is bounded; on expiry the CTA sets a shared abort flag, records UB_ERR_TIMEOUT in
 // the device error word, all roles leave their loops, and TMEM is freed before the kernel returns.
@@ -35,7 +39,7 @@ namespace {
 
 using namespace ub;
 
-constexpr int kTcThreads = 13 * 32;
+constexpr int kTcThreads = 14 * 32;
 constexpr int kTcProducerWarps = 8;
 constexpr int kTcBK = 64;
 constexpr uint32_t kTcWaitLimit = 2000000;
@@ -86,6 +90,23 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// same, with the A operand read from tensor memory (128 lanes x 8 columns of packed bf16 pairs per K = 16)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+      "%15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -114,24 +135,28 @@ __device__ __forceinline__ uint32_t deq_pair(uint32_t w4, __nv_bfloat162 dsc, __
   return bf162_bits(__hfma2(q, dsc, ndm));
 }
 
+constexpr int kTcMaxStages = 8;
+
 struct TcShared {
-  unsigned long long full[4], empty[4], tmem_full[2], tmem_empty[2];
+  unsigned long long full[kTcMaxStages], empty[kTcMaxStages], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-// TOK: tokens per tile (UMMA N): 64, 128 or 256.  STAGES: ring depth.
-// TMA_X: the token tile arrives through a 2-D tensor-map copy (one instruction per stage, hardware swizzle,
-// rows beyond M filled with zeros); otherwise producers copy it with 16-byte asynchronous copies.
-template <int TOK, int STAGES, bool TMA_X>
+// TOK: tokens per tile (UMMA N): 64, 128 or 256.  STAGES: ring depth (token tiles in shared memory and
+// weight stages in tensor memory advance together).
+template <int TOK, int STAGES>
 __global__ void __launch_bounds__(kTcThreads, 1)
-qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
-                    int M, int N, int K, int* err_word, const __grid_constant__ CUtensorMap x_map) {
+qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ wq, int M, int N, int K, int* err_word,
+                    const __grid_constant__ CUtensorMap x_map) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   __shared__ TcShared sh;
-  constexpr uint32_t kABytes = 128 * 128;        // 128 weight rows x 64 bf16
-  constexpr uint32_t kBBytes = TOK * 128;        // TOK token rows x 64 bf16
-  constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static_assert(STAGES <= kTcMaxStages, "barrier arrays");
+  constexpr uint32_t kBBytes = TOK * 128;              // TOK token rows x 64 bf16
+  constexpr uint32_t kStagingOff = STAGES * kBBytes;   // [TOK tokens][128 weight rows] bf16 output tile
+  constexpr int kAccBufs = TOK > 128 ? 1 : 2;          // accumulator buffers in TMEM columns 0..255
+  constexpr uint32_t kAccStride = 128;
+  constexpr uint32_t kATmemCol = 256;                  // first TMEM column of the weight stages (32 each)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this round-up
   const uint32_t smem_raw = static_cast<uint32_t>(__cvta_generic_to_shared(tc_smem));
@@ -139,9 +164,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
   unsigned char* const tiles = tc_smem + (smem_base - smem_raw);
   const uint32_t bars = static_cast<uint32_t>(__cvta_generic_to_shared(&sh));
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 32u + 8u * s; };
-  auto tfull_bar = [&](int b) { return bars + 64u + 8u * b; };
-  auto tempty_bar = [&](int b) { return bars + 80u + 8u * b; };
+  auto empty_bar = [&](int s) { return bars + 8u * kTcMaxStages + 8u * s; };
+  auto tfull_bar = [&](int b) { return bars + 16u * kTcMaxStages + 8u * b; };
+  auto tempty_bar = [&](int b) { return bars + 16u * kTcMaxStages + 16u + 8u * b; };
   volatile int* abort_flag = &sh.abort_flag;
 
   const int w_tiles = (N + 127) / 128, t_tiles = (M + TOK - 1) / TOK;
@@ -150,7 +175,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
-      tc_mbar_init(full_bar(s), kTcProducerWarps + (TMA_X ? 1 : 0));
+      tc_mbar_init(full_bar(s), kTcProducerWarps + 1);  // eight weight warps + the token copy's expect_tx
       tc_mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; b++) {
@@ -174,26 +199,30 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
   if (warp == 0) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // instruction descriptor: D = f32, A = B = bf16, both K-major, N = TOK, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TOK >> 3) << 17) | (8u << 24);
       int s = 0;
       uint32_t phase = 0, acc_phase = 0;
       int buf = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int tt = tile % t_tiles;
+        // UMMA N = the tile's valid tokens rounded up to 16 (a ragged last tile costs less)
+        const int valid = M - tt * TOK;
+        const uint32_t n_mma = valid >= TOK ? TOK : static_cast<uint32_t>((valid + 15) & ~15);
+        // instruction descriptor: D = f32, A = B = bf16, both K-major, N = n_mma, M = 128
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((n_mma >> 3) << 17) | (8u << 24);
         ok = tc_wait(tempty_bar(buf), acc_phase ^ 1, abort_flag);  // epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * 256u;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * kAccStride;
         for (int ks = 0; ks < ksteps; ks++) {
           ok = tc_wait(full_bar(s), phase, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_base + s * kStageBytes, b_addr = a_addr + kABytes;
-          const uint64_t a_desc = make_sw128_desc(a_addr), b_desc = make_sw128_desc(b_addr);
+          const uint64_t b_desc = make_sw128_desc(smem_base + s * kBBytes);
+          const uint32_t a_tmem = tmem_base + kATmemCol + 32u * s;
 #pragma unroll
-          for (int j = 0; j < 4; j++)  // K = 16 per instruction: 32 bytes further inside the 128-byte swizzle row
-            umma_bf16(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
+          for (int j = 0; j < 4; j++)  // K = 16 per instruction: 8 TMEM columns of A, 32 bytes of a B row
+            umma_bf16_ts(d_tmem, a_tmem + 8u * j, b_desc + 2 * j, idesc, (ks > 0 || j > 0) ? 1u : 0u);
           umma_commit(empty_bar(s));  // stage is free once these MMAs have read it
           if (++s == STAGES) {
             s = 0;
@@ -202,7 +231,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
         }
         if (!ok) break;
         umma_commit(tfull_bar(buf));  // accumulator complete
-        if (++buf == 2) {
+        if (++buf == kAccBufs) {
           buf = 0;
           acc_phase ^= 1;
         }
@@ -211,91 +240,80 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
   } else if (warp <= 4) {
     // ------------------------------------------------------------ epilogue (TMEM lanes 32*(warp%4) ..)
     const int lane_base = 32 * (warp & 3);
+    const int ew = warp - 1;  // 0..3: which quarter of the tile's tokens this warp writes out
+    unsigned char* const staging = tiles + kStagingOff;
+    const bool vec_ok = (N % 8) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
     uint32_t acc_phase = 0;
     int buf = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       const int wt = tile / t_tiles, tt = tile - wt * t_tiles;
-      ok = __all_sync(0xFFFFFFFFu, tc_wait(tfull_bar(buf), acc_phase, abort_flag));  // warp-uniform
+      const int n0 = wt * 128, m0 = tt * TOK;
+      const int valid = min(TOK, M - m0);
+      {
+        // all four epilogue warps take the same decision, so nobody is left alone at the named barrier
+        const uint32_t mine = tc_wait(tfull_bar(buf), acc_phase, abort_flag) ? 1u : 0u;
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(all_ok)
+            : "r"(mine)
+            : "memory");
+        ok = all_ok != 0;
+      }
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int n = wt * 128 + lane_base + lane;  // weight row = output column
-      const int m0 = tt * TOK;
+      // accumulator -> bf16 -> staging[token][weight row]; a warp's 32 lanes write 64 contiguous bytes
+      __nv_bfloat16* const st_col = reinterpret_cast<__nv_bfloat16*>(staging) + lane_base + lane;
 #pragma unroll 1
-      for (int c = 0; c < TOK; c += 32) {
+      for (int c = 0; c < valid; c += 32) {
         uint32_t v[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + static_cast<uint32_t>(buf * 256 + c), v);
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + static_cast<uint32_t>(buf) * kAccStride + c, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (n < N) {
 #pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const int m = m0 + c + j;
-            if (m < M) y[static_cast<size_t>(m) * N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
-          }
-        }
+        for (int j = 0; j < 32; j++) st_col[(c + j) * 128] = __float2bfloat16_rn(__uint_as_float(v[j]));
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) tc_mbar_arrive(tempty_bar(buf));
-      if (++buf == 2) {
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: staging complete, TMEM read
+      if (lane == 0) tc_mbar_arrive(tempty_bar(buf));  // the next tile's MMAs may overwrite the accumulator
+      if (++buf == kAccBufs) {
         buf = 0;
         acc_phase ^= 1;
       }
+      // staging -> y: token rows of 128 weight rows = 256 contiguous bytes, two tokens per warp instruction
+      if (vec_ok) {
+        const int ch = lane & 15;
+        const bool n_in = n0 + 8 * ch < N;
+        for (int t = 2 * ew + (lane >> 4); t < valid; t += 8) {
+          const uint4 val = *reinterpret_cast<const uint4*>(staging + t * 256 + ch * 16);
+          if (n_in) *reinterpret_cast<uint4*>(y + static_cast<size_t>(m0 + t) * N + n0 + 8 * ch) = val;
+        }
+      } else {
+        for (int t = ew; t < valid; t += 4) {
+#pragma unroll
+          for (int r = lane; r < 128; r += 32)
+            if (n0 + r < N)
+              y[static_cast<size_t>(m0 + t) * N + n0 + r] = reinterpret_cast<const __nv_bfloat16*>(staging)[t * 128 + r];
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // staging may be overwritten
     }
-  } else {
-    // ------------------------------------------------------------ producers (256 threads)
+  } else if (warp <= 4 + kTcProducerWarps) {
+    // ------------------------------------------------------------ weight producers (256 threads)
     // One flat loop over (tile, super-block), four K steps (the super-block's four 64-value groups) per
-    // iteration.  Latency is hidden by distance, not by occupancy:
-    //  * token tiles travel as 16-byte asynchronous copies straight to their swizzled position, issued
-    //    TWO steps ahead of the step being dequantised;
-    //  * a thread keeps the 4 x 32 bytes of nibbles of its row's current super-block in registers and
-    //    refills each 32-byte piece with the next super-block's right after using it (four steps ahead);
-    //    the 16-byte header is fetched one super-block ahead.
-    const int p = threadIdx.x - 5 * 32;        // 0..255
-    const int wrow = p & 127, half = p >> 7;   // weight row inside the tile; 0 = low nibbles, 1 = high nibbles
+    // iteration.  A thread owns one weight row (= its TMEM lane) and one nibble half, keeps the 4 x 32
+    // bytes of nibbles of the row's current super-block in registers and refills each 32-byte piece with
+    // the next super-block's right after using it (four steps ahead); the 16-byte header is fetched one
+    // super-block ahead.
+    const int p = threadIdx.x - 5 * 32;  // 0..255
+    // weight row inside the tile = the TMEM lane this warp may access (32 * (warp % 4) + lane);
+    // half: 0 = low nibbles (even sub-blocks), 1 = high nibbles
+    const int wrow = 32 * (warp & 3) + lane, half = p >> 7;
     const int nsb = K >> 8;
     const size_t row_bytes = static_cast<size_t>(nsb) * UB_Q4K_BYTES;
     const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const int total_sb = my_tiles * nsb;      // super-block iterations
-    const int total = total_sb * 4;           // K steps
-    constexpr int kXChunks = (TOK * 8 + 255) / 256;  // 16-byte token-tile chunks per thread and step
-
-    // token tile of one step -> `stage`, asynchronously.  A thread always copies the same column chunk
-    // c = p & 7 of rows (p >> 3) + 32 i, so source and destination are one base plus a constant stride.
-    const int xr = p >> 3, xc = p & 7;
-    const uint32_t x_dst_off = kABytes + xr * 128 + ((xc ^ (xr & 7)) << 4);
-    int x_ti = 0, x_ks = 0;                    // (tile index of this CTA, K step) of the next token tile
-    int x_m0 = ((blockIdx.x % t_tiles)) * TOK;
-    auto issue_x = [&](int stage) {
-      if (TMA_X) {
-        if (p == 0) {
-          const uint32_t bar = full_bar(stage);
-          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kBBytes) : "memory");
-          asm volatile(
-              "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
-                  "r"(smem_base + stage * kStageBytes + kABytes),
-              "l"(reinterpret_cast<uint64_t>(&x_map)), "r"(bar), "r"(x_ks * kTcBK), "r"(x_m0)
-              : "memory");
-        }
-      } else {
-        const uint32_t dst = smem_base + stage * kStageBytes + x_dst_off;
-        const __nv_bfloat16* src = x + static_cast<size_t>(x_m0 + xr) * K + x_ks * kTcBK + 8 * xc;
-#pragma unroll
-        for (int i = 0; i < kXChunks; i++) {
-          if (xr + 32 * i < TOK) {
-            const bool in = x_m0 + xr + 32 * i < M;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + i * 4096),
-                         "l"(in ? src + static_cast<size_t>(32 * i) * K : x), "r"(in ? 16 : 0)
-                         : "memory");
-          }
-        }
-      }
-      if (++x_ks == ksteps) {
-        x_ks = 0;
-        x_ti++;
-        x_m0 = ((blockIdx.x + x_ti * gridDim.x) % t_tiles) * TOK;
-      }
-    };
+    const int total_sb = my_tiles * nsb;  // super-block iterations
     // address of this thread's row's super-block for flat super-block index q (clamped to valid memory)
     auto sb_ptr = [&](int q) {
       const int ti = q / nsb, sb = q - ti * nsb;
@@ -304,28 +322,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
       return wq + static_cast<size_t>(n < N ? n : 0) * row_bytes + static_cast<size_t>(sb) * UB_Q4K_BYTES;
     };
 
-    int s = 0;             // stage of the step being dequantised
+    int s = 0;  // stage of the step being dequantised
     uint32_t phase = 0;
-    int sx = 0;            // stage the next token tile goes to (runs two steps ahead)
-    uint32_t phase_x = 0;
-    int it_x = 0;          // next step whose token tile has not been issued yet
     bool ok = true;
-    auto advance_x = [&]() {
-      // issue the token tile of step it_x (if any) once its stage is free; always commits one group
-      if (it_x < total && ok) {
-        ok = __all_sync(0xFFFFFFFFu, tc_wait(empty_bar(sx), phase_x ^ 1, abort_flag));
-        if (ok) {
-          issue_x(sx);
-          it_x++;
-          if (++sx == STAGES) {
-            sx = 0;
-            phase_x ^= 1;
-          }
-        }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-
     uint4 hdr = make_uint4(0, 0, 0, 0), qa[4], qb[4];
     if (total_sb > 0) {
       const uint8_t* blk = sb_ptr(0);
@@ -335,13 +334,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
         qa[G] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * G));
         qb[G] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * G));
       }
-      advance_x();
-      advance_x();
     }
-    // swizzled store offsets of this thread's four 16-byte chunks inside a weight tile (constant)
-    uint32_t a_off[4];
-#pragma unroll
-    for (int cc = 0; cc < 4; cc++) a_off[cc] = wrow * 128 + (((4 * half + cc) ^ (wrow & 7)) << 4);
+    const uint32_t a_lane = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kATmemCol;
 
     // one super-block (four K steps); HALF is a compile-time copy of `half` so that nibble selection and
     // the scale bytes' positions are immediate operands
@@ -349,7 +343,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
       constexpr int HALF = decltype(half_c)::value;
       const int ti = q / nsb;
       const int tile = blockIdx.x + ti * gridDim.x;
-      const bool n_ok = (tile / t_tiles) * 128 + wrow < N;
+      const bool n_ok = (tile / t_tiles) * 128 + wrow < N;  // rows past N produce zeros
       const float d = n_ok ? half_bits_to_f32(hdr.x) : 0.f, dmin = n_ok ? half_bits_to_f32(hdr.x >> 16) : 0.f;
       uint32_t scw[2], mnw[2];
       q4k_unpack_scales(hdr.y, hdr.z, hdr.w, scw[0], scw[1], mnw[0], mnw[1]);
@@ -358,9 +352,6 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
       hdr = __ldg(reinterpret_cast<const uint4*>(nblk));  // next super-block's header, used four steps from now
 #pragma unroll
       for (int G = 0; G < 4; G++) {
-        advance_x();  // token tile two steps ahead
-        if (!ok) break;
-        unsigned char* a_tile = tiles + static_cast<size_t>(s) * kStageBytes;
         const int j = 2 * G + HALF;
         const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
         const __nv_bfloat162 dsc = __float2bfloat162_rn(d * static_cast<float>(sc));
@@ -369,19 +360,23 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
         // refill this piece with the next super-block's (same group): four steps of distance
         qa[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 16 + 32 * G));
         qb[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 32 + 32 * G));
+        uint32_t ot[16];  // this thread's 32 values of the step = 16 TMEM columns of packed pairs
 #pragma unroll
         for (int cc = 0; cc < 4; cc++) {  // 8 values = bytes 8cc .. 8cc+7
           const uint32_t w0 = HALF ? (w[2 * cc] >> 4) & 0x0F0F0F0Fu : w[2 * cc] & 0x0F0F0F0Fu;
           const uint32_t w1 = HALF ? (w[2 * cc + 1] >> 4) & 0x0F0F0F0Fu : w[2 * cc + 1] & 0x0F0F0F0Fu;
-          uint4 o;
-          o.x = deq_pair<0x4140>(w0, dsc, ndm);
-          o.y = deq_pair<0x4342>(w0, dsc, ndm);
-          o.z = deq_pair<0x4140>(w1, dsc, ndm);
-          o.w = deq_pair<0x4342>(w1, dsc, ndm);
-          *reinterpret_cast<uint4*>(a_tile + a_off[cc]) = o;
+          ot[4 * cc] = deq_pair<0x4140>(w0, dsc, ndm);
+          ot[4 * cc + 1] = deq_pair<0x4342>(w0, dsc, ndm);
+          ot[4 * cc + 2] = deq_pair<0x4140>(w1, dsc, ndm);
+          ot[4 * cc + 3] = deq_pair<0x4342>(w1, dsc, ndm);
         }
-        if (!TMA_X) asm volatile("cp.async.wait_group 2;" ::: "memory");  // this step's token tile has landed
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+        // the MMAs that read this weight stage six steps ago must have completed
+        ok = __all_sync(0xFFFFFFFFu, tc_wait(empty_bar(s), phase ^ 1, abort_flag));
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem_st16(a_lane + 32u * s + 16u * HALF, ot);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) tc_mbar_arrive(full_bar(s));
         if (++s == STAGES) {
@@ -395,8 +390,32 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restri
     } else {
       for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 0>{}, q);
     }
-    (void)phase;
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  } else {
+    // ------------------------------------------------------------ token-tile copies (one lane)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % t_tiles) * TOK;
+        for (int ks = 0; ks < ksteps; ks++) {
+          ok = tc_wait(empty_bar(s), phase ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t bar = full_bar(s);
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kBBytes) : "memory");
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+                  "r"(smem_base + s * kBBytes),
+              "l"(reinterpret_cast<uint64_t>(&x_map)), "r"(bar), "r"(ks * kTcBK), "r"(m0)
+              : "memory");
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
   }
 
   // ---- teardown: every role arrives here, whether it finished or gave up ----
@@ -431,35 +450,32 @@ EncodeTiledFn encode_tiled_fn() {
 
 template <int TOK, int STAGES>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(STAGES) * (128 * 128 + TOK * 128) + 1024;
+  const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(TOK) * 256 + 1024;
   const int tiles = ((N + 127) / 128) * ((M + TOK - 1) / TOK);
   const int sms = ub::num_sms();
   const int grid = tiles < sms ? tiles : sms;
-  // token matrix as a 2-D tensor map: inner dimension K (bf16), outer M; box = 64 x TOK, 128-byte swizzle
+  // token matrix as a 2-D tensor map: inner dimension K (bf16), outer M; box = 64 x TOK, 128-byte swizzle;
+  // rows beyond M read as zeros
   CUtensorMap map;
   EncodeTiledFn enc = encode_tiled_fn();
-  bool use_tma = enc != nullptr;
-  if (use_tma) {
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
-    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(TOK)};
-    const cuuint32_t estr[2] = {1, 1};
-    use_tma = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (!enc) return ub::fail(UB_ERR_UNSUPPORTED);
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(TOK)};
+  const cuuint32_t estr[2] = {1, 1};
+  if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return ub::fail(UB_ERR_UNSUPPORTED);
+  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
   }
-  if (!use_tma) memset(&map, 0, sizeof(map));
-  auto launch = [&](auto kernel) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) {
-      ub::set_cuda_error(e);
-      return ub::fail(UB_ERR_CUDA);
-    }
-    kernel<<<grid, kTcThreads, smem, s>>>(static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x),
-                                          static_cast<const uint8_t*>(wq), M, N, K, ub::device_error_word(), map);
-    return ub::check_launch();
-  };
-  return use_tma ? launch(qgemm_q4k_tc_kernel<TOK, STAGES, true>) : launch(qgemm_q4k_tc_kernel<TOK, STAGES, false>);
+  kernel<<<grid, kTcThreads, smem, s>>>(static_cast<__nv_bfloat16*>(y), static_cast<const uint8_t*>(wq), M, N, K,
+                                        ub::device_error_word(), map);
+  return ub::check_launch();
 }
 
 }  // namespace
@@ -467,10 +483,11 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaS
 namespace ub {
 
 // y (bf16) [M,N] = x (bf16) [M,K] . dequant(Wq)^T on tcgen05; K % 256 == 0, pointers 16-byte aligned.
+// Returns UB_ERR_UNSUPPORTED when the driver offers no tensor-map encoder (the caller falls back).
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
-  if (M <= 64) return launch_tc<64, 4>(y, x, wq, M, N, K, s);
-  if (M <= 128) return launch_tc<128, 4>(y, x, wq, M, N, K, s);
-  return launch_tc<256, 4>(y, x, wq, M, N, K, s);
+  if (M <= 64) return launch_tc<64, 6>(y, x, wq, M, N, K, s);
+  if (M <= 128) return launch_tc<128, 6>(y, x, wq, M, N, K, s);
+  return launch_tc<256, 5>(y, x, wq, M, N, K, s);
 }
 
 }  // namespace ub

@@ -80,6 +80,8 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
   }
   if (conv_out) yout = ws + align_up(static_cast<size_t>(M) * K * 2, 256);
   int st = ub::q4k_gemm_tc(yout, xin, wq, M, N, K, s);
+  // no tensor-map encoder in this driver: the mma.sync kernel computes the same product
+  if (st == UB_ERR_UNSUPPORTED) st = ub::q4k_gemm_mma(yout, xin, wq, M, N, K, s);
   if (st != UB_OK) return st;
   if (conv_out) {
     const size_t n = static_cast<size_t>(M) * N;
