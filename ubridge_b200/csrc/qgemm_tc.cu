@@ -136,9 +136,12 @@ __device__ __forceinline__ uint32_t deq_pair(uint32_t w4, __nv_bfloat162 dsc, __
 }
 
 constexpr int kTcMaxStages = 8;
+constexpr int kTcWStages = 3;                        // ring of packed weight tiles (one super-block column each)
+constexpr uint32_t kTcWBytes = 128 * UB_Q4K_BYTES;   // 128 rows x 144 bytes
 
 struct TcShared {
   unsigned long long full[kTcMaxStages], empty[kTcMaxStages], tmem_full[2], tmem_empty[2];
+  unsigned long long wfull[kTcWStages], wempty[kTcWStages];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -148,12 +151,14 @@ struct TcShared {
 template <int TOK, int STAGES>
 __global__ void __launch_bounds__(kTcThreads, 1)
 qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ wq, int M, int N, int K, int* err_word,
-                    const __grid_constant__ CUtensorMap x_map) {
+                    const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   __shared__ TcShared sh;
   static_assert(STAGES <= kTcMaxStages, "barrier arrays");
   constexpr uint32_t kBBytes = TOK * 128;              // TOK token rows x 64 bf16
-  constexpr uint32_t kStagingOff = STAGES * kBBytes;   // [TOK tokens][128 weight rows] bf16 output tile
+  constexpr int kStageTok = TOK < 128 ? TOK : 128;     // tokens the output staging tile holds
+  constexpr uint32_t kStagingOff = STAGES * kBBytes;   // [kStageTok tokens][128 weight rows] bf16
+  constexpr uint32_t kWOff = kStagingOff + kStageTok * 256;  // packed weight ring: [128 rows][144 bytes] each
   constexpr int kAccBufs = TOK > 128 ? 1 : 2;          // accumulator buffers in TMEM columns 0..255
   constexpr uint32_t kAccStride = 128;
   constexpr uint32_t kATmemCol = 256;                  // first TMEM column of the weight stages (32 each)
@@ -167,6 +172,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
   auto empty_bar = [&](int s) { return bars + 8u * kTcMaxStages + 8u * s; };
   auto tfull_bar = [&](int b) { return bars + 16u * kTcMaxStages + 8u * b; };
   auto tempty_bar = [&](int b) { return bars + 16u * kTcMaxStages + 16u + 8u * b; };
+  auto wfull_bar = [&](int b) { return bars + 16u * kTcMaxStages + 32u + 8u * b; };
+  auto wempty_bar = [&](int b) { return bars + 16u * kTcMaxStages + 32u + 8u * kTcWStages + 8u * b; };
   volatile int* abort_flag = &sh.abort_flag;
 
   const int w_tiles = (N + 127) / 128, t_tiles = (M + TOK - 1) / TOK;
@@ -181,6 +188,10 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
     for (int b = 0; b < 2; b++) {
       tc_mbar_init(tfull_bar(b), 1);
       tc_mbar_init(tempty_bar(b), 4);
+    }
+    for (int b = 0; b < kTcWStages; b++) {
+      tc_mbar_init(wfull_bar(b), 1);
+      tc_mbar_init(wempty_bar(b), kTcProducerWarps);
     }
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -264,102 +275,91 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
       }
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // accumulator -> bf16 -> staging[token][weight row]; a warp's 32 lanes write 64 contiguous bytes
+      // accumulator -> bf16 -> staging[token][weight row] -> y, kStageTok tokens at a time.  A warp's 32
+      // lanes write 64 contiguous bytes of a staging row; token rows leave as 256 contiguous bytes.
       __nv_bfloat16* const st_col = reinterpret_cast<__nv_bfloat16*>(staging) + lane_base + lane;
 #pragma unroll 1
-      for (int c = 0; c < valid; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + static_cast<uint32_t>(buf) * kAccStride + c, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int c0 = 0; c0 < valid; c0 += kStageTok) {
+        const int part = min(kStageTok, valid - c0);
+#pragma unroll 1
+        for (int c = 0; c < part; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + static_cast<uint32_t>(buf) * kAccStride +
+                        c0 + c, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 32; j++) st_col[(c + j) * 128] = __float2bfloat16_rn(__uint_as_float(v[j]));
+          for (int j = 0; j < 32; j++) st_col[(c + j) * 128] = __float2bfloat16_rn(__uint_as_float(v[j]));
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: staging complete
+        // after the last part the next tile's MMAs may overwrite the accumulator
+        if (c0 + kStageTok >= valid && lane == 0) tc_mbar_arrive(tempty_bar(buf));
+        if (vec_ok) {
+          const int ch = lane & 15;
+          const bool n_in = n0 + 8 * ch < N;
+          for (int t = 2 * ew + (lane >> 4); t < part; t += 8) {
+            const uint4 val = *reinterpret_cast<const uint4*>(staging + t * 256 + ch * 16);
+            if (n_in) *reinterpret_cast<uint4*>(y + static_cast<size_t>(m0 + c0 + t) * N + n0 + 8 * ch) = val;
+          }
+        } else {
+          for (int t = ew; t < part; t += 4) {
+#pragma unroll
+            for (int r = lane; r < 128; r += 32)
+              if (n0 + r < N)
+                y[static_cast<size_t>(m0 + c0 + t) * N + n0 + r] =
+                    reinterpret_cast<const __nv_bfloat16*>(staging)[t * 128 + r];
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // staging may be overwritten
       }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: staging complete, TMEM read
-      if (lane == 0) tc_mbar_arrive(tempty_bar(buf));  // the next tile's MMAs may overwrite the accumulator
       if (++buf == kAccBufs) {
         buf = 0;
         acc_phase ^= 1;
       }
-      // staging -> y: token rows of 128 weight rows = 256 contiguous bytes, two tokens per warp instruction
-      if (vec_ok) {
-        const int ch = lane & 15;
-        const bool n_in = n0 + 8 * ch < N;
-        for (int t = 2 * ew + (lane >> 4); t < valid; t += 8) {
-          const uint4 val = *reinterpret_cast<const uint4*>(staging + t * 256 + ch * 16);
-          if (n_in) *reinterpret_cast<uint4*>(y + static_cast<size_t>(m0 + t) * N + n0 + 8 * ch) = val;
-        }
-      } else {
-        for (int t = ew; t < valid; t += 4) {
-#pragma unroll
-          for (int r = lane; r < 128; r += 32)
-            if (n0 + r < N)
-              y[static_cast<size_t>(m0 + t) * N + n0 + r] = reinterpret_cast<const __nv_bfloat16*>(staging)[t * 128 + r];
-        }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // staging may be overwritten
     }
   } else if (warp <= 4 + kTcProducerWarps) {
     // ------------------------------------------------------------ weight producers (256 threads)
     // One flat loop over (tile, super-block), four K steps (the super-block's four 64-value groups) per
-    // iteration.  A thread owns one weight row (= its TMEM lane) and one nibble half, keeps the 4 x 32
-    // bytes of nibbles of the row's current super-block in registers and refills each 32-byte piece with
-    // the next super-block's right after using it (four steps ahead); the 16-byte header is fetched one
-    // super-block ahead.
+    // iteration.  Packed weights arrive in shared memory as [128 rows][144 bytes] per super-block; a
+    // thread owns one weight row (= its TMEM lane) and one nibble half and reads its row's header and
+    // 32-byte pieces from there (rows are 144 bytes apart, so a quarter-warp's 16-byte reads hit all
+    // 32 banks once).
     const int p = threadIdx.x - 5 * 32;  // 0..255
     // weight row inside the tile = the TMEM lane this warp may access (32 * (warp % 4) + lane);
     // half: 0 = low nibbles (even sub-blocks), 1 = high nibbles
     const int wrow = 32 * (warp & 3) + lane, half = p >> 7;
     const int nsb = K >> 8;
-    const size_t row_bytes = static_cast<size_t>(nsb) * UB_Q4K_BYTES;
     const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const int total_sb = my_tiles * nsb;  // super-block iterations
-    // address of this thread's row's super-block for flat super-block index q (clamped to valid memory)
-    auto sb_ptr = [&](int q) {
-      const int ti = q / nsb, sb = q - ti * nsb;
-      const int tile = blockIdx.x + ti * gridDim.x;
-      const int n = (tile / t_tiles) * 128 + wrow;
-      return wq + static_cast<size_t>(n < N ? n : 0) * row_bytes + static_cast<size_t>(sb) * UB_Q4K_BYTES;
-    };
+    const unsigned char* const w_ring = tiles + kWOff + wrow * UB_Q4K_BYTES;
+    const uint32_t a_lane = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kATmemCol;
 
     int s = 0;  // stage of the step being dequantised
     uint32_t phase = 0;
+    int ws = 0;  // packed-weight ring slot
+    uint32_t wphase = 0;
     bool ok = true;
-    uint4 hdr = make_uint4(0, 0, 0, 0), qa[4], qb[4];
-    if (total_sb > 0) {
-      const uint8_t* blk = sb_ptr(0);
-      hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-#pragma unroll
-      for (int G = 0; G < 4; G++) {
-        qa[G] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * G));
-        qb[G] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * G));
-      }
-    }
-    const uint32_t a_lane = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kATmemCol;
 
     // one super-block (four K steps); HALF is a compile-time copy of `half` so that nibble selection and
     // the scale bytes' positions are immediate operands
-    auto super_block = [&](auto half_c, int q) {
+    auto super_block = [&](auto half_c) {
       constexpr int HALF = decltype(half_c)::value;
-      const int ti = q / nsb;
-      const int tile = blockIdx.x + ti * gridDim.x;
-      const bool n_ok = (tile / t_tiles) * 128 + wrow < N;  // rows past N produce zeros
-      const float d = n_ok ? half_bits_to_f32(hdr.x) : 0.f, dmin = n_ok ? half_bits_to_f32(hdr.x >> 16) : 0.f;
+      ok = __all_sync(0xFFFFFFFFu, tc_wait(wfull_bar(ws), wphase, abort_flag));
+      if (!ok) return;
+      const unsigned char* blk = w_ring + ws * kTcWBytes;
+      const uint4 hdr = *reinterpret_cast<const uint4*>(blk);  // rows past N arrive as zeros: d = dmin = 0
+      const float d = half_bits_to_f32(hdr.x), dmin = half_bits_to_f32(hdr.x >> 16);
       uint32_t scw[2], mnw[2];
       q4k_unpack_scales(hdr.y, hdr.z, hdr.w, scw[0], scw[1], mnw[0], mnw[1]);
-      const bool more = q + 1 < total_sb;
-      const uint8_t* nblk = sb_ptr(more ? q + 1 : q);
-      hdr = __ldg(reinterpret_cast<const uint4*>(nblk));  // next super-block's header, used four steps from now
 #pragma unroll
       for (int G = 0; G < 4; G++) {
         const int j = 2 * G + HALF;
         const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
         const __nv_bfloat162 dsc = __float2bfloat162_rn(d * static_cast<float>(sc));
         const __nv_bfloat162 ndm = __float2bfloat162_rn(-dmin * static_cast<float>(mn));
-        const uint32_t w[8] = {qa[G].x, qa[G].y, qa[G].z, qa[G].w, qb[G].x, qb[G].y, qb[G].z, qb[G].w};
-        // refill this piece with the next super-block's (same group): four steps of distance
-        qa[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 16 + 32 * G));
-        qb[G] = __ldg(reinterpret_cast<const uint4*>(nblk + 32 + 32 * G));
+        const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * G);
+        const uint4 qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * G);
+        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
         uint32_t ot[16];  // this thread's 32 values of the step = 16 TMEM columns of packed pairs
 #pragma unroll
         for (int cc = 0; cc < 4; cc++) {  // 8 values = bytes 8cc .. 8cc+7
@@ -370,9 +370,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
           ot[4 * cc + 2] = deq_pair<0x4140>(w1, dsc, ndm);
           ot[4 * cc + 3] = deq_pair<0x4342>(w1, dsc, ndm);
         }
-        // the MMAs that read this weight stage six steps ago must have completed
+        // the MMAs that read this weight stage one ring turn ago must have completed
         ok = __all_sync(0xFFFFFFFFu, tc_wait(empty_bar(s), phase ^ 1, abort_flag));
-        if (!ok) break;
+        if (!ok) return;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         tmem_st16(a_lane + 32u * s + 16u * HALF, ot);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -384,22 +384,56 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
           phase ^= 1;
         }
       }
+      __syncwarp();
+      if (lane == 0) tc_mbar_arrive(wempty_bar(ws));  // this warp has read all it needs from the slot
+      if (++ws == kTcWStages) {
+        ws = 0;
+        wphase ^= 1;
+      }
     };
     if (half) {
-      for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 1>{}, q);
+      for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 1>{});
     } else {
-      for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 0>{}, q);
+      for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 0>{});
     }
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
   } else {
-    // ------------------------------------------------------------ token-tile copies (one lane)
+    // ------------------------------------------------------------ bulk copies (one lane)
+    // Packed weight tiles run kTcWStages - 1 super-blocks ahead of the token tiles; token tiles run as far
+    // ahead of the MMA as the ring allows.
     if (lane == 0) {
-      int s = 0;
-      uint32_t phase = 0;
+      const int nsb = K >> 8;
+      const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const int total_sb = my_tiles * nsb;
+      int s = 0, ws = 0;
+      uint32_t phase = 0, wphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % t_tiles) * TOK;
-        for (int ks = 0; ks < ksteps; ks++) {
+      int wq_next = 0;  // next super-block (flat index) whose packed weights have not been requested
+      auto issue_w = [&]() {
+        const int ti = wq_next / nsb, sb = wq_next - ti * nsb;
+        const int n0 = ((blockIdx.x + ti * gridDim.x) / t_tiles) * 128;
+        ok = tc_wait(wempty_bar(ws), wphase ^ 1, abort_flag);
+        if (!ok) return;
+        const uint32_t bar = wfull_bar(ws);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kTcWBytes) : "memory");
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+                "r"(smem_base + kWOff + ws * kTcWBytes),
+            "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * UB_Q4K_BYTES), "r"(n0)
+            : "memory");
+        wq_next++;
+        if (++ws == kTcWStages) {
+          ws = 0;
+          wphase ^= 1;
+        }
+      };
+      for (int i = 0; i < kTcWStages - 1 && wq_next < total_sb && ok; i++) issue_w();
+      for (int q = 0; q < total_sb && ok; q++) {
+        if (wq_next < total_sb) issue_w();
+        if (!ok) break;
+        const int ti = q / nsb, sb = q - ti * nsb;
+        const int m0 = ((blockIdx.x + ti * gridDim.x) % t_tiles) * TOK;
+        for (int G = 0; G < 4; G++) {
           ok = tc_wait(empty_bar(s), phase ^ 1, abort_flag);
           if (!ok) break;
           const uint32_t bar = full_bar(s);
@@ -407,7 +441,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
           asm volatile(
               "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
                   "r"(smem_base + s * kBBytes),
-              "l"(reinterpret_cast<uint64_t>(&x_map)), "r"(bar), "r"(ks * kTcBK), "r"(m0)
+              "l"(reinterpret_cast<uint64_t>(&x_map)), "r"(bar), "r"((sb * 4 + G) * kTcBK), "r"(m0)
               : "memory");
           if (++s == STAGES) {
             s = 0;
@@ -450,7 +484,8 @@ EncodeTiledFn encode_tiled_fn() {
 
 template <int TOK, int STAGES>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(TOK) * 256 + 1024;
+  const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(TOK < 128 ? TOK : 128) * 256 +
+                      static_cast<size_t>(kTcWStages) * kTcWBytes + 1024;
   const int tiles = ((N + 127) / 128) * ((M + TOK - 1) / TOK);
   const int sms = ub::num_sms();
   const int grid = tiles < sms ? tiles : sms;
@@ -467,6 +502,17 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaS
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ub::fail(UB_ERR_UNSUPPORTED);
+  // packed weights as a 2-D byte tensor: inner dimension = one row's bytes, outer = N rows; box = one
+  // super-block (144 bytes) of 128 rows, no swizzle; rows beyond N read as zeros
+  CUtensorMap wmap;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(K / UB_QK_K) * UB_Q4K_BYTES;
+  const cuuint64_t wdims[2] = {row_bytes, static_cast<cuuint64_t>(N)};
+  const cuuint64_t wstrides[1] = {row_bytes};
+  const cuuint32_t wbox[2] = {UB_Q4K_BYTES, 128};
+  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(wq), wdims, wstrides, wbox, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return ub::fail(UB_ERR_UNSUPPORTED);
   auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
@@ -474,7 +520,7 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaS
     return ub::fail(UB_ERR_CUDA);
   }
   kernel<<<grid, kTcThreads, smem, s>>>(static_cast<__nv_bfloat16*>(y), static_cast<const uint8_t*>(wq), M, N, K,
-                                        ub::device_error_word(), map);
+                                        ub::device_error_word(), map, wmap);
   return ub::check_launch();
 }
 
@@ -487,7 +533,7 @@ namespace ub {
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
   if (M <= 64) return launch_tc<64, 6>(y, x, wq, M, N, K, s);
   if (M <= 128) return launch_tc<128, 6>(y, x, wq, M, N, K, s);
-  return launch_tc<256, 5>(y, x, wq, M, N, K, s);
+  return launch_tc<256, 4>(y, x, wq, M, N, K, s);
 }
 
 }  // namespace ub
