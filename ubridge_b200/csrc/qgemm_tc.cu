@@ -19,10 +19,12 @@
 //   warp 0        allocates TMEM, then one elected lane issues tcgen05.mma and tcgen05.commit
 //   warps 1-4     epilogue: tcgen05.ld -> bf16 -> staging tile in shared memory (accumulator released
 //                 here) -> 16-byte coalesced stores to y, overlapping the next tile's main loop
-//   warps 5-12    weight producers: nibbles become bf16 (128 + q) with one byte permute per pair, minus 128
-//                 (exact), times d*sc minus dmin*m with packed bf16 FMAs; tcgen05.st, tcgen05.wait::st,
-//                 mbarrier arrive.  Packed weights are fetched four K steps ahead into registers.
-//   warp 13       one lane streams token tiles with cp.async.bulk.tensor as far ahead as the ring allows
+//   warps 5-12    weight producers: read their row's packed super-block from a shared-memory ring, turn
+//                 nibbles into bf16 (128 + q) with one byte permute per pair, minus 128 (exact), times d*sc
+//                 minus dmin*m with packed bf16 FMAs; tcgen05.st, tcgen05.wait::st, mbarrier arrive
+//   warp 13       one lane issues all bulk copies: packed weight tiles ([128 rows][144 bytes], one 2-D
+//                 tensor-map copy per super-block column, two super-blocks ahead) and token tiles (one
+//                 copy per K step, as far ahead as the ring allows)
 //
 // Every mbarrier wait is bounded; on expiry the CTA sets a shared abort flag, records UB_ERR_TIMEOUT in
 // the device error word, all roles leave their loops, and TMEM is freed before the kernel returns.
