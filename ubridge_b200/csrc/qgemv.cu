@@ -923,7 +923,11 @@ inline size_t dtype_size(int dt) { return dt == UB_DTYPE_F32 ? 4 : 2; }
 
 namespace ub {
 
-// Rows of x are processed four (then two, then one) at a time; each pass streams W once.
+template <typename XT>
+int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s);
+
+// Q4_K: up to eight rows of x per pass on the integer tensor-core kernel when its shared-memory plan fits.
+// Otherwise rows of x are processed four (then two, then one) at a time; each pass streams W once.
 template <typename XT>
 int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
@@ -934,6 +938,15 @@ int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K
     const XT* xp = x + static_cast<size_t>(m0) * K;
     void* yp = static_cast<char*>(y) + static_cast<size_t>(m0) * N * dtype_size(y_dtype);
     int st;
+    if (is_q4k && (reinterpret_cast<uintptr_t>(wq) & 15) == 0) {
+      const int mi = left >= 8 ? 8 : left;
+      st = q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, s);
+      if (st == UB_OK) {
+        m0 += mi;
+        continue;
+      }
+      if (st != UB_ERR_UNSUPPORTED) return st;
+    }
     if (is_q4k) {
       st = mt == 4 ? launch_q4k<XT, 4>(w, xp, yp, N, K, y_dtype, s)
                    : (mt == 2 ? launch_q4k<XT, 2>(w, xp, yp, N, K, y_dtype, s)

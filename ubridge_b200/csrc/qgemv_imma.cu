@@ -1,0 +1,396 @@
+// Decode GEMV / small-batch matmul for Q4_K weights on the integer tensor-core path.
+//
+//   y[M,N] = x[M,K] . dequant(Wq)^T   for M <= 8 tokens per launch, f32 accumulation of exact integer dots.
+//
+// Replaces the reference's LHS-resident decode matmul (kernels/matmul.cpp:1197-1208,
+// kernels/third_party/matmul_decoding.h:12-570) for GGUF Q4_K weights (block layout kernels/quant.cpp:145-150,
+// scale unpacking :356-363).
+//
+// Idea.  A Q4_K byte holds two weights of two different 32-value sub-blocks (low nibble: sub-block 2G, high
+// nibble: 2G+1).  mma.sync.m16n8k32 (u8 x s8 -> s32) multiplies 16 weight rows x 32 bytes by 8 columns, so one
+// instruction covers one sub-block pair of 16 rows, and the bytes are used AS THEY LIE IN MEMORY:
+//     MMA 1:  A = raw bytes (lo + 16 hi),   B = [ x(2G) | 0 ]          -> sum(lo x(2G)) + 16 sum(hi x(2G)) | 0
+//     MMA 2:  A = raw & 0xF0 (16 hi),       B = [ -x(2G) | x(2G+1) ]   accumulated on top
+//                                                                       -> sum(lo x(2G)) | 16 sum(hi x(2G+1))
+// One mask per word is all the unpacking there is.  Activations are quantised once per launch to 15-bit
+// block fixed point per 256 values (q = 254 hi + lo, |hi|,|lo| <= 127, scale amax / 32258), the two limbs are
+// two B columns, so a token occupies four of the eight columns and a launch carries token PAIRS.  The integer
+// dots are exact; they meet the 6-bit scales in integer arithmetic, the mins through dp4a against the
+// sub-block sums of q, and turn into f32 once per (row, super-block).
+//
+// Data movement.  One persistent CTA per SM owns a contiguous range of rows.  A producer warp streams 16-row
+// tiles (one bulk copy per row, rows padded to a bank-conflict-free stride) into an mbarrier ring; 16 compute
+// warps each own one super-block column of the tile.  Per-row partial sums stay in registers for up to seven
+// tiles and are added across warps once at the end, in a fixed order.
+// Every mbarrier wait is bounded: on expiry the kernel records UB_ERR_TIMEOUT in the device error word,
+// stops waiting and runs out its loops.
+#include "common.cuh"
+
+namespace {
+
+using namespace ub;
+
+constexpr int kCW = 16;                     // compute warps; warp kCW is the producer
+constexpr int kImmaThreads = (kCW + 1) * 32;
+constexpr int kMT = 7;                      // 16-row tiles whose partial sums a lane keeps in registers
+constexpr int kChunkSb = 16;                // super-blocks of K per ring stage (one per compute warp)
+constexpr int kMaxStages = 8;
+constexpr uint32_t kSpinLimit = 400000;
+constexpr float kXQMax = 32258.f;           // 127 * 254
+constexpr size_t kSmemBudget = 220 * 1024;
+
+__device__ __forceinline__ void ib_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void ib_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ib_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool ib_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool ib_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; i++)
+    if (ib_try(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void ib_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// d += A(16x32 u8, row) . B(32x8 s8, col)
+__device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
+}
+__device__ __forceinline__ int dp4a_u_s(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+template <typename XT>
+__device__ __forceinline__ void ld_x8(const XT* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void ld_x8<float>(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void ld_x8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+__device__ __forceinline__ void st_y(void* y, size_t idx, int dtype, float v) {
+  if (dtype == UB_DTYPE_F32)
+    static_cast<float*>(y)[idx] = v;
+  else if (dtype == UB_DTYPE_BF16)
+    static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+  else
+    static_cast<__half*>(y)[idx] = __float2half_rn(v);
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  return (a & 255) | ((b & 255) << 8) | ((c & 255) << 16) | (static_cast<uint32_t>(d & 255) << 24);
+}
+
+// Shared-memory geometry shared by host and device.
+struct ImmaGeom {
+  int nsb, nchunks, row_stride, stage_bytes;
+};
+__host__ __device__ inline ImmaGeom imma_geom(int K) {
+  ImmaGeom g;
+  g.nsb = K >> 8;
+  g.nchunks = (g.nsb + kChunkSb - 1) / kChunkSb;
+  const int cs = g.nsb < kChunkSb ? g.nsb : kChunkSb;
+  // 16-byte loads of eight rows must fall into distinct banks: stride = 32 bytes modulo 128
+  g.row_stride = (cs * UB_Q4K_BYTES + 127) / 128 * 128 + 32;
+  g.stage_bytes = 16 * g.row_stride;
+  return g;
+}
+
+// MP: token pairs per launch (tokens 2p and 2p+1 share an MMA; M <= 2 MP, missing tokens are zeros).
+template <typename XT, int MP>
+__global__ void __launch_bounds__(kImmaThreads, 1)
+qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void* __restrict__ y, int M, int N,
+                      int K, int y_dtype, int S, int* err_word) {
+  extern __shared__ __align__(128) unsigned char ismem[];
+  __shared__ __align__(8) unsigned long long bars[2 * kMaxStages];  // full[S], empty[S]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const ImmaGeom geo = imma_geom(K);
+  const int nsb = geo.nsb, nchunks = geo.nchunks;
+  const size_t row_bytes = static_cast<size_t>(nsb) * UB_Q4K_BYTES;
+  const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ismem));
+  const uint32_t bars_s = static_cast<uint32_t>(__cvta_generic_to_shared(bars));
+  unsigned char* const bfrag = ismem + static_cast<size_t>(S) * geo.stage_bytes;  // [MP][nsb][4 G][2][32 lanes] uint2
+  unsigned char* const meta = bfrag + static_cast<size_t>(MP) * nsb * 2048;        // [MP][nsb][4 t] uint4
+  float* const red = reinterpret_cast<float*>(ismem);  // aliases the ring between batches
+
+  // rows of this CTA: contiguous, near-even split of N over the grid
+  const int base = N / gridDim.x, rem = N % gridDim.x;
+  const int r0 = blockIdx.x * base + min(static_cast<int>(blockIdx.x), rem);
+  const int nrows = base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
+  const int nbatches = (nrows + 16 * kMT - 1) / (16 * kMT);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      ib_init(bars_s + 8 * s, 1);
+      ib_init(bars_s + 8 * (kMaxStages + s), kCW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  bool ok = true;
+  int it = 0;  // ring items issued / consumed so far (same sequence on both sides)
+
+  if (warp < kCW) {
+    // ---- activations -> fragments of the B operand, once per launch ----
+    for (int u = warp; u < 2 * MP * nsb; u += kCW) {
+      const int m = u / nsb, sb = u - m * nsb;
+      float v[8];
+      if (m < M) {
+        ld_x8<XT>(x + static_cast<size_t>(m) * K + sb * 256 + 8 * lane, v);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = 0.f;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      const float inv = amax > 0.f ? kXQMax / amax : 0.f;
+      const float xs = amax * (1.f / kXQMax);
+      int hi[8], lo[8], sum = 0;
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        const int q = __float2int_rn(v[e] * inv);
+        hi[e] = __float2int_rn(static_cast<float>(q) * (1.f / 254.f));
+        lo[e] = q - 254 * hi[e];
+        sum += q;
+      }
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);  // sum of q over this lane's 32-value sub-block
+      const uint2 hv = make_uint2(pack4(hi[0], hi[1], hi[2], hi[3]), pack4(hi[4], hi[5], hi[6], hi[7]));
+      const uint2 lv = make_uint2(pack4(lo[0], lo[1], lo[2], lo[3]), pack4(lo[4], lo[5], lo[6], lo[7]));
+      const uint2 nhv = make_uint2(pack4(-hi[0], -hi[1], -hi[2], -hi[3]), pack4(-hi[4], -hi[5], -hi[6], -hi[7]));
+      const uint2 nlv = make_uint2(pack4(-lo[0], -lo[1], -lo[2], -lo[3]), pack4(-lo[4], -lo[5], -lo[6], -lo[7]));
+      const int p = m >> 1, cb = 4 * (m & 1);
+      const int j = lane >> 2, tt = lane & 3, G = j >> 1;
+      uint2* f1 = reinterpret_cast<uint2*>(bfrag) + ((static_cast<size_t>(p) * nsb + sb) * 4 + G) * 64;  // MMA 1
+      uint2* f2 = f1 + 32;                                                                                // MMA 2
+      if ((j & 1) == 0) {
+        f1[(cb + 0) * 4 + tt] = hv;
+        f1[(cb + 1) * 4 + tt] = lv;
+        f2[(cb + 0) * 4 + tt] = nhv;
+        f2[(cb + 1) * 4 + tt] = nlv;
+      } else {
+        f1[(cb + 2) * 4 + tt] = make_uint2(0, 0);
+        f1[(cb + 3) * 4 + tt] = make_uint2(0, 0);
+        f2[(cb + 2) * 4 + tt] = hv;
+        f2[(cb + 3) * 4 + tt] = lv;
+      }
+      // sub-block sums as three byte limbs (top one signed), four sub-blocks per word, for the min term
+      int sj[8];
+#pragma unroll
+      for (int q = 0; q < 8; q++) sj[q] = __shfl_sync(0xFFFFFFFFu, sum, 4 * q);
+      if (lane < 2) {
+        const int s4[4] = {lane ? sj[4] : sj[0], lane ? sj[5] : sj[1], lane ? sj[6] : sj[2], lane ? sj[7] : sj[3]};
+        uint4 mt;
+        mt.x = pack4(s4[0], s4[1], s4[2], s4[3]);
+        mt.y = pack4(s4[0] >> 8, s4[1] >> 8, s4[2] >> 8, s4[3] >> 8);
+        mt.z = pack4(s4[0] >> 16, s4[1] >> 16, s4[2] >> 16, s4[3] >> 16);
+        mt.w = __float_as_uint(xs);
+        reinterpret_cast<uint4*>(meta)[(static_cast<size_t>(p) * nsb + sb) * 4 + 2 * (m & 1) + lane] = mt;
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kCW * 32) : "memory");  // compute warps: fragments complete
+  }
+
+  const int par = t & 1;
+  for (int b = 0; b < nbatches; b++) {
+    const int rb0 = r0 + b * 16 * kMT;
+    const int brow = min(16 * kMT, nrows - b * 16 * kMT);
+    const int n_mt = (brow + 15) >> 4;
+
+    float acc[kMT][MP][2];  // consumers: partial sums of rows (g, g + 8) of each tile, per token pair
+    if (warp == kCW) {
+      // ---- producer: 16-row tiles, one bulk copy per row ----
+      for (int mt = 0; mt < n_mt; mt++) {
+        const int rows_here = min(16, brow - 16 * mt);
+        for (int c = 0; c < nchunks; c++, it++) {
+          const int slot = it % S, round = it / S;
+          if (ok && round > 0) ok = ib_wait(bars_s + 8 * (kMaxStages + slot), (round - 1) & 1);
+          ok = __all_sync(0xFFFFFFFFu, ok);
+          if (!ok) continue;
+          const int cs = min(kChunkSb, nsb - c * kChunkSb);
+          const uint32_t cbytes = static_cast<uint32_t>(cs * UB_Q4K_BYTES);
+          const uint32_t full = bars_s + 8 * slot;
+          if (lane == 0) ib_expect_tx(full, cbytes * rows_here);
+          __syncwarp();
+          if (lane < rows_here)
+            ib_copy(ring_s + slot * geo.stage_bytes + lane * geo.row_stride,
+                    wq + static_cast<size_t>(rb0 + 16 * mt + lane) * row_bytes +
+                        static_cast<size_t>(c) * kChunkSb * UB_Q4K_BYTES,
+                    cbytes, full);
+        }
+      }
+    } else {
+      // ---- consumers: warp w owns super-block w of every chunk ----
+#pragma unroll
+      for (int mt = 0; mt < kMT; mt++)
+#pragma unroll
+        for (int p = 0; p < MP; p++) acc[mt][p][0] = acc[mt][p][1] = 0.f;
+
+#pragma unroll
+      for (int mt = 0; mt < kMT; mt++) {
+        if (mt < n_mt) {
+          for (int c = 0; c < nchunks; c++, it++) {
+            const int slot = it % S, round = it / S;
+            if (ok) ok = __all_sync(0xFFFFFFFFu, ib_wait(bars_s + 8 * slot, round & 1));
+            const int cs = min(kChunkSb, nsb - c * kChunkSb);
+            if (ok && warp < cs) {
+              const int sb = c * kChunkSb + warp;
+              const unsigned char* rowA =
+                  ismem + static_cast<size_t>(slot) * geo.stage_bytes + g * geo.row_stride + warp * UB_Q4K_BYTES;
+              const unsigned char* rowB = rowA + 8 * geo.row_stride;
+              const uint4 hA = *reinterpret_cast<const uint4*>(rowA), hB = *reinterpret_cast<const uint4*>(rowB);
+              uint2 wA[4], wB[4];
+#pragma unroll
+              for (int G = 0; G < 4; G++) {
+                wA[G] = *reinterpret_cast<const uint2*>(rowA + 16 + 32 * G + 8 * t);
+                wB[G] = *reinterpret_cast<const uint2*>(rowB + 16 + 32 * G + 8 * t);
+              }
+              uint32_t scA[2], mnA[2], scB[2], mnB[2];
+              q4k_unpack_scales(hA.y, hA.z, hA.w, scA[0], scA[1], mnA[0], mnA[1]);
+              q4k_unpack_scales(hB.y, hB.z, hB.w, scB[0], scB[1], mnB[0], mnB[1]);
+              // this lane's columns belong to sub-blocks 2G + par: bring their scales to bytes 0 and 2
+              scA[0] >>= 8 * par, scA[1] >>= 8 * par, scB[0] >>= 8 * par, scB[1] >>= 8 * par;
+              // ... and to sub-blocks 4 par .. 4 par + 3 for the min term
+              const uint32_t mA = par ? mnA[1] : mnA[0], mB = par ? mnB[1] : mnB[0];
+              const float dA = half_bits_to_f32(hA.x), dminA = half_bits_to_f32(hA.x >> 16);
+              const float dB = half_bits_to_f32(hB.x), dminB = half_bits_to_f32(hB.x >> 16);
+#pragma unroll
+              for (int p = 0; p < MP; p++) {
+                const uint2* f1 = reinterpret_cast<const uint2*>(bfrag) + (static_cast<size_t>(p) * nsb + sb) * 256 + lane;
+                const uint4 mt4 = reinterpret_cast<const uint4*>(meta)[(static_cast<size_t>(p) * nsb + sb) * 4 + t];
+                int hiA = 0, loA = 0, hiB = 0, loB = 0;
+#pragma unroll
+                for (int G = 0; G < 4; G++) {
+                  const uint2 b1 = f1[G * 64], b2 = f1[G * 64 + 32];
+                  int d[4] = {0, 0, 0, 0};
+                  imma_u8s8(d, wA[G].x, wB[G].x, wA[G].y, wB[G].y, b1);
+                  imma_u8s8(d, wA[G].x & 0xF0F0F0F0u, wB[G].x & 0xF0F0F0F0u, wA[G].y & 0xF0F0F0F0u,
+                            wB[G].y & 0xF0F0F0F0u, b2);
+                  const int sa = (G & 1) ? __byte_perm(scA[G >> 1], 0, 0x4442) : (scA[G >> 1] & 0xFF);
+                  const int sbv = (G & 1) ? __byte_perm(scB[G >> 1], 0, 0x4442) : (scB[G >> 1] & 0xFF);
+                  hiA += d[0] * sa, loA += d[1] * sa, hiB += d[2] * sbv, loB += d[3] * sbv;
+                }
+                const float xs = __uint_as_float(mt4.w);
+                const float xsm = par ? xs * 0.0625f : xs;  // odd lanes carry 16 x the high nibbles
+                const int tA = (dp4a_u_s(mA, mt4.z, 0) * 256 + static_cast<int>(__dp4a(mA, mt4.y, 0u))) * 256 +
+                               static_cast<int>(__dp4a(mA, mt4.x, 0u));
+                const int tB = (dp4a_u_s(mB, mt4.z, 0) * 256 + static_cast<int>(__dp4a(mB, mt4.y, 0u))) * 256 +
+                               static_cast<int>(__dp4a(mB, mt4.x, 0u));
+                const float fA = fmaf(static_cast<float>(hiA), 254.f, static_cast<float>(loA));
+                const float fB = fmaf(static_cast<float>(hiB), 254.f, static_cast<float>(loB));
+                acc[mt][p][0] += fmaf(dA * xsm, fA, -(dminA * xs) * static_cast<float>(tA));
+                acc[mt][p][1] += fmaf(dB * xsm, fB, -(dminB * xs) * static_cast<float>(tB));
+              }
+            }
+            __syncwarp();
+            if (lane == 0) ib_arrive(bars_s + 8 * (kMaxStages + slot));
+          }
+        }
+      }
+    }
+    __syncthreads();  // (A) every stage of this batch has been consumed: the ring may hold the partial sums
+    if (warp < kCW) {
+      // the two lanes of a (row, token) pair hold its even and odd sub-blocks
+#pragma unroll
+      for (int mt = 0; mt < kMT; mt++)
+#pragma unroll
+        for (int p = 0; p < MP; p++)
+#pragma unroll
+          for (int rs = 0; rs < 2; rs++) {
+            const float v = acc[mt][p][rs] + __shfl_xor_sync(0xFFFFFFFFu, acc[mt][p][rs], 1);
+            if (par == 0) red[((((warp * kMT + mt) * MP + p) * 2 + rs) * 8 + g) * 2 + (t >> 1)] = v;
+          }
+    }
+    __syncthreads();  // (B) partial sums visible
+    for (int o = threadIdx.x; o < n_mt * 16 * 2 * MP; o += kImmaThreads) {
+      const int rl = o / (2 * MP), tok = o - rl * (2 * MP);
+      if (rl < brow && tok < M) {
+        const int mt = rl >> 4, rs = (rl >> 3) & 1, gg = rl & 7, p = tok >> 1, tk = tok & 1;
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kCW; w++) tot += red[((((w * kMT + mt) * MP + p) * 2 + rs) * 8 + gg) * 2 + tk];
+        st_y(y, static_cast<size_t>(tok) * N + rb0 + rl, y_dtype, tot);
+      }
+    }
+    __syncthreads();  // (C) the ring is free again
+  }
+  if (!ok && lane == 0) report_device_error(err_word, UB_ERR_TIMEOUT);
+}
+
+template <typename XT, int MP>
+int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
+  const ImmaGeom geo = imma_geom(K);
+  const size_t fixed = static_cast<size_t>(MP) * geo.nsb * (2048 + 64);
+  if (fixed + 2 * static_cast<size_t>(geo.stage_bytes) > kSmemBudget) return UB_ERR_UNSUPPORTED;
+  int S = static_cast<int>((kSmemBudget - fixed) / geo.stage_bytes);
+  if (S > kMaxStages) S = kMaxStages;
+  const size_t red_bytes = static_cast<size_t>(kCW) * kMT * MP * 32 * sizeof(float);
+  if (static_cast<size_t>(S) * geo.stage_bytes < red_bytes) return UB_ERR_UNSUPPORTED;
+  const size_t smem = static_cast<size_t>(S) * geo.stage_bytes + fixed;
+  auto kernel = qgemv_q4k_imma_kernel<XT, MP>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  const int sms = ub::num_sms();
+  const int tiles = (N + 15) / 16;
+  const int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, kImmaThreads, smem, s>>>(wq, x, y, M, N, K, y_dtype, S, ub::device_error_word());
+  return ub::check_launch();
+}
+
+}  // namespace
+
+namespace ub {
+
+// y[M,N] = x[M,K] . dequant(Wq)^T for 1 <= M <= 8; returns UB_ERR_UNSUPPORTED (without setting the thread's
+// status) when the shape does not fit this kernel's shared-memory plan, so that the caller can use another.
+template <typename XT>
+int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
+  const uint8_t* w = static_cast<const uint8_t*>(wq);
+  if (M <= 2) return launch_imma<XT, 1>(w, x, y, M, N, K, y_dtype, s);
+  if (M <= 4) return launch_imma<XT, 2>(w, x, y, M, N, K, y_dtype, s);
+  return launch_imma<XT, 4>(w, x, y, M, N, K, y_dtype, s);
+}
+
+template int q4k_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, cudaStream_t);
+template int q4k_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, cudaStream_t);
+
+}  // namespace ub
