@@ -20,7 +20,9 @@ Printed JSON (one line, rank 0):
 and device, so the CPU restatement is the only reference arm that can run).
 
 Other workloads (c1, c2_m4, c2_m16, c3, c4, c5_m1, c5_m512) print the same line for the other
-configurations; c4 and c5 shard over the ranks (expert / tensor parallel) with NCCL all-reduces.
+configurations.  The linear workloads run one replica per GPU (weak scaling); c4 (MoE layer) and c5
+(70B-shaped linear stack) shard over the ranks (expert / tensor parallel, strong scaling) with NCCL
+all-reduces through the eccl entry points.
 """
 from __future__ import annotations
 
@@ -145,6 +147,9 @@ class CpuArm:
         per_call = el / reps
         if wl["unit"] == "GB/s":
             value = self.w.nbytes / per_call / 1e9
+        elif wl["unit"] == "tok/s":
+            # expert GEMM rate of the sample, converted with the layer's flop per token
+            value = 2.0 * self.Ms * wl["N"] * wl["K"] / per_call / wl["flop_per_token"]
         else:
             value = 2.0 * self.Ms * wl["N"] * wl["K"] / per_call / 1e12
         sample = "%d x [%dx%d %s] . x[%d rows] in %.2f s" % (reps, wl["N"], wl["K"], "Q4_K" if wl["is_q4k"] else "Q8_0",
@@ -167,6 +172,17 @@ WORKLOADS = {
                desc="Q4_K 14336x4096 prefill GEMM, M=2048"),
     "c3_m1024": dict(N=14336, K=4096, M=1024, is_q4k=True, x_bf16=True, unit="TFLOP/s", seed=1002, copies=2,
                      cpu_rows=64, desc="Q4_K 14336x4096 prefill GEMM, M=1024 (the small case profiled under ncu)"),
+    # sharded workloads.  N, K, M, cpu_rows describe the matrix the CPU arm samples (one expert's gate
+    # projection; a quarter of the gate projection of the 70B-shaped MLP).
+    "c4": dict(kind="ep", T=256, H=4096, I=14336, E=8, top_k=2, block=64, unit="tok/s", seed=1004, is_q4k=True,
+               x_bf16=True, N=14336, K=4096, M=256, cpu_rows=64, flop_per_token=2 * 3 * 2.0 * 4096 * 14336,
+               desc="Mixtral-shaped fused MoE layer, 8 experts top-2, 256 tokens, Q4_K experts, expert parallel"),
+    "c5_m1": dict(kind="tp", hidden=8192, inter=28672, q_heads=64, kv_heads=8, head_dim=128, unit="GB/s", seed=1005,
+                  is_q4k=True, x_bf16=True, N=7168, K=8192, M=1,
+                  desc="Llama-3-70B-shaped QKV/O + MLP linear stack, Q4_K, tensor parallel, M=1"),
+    "c5_m512": dict(kind="tp", hidden=8192, inter=28672, q_heads=64, kv_heads=8, head_dim=128, unit="TFLOP/s",
+                    seed=1005, is_q4k=True, x_bf16=True, N=7168, K=8192, M=512, cpu_rows=32,
+                    desc="Llama-3-70B-shaped QKV/O + MLP linear stack, Q4_K, tensor parallel, M=512"),
 }
 
 
@@ -242,7 +258,7 @@ def run_linear(args, wl, rank, world, torch, dist):
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
 
-    # decode kernel: M rows are processed 4/2/1 at a time, one launch each
+    # Q8_0 decode kernel: M rows are processed 4/2/1 at a time, one launch each
     def decode_launches(m):
         n = 0
         while m > 0:
@@ -250,7 +266,10 @@ def run_linear(args, wl, rank, world, torch, dist):
             m -= t_
             n += 1
         return n
-    launches_per_call = decode_launches(M) if (M <= 16 or not is_q4k) else 1
+    if is_q4k:
+        launches_per_call = (M + 7) // 8 if M <= 16 else 1  # decode kernel: up to eight rows per pass
+    else:
+        launches_per_call = decode_launches(M)
     launches = args.steps * copies * passes * launches_per_call
 
     calls = copies * passes * world
@@ -326,6 +345,162 @@ def run_linear(args, wl, rank, world, torch, dist):
                 dtype="u4+f16 scales -> f32 accumulate" if is_q4k else "i8+f16 scales -> f32 accumulate")
 
 
+def run_sharded(args, wl, rank, world, torch, dist):
+    """Tensor-parallel (c5) and expert-parallel (c4) workloads: the matrices are split over the ranks, every
+    rank streams its shard and the partial outputs meet in NCCL all-reduces (strong scaling)."""
+    import ubridge_b200 as ub
+    from oracle import oracle as o  # input generation only
+    from ubridge_b200 import eccl, parallel
+
+    dev_index = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(dev_index)
+    dev = ub.GcuDevice(dev_index)
+    dev.bind_to_thread()
+    ext = torch.cuda.ExternalStream(dev.stream.value)
+    comm, all_reduce = None, None
+    if world > 1:
+        box = [eccl.Id().internal() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = eccl.Comm.from_rank(rank, world, eccl.Id(box[0]))
+
+        def all_reduce(buf, count):
+            comm.all_reduce(buf, buf, count, eccl.Bfloat16, eccl.ReduceOp.Sum, stream=dev.stream)
+
+    rng = np.random.default_rng(wl["seed"] + 17 * rank)
+    q4 = lambda n, k: o.gen_q4k_weight(rng, n, k).reshape(-1)  # noqa: E731
+    kind = wl["kind"]
+    if kind == "tp":
+        H, I, M = wl["hidden"], wl["inter"], wl["M"]
+        ql, kvl, il = wl["q_heads"] * wl["head_dim"] // world, wl["kv_heads"] * wl["head_dim"] // world, I // world
+        shapes = [(ql + 2 * kvl, H), (H, ql), (2 * il, H), (H, il)]  # this rank's shards, generated at shard shape
+        shard_bytes = sum(n * Q4K_ROW_BYTES(k) for n, k in shapes)
+        total_bytes = shard_bytes * world
+        flop = 2.0 * M * sum(n * k for n, k in shapes) * world
+        in_elems, out_elems = M * H, M * H
+    else:
+        T, H, I, E = wl["T"], wl["H"], wl["I"], wl["E"]
+        e0, e1 = parallel.expert_range(E, rank, world)
+        el = e1 - e0
+        shard_bytes = el * (2 * I * Q4K_ROW_BYTES(H) + H * Q4K_ROW_BYTES(I))
+        total_bytes = E * (2 * I * Q4K_ROW_BYTES(H) + H * Q4K_ROW_BYTES(I))
+        flop = T * wl["flop_per_token"]
+        in_elems, out_elems = T * H, T * H
+    # distinct copies of the shard so that consecutive steps stream from HBM, not from the 126 MB L2
+    ncopies = max(1, -(-300_000_000 // shard_bytes))
+    layers = []
+    for _c in range(ncopies):
+        if kind == "tp":
+            ws_ = [q4(n, k) for n, k in shapes]
+            layers.append(parallel.TPLinearStack(dev, H, I, wl["q_heads"], wl["kv_heads"], wl["head_dim"], world,
+                                                 ws_[0], ws_[1], ws_[2], ws_[3], M, all_reduce))
+        else:
+            w13 = np.concatenate([q4(2 * I, H) for _e in range(el)])
+            w2 = np.concatenate([q4(H, I) for _e in range(el)])
+            layers.append(parallel.EPMoELayer(dev, T, H, I, E, wl["top_k"], wl["block"], rank, world, w13, w2,
+                                              all_reduce))
+    xr = np.random.default_rng(wl["seed"])  # activations are replicated: same seed on every rank
+    x_host = o.f32_to_bf16_bits(o.gen_activation(xr, in_elems // H, H, True)).reshape(-1)
+    d_x = dev.htod_sync_copy(x_host)
+    d_logits = None
+    if kind == "ep":
+        lg_host = o.f32_to_bf16_bits(o.gen_activation(xr, wl["T"], wl["E"], True)).reshape(-1)
+        d_logits = dev.htod_sync_copy(lg_host)
+
+    def forward(layer):
+        return layer.forward(d_x, wl["M"]) if kind == "tp" else layer.forward(d_x, d_logits)
+
+    # one eager pass per copy (resolves symbols, sets attributes), then one graph per copy
+    for layer in layers:
+        forward(layer)
+    dev.synchronize()
+    graphs = []
+    with torch.cuda.stream(ext):
+        for layer in layers:
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=ext):
+                forward(layer)
+            graphs.append(g_)
+        for i in range(args.warmup):
+            graphs[i % ncopies].replay()
+        ext.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(dev_index)
+        if rank == 0:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(ext)
+        for i in range(args.steps):
+            graphs[i % ncopies].replay()
+        ev1.record(ext)
+        ext.synchronize()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if rank == 0 else None
+    ms_total = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    s_step = ms_step * 1e-3
+
+    def metric_value(sec):
+        if wl["unit"] == "GB/s":
+            return total_bytes / sec / 1e9
+        if wl["unit"] == "TFLOP/s":
+            return flop / sec / 1e12
+        return wl["T"] / sec
+
+    value = metric_value(s_step)
+    # ---- end to end: host activations in, host result out, every step (eager launches through the API)
+    host_x = torch.from_numpy(x_host.view(np.uint8).reshape(-1).copy()).pin_memory()
+    host_y = torch.empty((out_elems * 2,), dtype=torch.uint8).pin_memory()
+    lib = ub.lib()
+
+    def e2e_step(i):
+        lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), ctypes.c_void_p(host_x.data_ptr()), host_x.numel())
+        out = forward(layers[i % ncopies])
+        lib.ub_memcpy_dtoh(dev._handle, ctypes.c_void_p(host_y.data_ptr()), ctypes.c_void_p(out.ptr), host_y.numel())
+        dev.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        e2e_step(i)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    el_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([el_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        el_s = float(t.item())
+    e2e = {"value": metric_value(el_s / args.steps), "unit": wl["unit"], "h2d_bytes_per_step": int(host_x.numel()),
+           "d2h_bytes_per_step": int(host_y.numel())}
+
+    peaks = measured_peaks()
+    # per-GPU roofline: this rank's shard bytes (or flop) per step against one GPU's measured peak
+    hbm = shard_bytes / s_step / 1e9
+    tf = flop / world / s_step / 1e12
+    tensor_peak = peaks["bf16_tflops"] if ms_total < 1000.0 else peaks["bf16_tflops_sustained"]
+    if wl["unit"] == "TFLOP/s":
+        roof = {"bound": "tensor", "achieved": tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": tf / tensor_peak}
+    else:
+        roof = {"bound": "hbm", "achieved": hbm, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": hbm / peaks["hbm_gbs"],
+                "tensor_frac": tf / tensor_peak}
+    roof.update({"traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": peaks["source"], "per_gpu": True,
+                 "algorithmic_bytes_per_step_per_gpu": shard_bytes, "algorithmic_flops_per_step": flop,
+                 "step_us": s_step * 1e6})
+    # kernels of ours per step: tp = 4 matmuls (+ conversions none: bf16) + copy + SiLU.up; ep = the fused layer
+    launches = args.steps * layers[0].launches_per_forward
+    if comm is not None:
+        dev.synchronize()
+        comm.destroy()
+    return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
+                dtype="u4+f16 scales -> f32 accumulate", ncopies=ncopies)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -339,12 +514,20 @@ def main():
     wl = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    metric = "weight_GBps" if wl["unit"] == "GB/s" else "TFLOPS"
-    config = {"workload": "%s: %s; one step = %d matmuls over %d distinct weight copies (%.0f MB, larger than L2)" % (
-        args.workload, wl["desc"], wl["copies"] * wl.get("passes", 1), wl["copies"],
-        wl["copies"] * wl["N"] * (Q4K_ROW_BYTES(wl["K"]) if wl["is_q4k"] else Q8_ROW_BYTES(wl["K"])) / 1e6),
-        "N": wl["N"], "K": wl["K"], "M": wl["M"], "format": "Q4_K" if wl["is_q4k"] else "Q8_0",
-        "l2_policy": "inputs larger than L2", "parallelism": "replicas x%d" % args.gpus}
+    metric = {"GB/s": "weight_GBps", "TFLOP/s": "TFLOPS", "tok/s": "moe_tokens_per_s"}[wl["unit"]]
+    sharded = "kind" in wl
+    if sharded:
+        config = {"workload": "%s: %s; one step = one pass over the layer; consecutive steps use distinct weight "
+                              "copies (>= 300 MB per GPU in total, larger than L2)" % (args.workload, wl["desc"]),
+                  "M": wl["M"], "format": "Q4_K", "l2_policy": "inputs larger than L2",
+                  "parallelism": "%s%d" % (wl["kind"], args.gpus)}
+    else:
+        config = {"workload": "%s: %s; one step = %d matmuls over %d distinct weight copies (%.0f MB, larger than "
+                              "L2)" % (args.workload, wl["desc"], wl["copies"] * wl.get("passes", 1), wl["copies"],
+                                       wl["copies"] * wl["N"] *
+                                       (Q4K_ROW_BYTES(wl["K"]) if wl["is_q4k"] else Q8_ROW_BYTES(wl["K"])) / 1e6),
+                  "N": wl["N"], "K": wl["K"], "M": wl["M"], "format": "Q4_K" if wl["is_q4k"] else "Q8_0",
+                  "l2_policy": "inputs larger than L2", "parallelism": "replicas x%d" % args.gpus}
 
     if args.impl == "reference":
         if rank != 0:
@@ -361,7 +544,8 @@ def main():
         value = statistics.mean(vals)
         line = {"impl": "reference", "metric": metric, "value": value, "unit": wl["unit"], "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config,
                 "cpu_baseline": {"value": value, "unit": wl["unit"], "cores": cores, "kind": "port",
                                  "sample": "each step: " + sample},
                 "e2e": {"value": value, "unit": wl["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -377,7 +561,7 @@ def main():
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         dist.init_process_group("nccl")
     try:
-        res = run_linear(args, wl, rank, world, torch, dist)
+        res = (run_sharded if sharded else run_linear)(args, wl, rank, world, torch, dist)
         if rank == 0:
             cpu = None
             if world == 1:
@@ -386,7 +570,8 @@ def main():
                 cpu = {"value": v, "unit": wl["unit"], "cores": arm.cores, "kind": "port", "sample": sample}
             line = {"metric": metric, "value": res["value"], "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
                     "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
-                    "scaling": "weak", "vs_baseline": None, "dtype": res["dtype"], "data": "synthetic",
+                    "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": res["dtype"],
+                    "data": "synthetic",
                     "config": config, "roofline": res["roofline"], "cpu_baseline": cpu, "e2e": res["e2e"],
                     "gpu_launches": res["launches"], "clocks": res["clocks"]}
             print(json.dumps(line))

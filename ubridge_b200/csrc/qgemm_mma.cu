@@ -247,6 +247,15 @@ int q4k_gemm_mma(void* y, const void* x, const void* wq, int M, int N, int K, cu
 
 }  // namespace ub
 
+namespace ub {
+bool q4k_moe_tc_supported(int positions, int K, int N, int block);
+int moe_gather_rows(void* xg, const void* hidden, const int32_t* sorted_ids, const int32_t* num_post_pad, int positions,
+                    int num_valid, int top_k, int H, cudaStream_t s);
+int q4k_moe_gemm_tc(void* C, const void* A, const void* Bq, const float* topk_w, const int32_t* sorted_ids,
+                    const int32_t* experts_ids, const int32_t* num_post_pad, int positions, int K, int N, int E,
+                    int num_valid, int block, int act_silu_mul, cudaStream_t s);
+}  // namespace ub
+
 extern "C" {
 
 int ub_fused_moe_q4k_gemm(void* C, const void* A, const void* Bq, const float* topk_weights, const int32_t* sorted_ids,
@@ -285,7 +294,10 @@ int ub_fused_moe_q4k_gemm(void* C, const void* A, const void* Bq, const float* t
 
 // Workspace layout of ub_moe_layer_q4k (each region 256-byte aligned):
 //   w_t [T*k] bf16 | w_f32 [T*k] f32 | idx [T*k] i32 | sorted_ids [T*k + E*(block-1)] i32 |
-//   experts_ids [max_blocks] i32 | num_post_pad [1] i32 | act [T*k, I] bf16 | c2 [T*k, H] bf16
+//   experts_ids [max_blocks] i32 | num_post_pad [1] i32 | act [max_padded, I] bf16 | c2 [T*k, H] bf16 |
+//   xg [max_padded, H] bf16
+// (act holds slot-indexed rows on the mma.sync path and aligned-order rows on the tcgen05 path; xg is the
+// hidden states gathered into aligned order for the tcgen05 path.)
 size_t ub_moe_layer_q4k_workspace_bytes(int T, int H, int I, int E, int top_k, int block_size) {
   if (T <= 0 || H <= 0 || I <= 0 || E <= 0 || top_k <= 0 || block_size <= 0) return 0;
   const size_t slots = static_cast<size_t>(T) * top_k;
@@ -297,8 +309,9 @@ size_t ub_moe_layer_q4k_workspace_bytes(int T, int H, int I, int E, int top_k, i
   b += align_up(max_padded * 4, 256);
   b += align_up((max_padded / block_size + 1) * 4, 256);
   b += 256;
-  b += align_up(slots * I * 2, 256);
+  b += align_up(max_padded * I * 2, 256);
   b += align_up(slots * H * 2, 256);
+  b += align_up(max_padded * H * 2, 256);
   return b;
 }
 
@@ -323,14 +336,37 @@ int ub_moe_layer_q4k(void* out, const void* hidden, const void* router_logits, c
   int32_t* sorted_ids = reinterpret_cast<int32_t*>(p); p += align_up(max_padded * 4, 256);
   int32_t* experts_ids = reinterpret_cast<int32_t*>(p); p += align_up((max_padded / block_size + 1) * 4, 256);
   int32_t* npp = reinterpret_cast<int32_t*>(p); p += 256;
-  __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p); p += align_up(slots * I * 2, 256);
-  __nv_bfloat16* c2 = reinterpret_cast<__nv_bfloat16*>(p);
+  __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p); p += align_up(max_padded * I * 2, 256);
+  __nv_bfloat16* c2 = reinterpret_cast<__nv_bfloat16*>(p); p += align_up(slots * H * 2, 256);
+  __nv_bfloat16* xg = reinterpret_cast<__nv_bfloat16*>(p);
 
   int st = ub::topk_softmax_bf16_impl(router_logits, w_t, idx, T, E, top_k, norm_topk_prob != 0, s);
   if (st != UB_OK) return st;
   bf16_to_f32_kernel<<<static_cast<int>((slots + 255) / 256), 256, 0, s>>>(w_f32, w_t, static_cast<int>(slots));
   st = ub::moe_align(sorted_ids, experts_ids, npp, idx, nullptr, expert_map, E, block_size, T, top_k, s);
   if (st != UB_OK) return st;
+  const int positions = static_cast<int>(max_padded);
+  if (ub::q4k_moe_tc_supported(positions, H, I, block_size) && ub::q4k_moe_tc_supported(positions, I, H, block_size) &&
+      (reinterpret_cast<uintptr_t>(w13q) & 15) == 0 && (reinterpret_cast<uintptr_t>(w2q) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(hidden) & 15) == 0) {
+    // tcgen05 path: gather the tokens into aligned order once, keep the SiLU.up activations in that order
+    st = ub::moe_gather_rows(xg, hidden, sorted_ids, npp, positions, static_cast<int>(slots), top_k, H, s);
+    if (st != UB_OK) return st;
+    st = ub::q4k_moe_gemm_tc(act, xg, w13q, nullptr, sorted_ids, experts_ids, npp, positions, H, I, E,
+                             static_cast<int>(slots), block_size, 1, s);
+    if (st != UB_OK) return ub::fail(st);
+    if (expert_map) {  // slots of experts held elsewhere contribute zeros
+      cudaError_t ce = cudaMemsetAsync(c2, 0, slots * H * 2, s);
+      if (ce != cudaSuccess) {
+        ub::set_cuda_error(ce);
+        return ub::fail(UB_ERR_CUDA);
+      }
+    }
+    st = ub::q4k_moe_gemm_tc(c2, act, w2q, w_f32, sorted_ids, experts_ids, npp, positions, I, H, E,
+                             static_cast<int>(slots), block_size, 0, s);
+    if (st != UB_OK) return ub::fail(st);
+    return ub_topk_sum(out, c2, T, top_k, H, UB_DTYPE_BF16, stream);
+  }
   st = ub_fused_moe_q4k_gemm(act, hidden, w13q, nullptr, sorted_ids, experts_ids, npp, T, H, 2 * I, E,
                              static_cast<int>(slots), top_k, block_size, 0, 1, nullptr, 0, stream);
   if (st != UB_OK) return st;

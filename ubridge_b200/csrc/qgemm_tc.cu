@@ -141,21 +141,46 @@ constexpr int kTcMaxStages = 8;
 constexpr int kTcWStages = 3;                        // ring of packed weight tiles (one super-block column each)
 constexpr uint32_t kTcWBytes = 128 * UB_Q4K_BYTES;   // 128 rows x 144 bytes
 
+constexpr int kTcMaxRuns = 256;  // token runs (consecutive alignment blocks of one expert) a grouped launch handles
+
+// Grouped (MoE) launch: rows of A are in aligned order (position i holds the token of sorted_ids[i]).
+struct TcGroup {
+  const int32_t* experts_ids;   // [blocks] expert of each alignment block, -1 = not on this rank
+  const int32_t* num_post_pad;  // [1] padded number of positions
+  const int32_t* sorted_ids;    // [positions] slot id (token * top_k + j) or a padding value >= num_valid
+  const float* topk_w;          // [num_valid] routed weights (mode 2, may be null)
+  int block;                    // alignment block size (multiple of 16, <= TOK)
+  int num_valid;                // T * top_k
+  int rows_per_expert;          // weight rows per expert in the packed tensor (2 I for mode 1, N for mode 2)
+};
+
+struct TcRun {
+  int e, m0, len;
+};
+
 struct TcShared {
   unsigned long long full[kTcMaxStages], empty[kTcMaxStages], tmem_full[2], tmem_empty[2];
   unsigned long long wfull[kTcWStages], wempty[kTcWStages];
   uint32_t tmem_base;
   int abort_flag;
+  int nruns;
 };
 
 // TOK: tokens per tile (UMMA N): 64, 128 or 256.  STAGES: ring depth (token tiles in shared memory and
 // weight stages in tensor memory advance together).
-template <int TOK, int STAGES>
+// MODE 0: dense y[M,N].  MODE 1 (grouped): weight tile = 64 gate rows + the 64 matching up rows of the run's
+// expert, output act[position, N] = silu(gate) * up.  MODE 2 (grouped): output row sorted_ids[position],
+// multiplied by the routed weight.  In the grouped modes M is the number of positions of A.
+template <int TOK, int STAGES, int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1)
-qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ wq, int M, int N, int K, int* err_word,
-                    const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map) {
+qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err_word,
+                    const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+                    const TcGroup grp) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   __shared__ TcShared sh;
+  __shared__ TcRun runs[MODE == 0 ? 1 : kTcMaxRuns];
+  __shared__ float run_w[MODE == 2 ? TOK : 1];
+  __shared__ int run_dst[MODE == 2 ? TOK : 1];
   static_assert(STAGES <= kTcMaxStages, "barrier arrays");
   constexpr uint32_t kBBytes = TOK * 128;              // TOK token rows x 64 bf16
   constexpr int kStageTok = TOK < 128 ? TOK : 128;     // tokens the output staging tile holds
@@ -178,9 +203,48 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
   auto wempty_bar = [&](int b) { return bars + 16u * kTcMaxStages + 32u + 8u * kTcWStages + 8u * b; };
   volatile int* abort_flag = &sh.abort_flag;
 
-  const int w_tiles = (N + 127) / 128, t_tiles = (M + TOK - 1) / TOK;
-  const int ntiles = w_tiles * t_tiles;
+  constexpr int kTileCols = MODE == 1 ? 64 : 128;  // output columns per tile
+  const int w_tiles = (N + kTileCols - 1) / kTileCols, t_tiles = (M + TOK - 1) / TOK;
   const int ksteps = K / kTcBK;
+
+  if (MODE != 0) {
+    // Token runs: consecutive alignment blocks of one expert, merged up to TOK tokens.  Every CTA builds
+    // the same table (expert ids staged through the output staging tile, then one thread scans them).
+    int* ids = reinterpret_cast<int*>(tiles + kStagingOff);
+    const int padded = *grp.num_post_pad;
+    int nblocks = padded > 0 ? (padded + grp.block - 1) / grp.block : 0;
+    if (nblocks > kTcMaxRuns) nblocks = kTcMaxRuns;  // the launcher guarantees this never cuts
+    for (int i = threadIdx.x; i < nblocks; i += kTcThreads) ids[i] = grp.experts_ids[i];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int n = 0;
+      for (int b = 0; b < nblocks; b++) {
+        const int e = ids[b];
+        if (e < 0) continue;
+        if (n > 0 && runs[n - 1].e == e && runs[n - 1].m0 + runs[n - 1].len == b * grp.block &&
+            runs[n - 1].len + grp.block <= TOK) {
+          runs[n - 1].len += grp.block;
+        } else {
+          runs[n].e = e, runs[n].m0 = b * grp.block, runs[n].len = grp.block;
+          n++;
+        }
+      }
+      sh.nruns = n;
+    }
+    __syncthreads();
+  }
+  const int ntiles = MODE == 0 ? w_tiles * t_tiles : sh.nruns * w_tiles;
+  // tile -> (first token row of A, valid tokens, first weight row in the packed tensor, first output column)
+  auto tile_info = [&](int tile, int& m0, int& valid, int& wrow0, int& n0) {
+    if (MODE == 0) {
+      const int wt = tile / t_tiles, tt = tile - wt * t_tiles;
+      m0 = tt * TOK, valid = min(TOK, M - m0), wrow0 = wt * 128, n0 = wt * 128;
+    } else {
+      const int run = tile / w_tiles, wt = tile - run * w_tiles;
+      const TcRun r = runs[run];
+      m0 = r.m0, valid = r.len, n0 = wt * kTileCols, wrow0 = r.e * grp.rows_per_expert + n0;
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -217,9 +281,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
       int buf = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int tt = tile % t_tiles;
+        int m0_, valid, wrow0_, n0_;
+        tile_info(tile, m0_, valid, wrow0_, n0_);
         // UMMA N = the tile's valid tokens rounded up to 16 (a ragged last tile costs less)
-        const int valid = M - tt * TOK;
         const uint32_t n_mma = valid >= TOK ? TOK : static_cast<uint32_t>((valid + 15) & ~15);
         // instruction descriptor: D = f32, A = B = bf16, both K-major, N = n_mma, M = 128
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((n_mma >> 3) << 17) | (8u << 24);
@@ -260,9 +324,17 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
     int buf = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      const int wt = tile / t_tiles, tt = tile - wt * t_tiles;
-      const int n0 = wt * 128, m0 = tt * TOK;
-      const int valid = min(TOK, M - m0);
+      int m0, valid, wrow0_, n0;
+      tile_info(tile, m0, valid, wrow0_, n0);
+      if (MODE == 2) {
+        // destination row and routed weight of every token of the run (visible after the barrier below)
+        for (int tk = threadIdx.x - 32; tk < valid; tk += 128) {
+          const int sid = grp.sorted_ids[m0 + tk];
+          const bool live = sid >= 0 && sid < grp.num_valid;
+          run_dst[tk] = live ? sid : -1;
+          run_w[tk] = live ? (grp.topk_w ? grp.topk_w[sid] : 1.f) : 0.f;
+        }
+      }
       {
         // all four epilogue warps take the same decision, so nobody is left alone at the named barrier
         const uint32_t mine = tc_wait(tfull_bar(buf), acc_phase, abort_flag) ? 1u : 0u;
@@ -290,26 +362,52 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
                         c0 + c, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int j = 0; j < 32; j++) st_col[(c + j) * 128] = __float2bfloat16_rn(__uint_as_float(v[j]));
+          for (int j = 0; j < 32; j++) {
+            float f = __uint_as_float(v[j]);
+            if (MODE == 2) f *= run_w[c0 + c + j];
+            st_col[(c + j) * 128] = __float2bfloat16_rn(f);
+          }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: staging complete
         // after the last part the next tile's MMAs may overwrite the accumulator
         if (c0 + kStageTok >= valid && lane == 0) tc_mbar_arrive(tempty_bar(buf));
-        if (vec_ok) {
+        if (MODE == 1) {
+          // staging row = 64 gate values then 64 up values of one position: eight lanes per position
+          const int ch = lane & 7;
+          const bool n_in = n0 + 8 * ch < N;
+          for (int t = 4 * ew + (lane >> 3); t < part; t += 16) {
+            const uint4 gv = *reinterpret_cast<const uint4*>(staging + t * 256 + ch * 16);
+            const uint4 uv = *reinterpret_cast<const uint4*>(staging + t * 256 + 128 + ch * 16);
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              const float g0 = __uint_as_float(gw[i] << 16), g1 = __uint_as_float(gw[i] & 0xFFFF0000u);
+              const float u0 = __uint_as_float(uw[i] << 16), u1 = __uint_as_float(uw[i] & 0xFFFF0000u);
+              const __nv_bfloat162 o2 =
+                  __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+              ow[i] = bf162_bits(o2);
+            }
+            if (n_in)
+              *reinterpret_cast<uint4*>(y + static_cast<size_t>(m0 + c0 + t) * N + n0 + 8 * ch) =
+                  make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          }
+        } else if (vec_ok) {
           const int ch = lane & 15;
           const bool n_in = n0 + 8 * ch < N;
           for (int t = 2 * ew + (lane >> 4); t < part; t += 8) {
             const uint4 val = *reinterpret_cast<const uint4*>(staging + t * 256 + ch * 16);
-            if (n_in) *reinterpret_cast<uint4*>(y + static_cast<size_t>(m0 + c0 + t) * N + n0 + 8 * ch) = val;
+            const int row = MODE == 2 ? run_dst[c0 + t] : m0 + c0 + t;
+            if (n_in && row >= 0) *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * N + n0 + 8 * ch) = val;
           }
         } else {
           for (int t = ew; t < part; t += 4) {
+            const int row = MODE == 2 ? run_dst[c0 + t] : m0 + c0 + t;
 #pragma unroll
             for (int r = lane; r < 128; r += 32)
-              if (n0 + r < N)
-                y[static_cast<size_t>(m0 + c0 + t) * N + n0 + r] =
-                    reinterpret_cast<const __nv_bfloat16*>(staging)[t * 128 + r];
+              if (n0 + r < N && row >= 0)
+                y[static_cast<size_t>(row) * N + n0 + r] = reinterpret_cast<const __nv_bfloat16*>(staging)[t * 128 + r];
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // staging may be overwritten
@@ -413,7 +511,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
       int wq_next = 0;  // next super-block (flat index) whose packed weights have not been requested
       auto issue_w = [&]() {
         const int ti = wq_next / nsb, sb = wq_next - ti * nsb;
-        const int n0 = ((blockIdx.x + ti * gridDim.x) / t_tiles) * 128;
+        int m0_, valid_, wrow0, n0_;
+        tile_info(blockIdx.x + ti * gridDim.x, m0_, valid_, wrow0, n0_);
         ok = tc_wait(wempty_bar(ws), wphase ^ 1, abort_flag);
         if (!ok) return;
         const uint32_t bar = wfull_bar(ws);
@@ -421,8 +520,14 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
                 "r"(smem_base + kWOff + ws * kTcWBytes),
-            "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * UB_Q4K_BYTES), "r"(n0)
+            "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * UB_Q4K_BYTES), "r"(wrow0)
             : "memory");
+        if (MODE == 1)  // second half of the tile: the up rows matching the 64 gate rows (box = 64 rows)
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+                  "r"(smem_base + kWOff + ws * kTcWBytes + kTcWBytes / 2),
+              "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * UB_Q4K_BYTES), "r"(wrow0 + N)
+              : "memory");
         wq_next++;
         if (++ws == kTcWStages) {
           ws = 0;
@@ -434,7 +539,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ w
         if (wq_next < total_sb) issue_w();
         if (!ok) break;
         const int ti = q / nsb, sb = q - ti * nsb;
-        const int m0 = ((blockIdx.x + ti * gridDim.x) % t_tiles) * TOK;
+        int m0, valid_, wrow0_, n0_;
+        tile_info(blockIdx.x + ti * gridDim.x, m0, valid_, wrow0_, n0_);
         for (int G = 0; G < 4; G++) {
           ok = tc_wait(empty_bar(s), phase ^ 1, abort_flag);
           if (!ok) break;
@@ -484,13 +590,17 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int TOK, int STAGES>
-int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
+template <int TOK, int STAGES, int MODE>
+int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const TcGroup& grp, int w_rows_total,
+              cudaStream_t s) {
   const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(TOK < 128 ? TOK : 128) * 256 +
                       static_cast<size_t>(kTcWStages) * kTcWBytes + 1024;
-  const int tiles = ((N + 127) / 128) * ((M + TOK - 1) / TOK);
   const int sms = ub::num_sms();
-  const int grid = tiles < sms ? tiles : sms;
+  int grid = sms;  // grouped launches learn their tile count on the device; idle CTAs leave at once
+  if (MODE == 0) {
+    const int tiles = ((N + 127) / 128) * ((M + TOK - 1) / TOK);
+    grid = tiles < sms ? tiles : sms;
+  }
   // token matrix as a 2-D tensor map: inner dimension K (bf16), outer M; box = 64 x TOK, 128-byte swizzle;
   // rows beyond M read as zeros
   CUtensorMap map;
@@ -504,26 +614,42 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaS
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ub::fail(UB_ERR_UNSUPPORTED);
-  // packed weights as a 2-D byte tensor: inner dimension = one row's bytes, outer = N rows; box = one
-  // super-block (144 bytes) of 128 rows, no swizzle; rows beyond N read as zeros
+  // packed weights as a 2-D byte tensor: inner dimension = one row's bytes, outer = all weight rows (of all
+  // experts); box = one super-block (144 bytes) of 128 rows (64 for the gate/up halves of mode 1), no
+  // swizzle; rows beyond the tensor read as zeros
   CUtensorMap wmap;
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(K / UB_QK_K) * UB_Q4K_BYTES;
-  const cuuint64_t wdims[2] = {row_bytes, static_cast<cuuint64_t>(N)};
+  const cuuint64_t wdims[2] = {row_bytes, static_cast<cuuint64_t>(w_rows_total)};
   const cuuint64_t wstrides[1] = {row_bytes};
-  const cuuint32_t wbox[2] = {UB_Q4K_BYTES, 128};
+  const cuuint32_t wbox[2] = {UB_Q4K_BYTES, MODE == 1 ? 64u : 128u};
   if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(wq), wdims, wstrides, wbox, estr,
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ub::fail(UB_ERR_UNSUPPORTED);
-  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES>;
+  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
   }
-  kernel<<<grid, kTcThreads, smem, s>>>(static_cast<__nv_bfloat16*>(y), static_cast<const uint8_t*>(wq), M, N, K,
-                                        ub::device_error_word(), map, wmap);
+  kernel<<<grid, kTcThreads, smem, s>>>(static_cast<__nv_bfloat16*>(y), M, N, K, ub::device_error_word(), map, wmap,
+                                        grp);
   return ub::check_launch();
+}
+
+// xg[i, :] = hidden[sorted_ids[i] / top_k, :] for the positions the alignment produced (zeros for padding)
+__global__ void __launch_bounds__(256) moe_gather_rows_kernel(__nv_bfloat16* __restrict__ xg,
+                                                              const __nv_bfloat16* __restrict__ hidden,
+                                                              const int32_t* __restrict__ sorted_ids,
+                                                              const int32_t* __restrict__ num_post_pad, int num_valid,
+                                                              int top_k, int H) {
+  const int i = blockIdx.x;
+  if (i >= *num_post_pad) return;
+  const int sid = sorted_ids[i];
+  const bool live = sid >= 0 && sid < num_valid;
+  const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(live ? sid / top_k : 0) * H);
+  uint4* dst = reinterpret_cast<uint4*>(xg + static_cast<size_t>(i) * H);
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = live ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
 }
 
 }  // namespace
@@ -533,9 +659,46 @@ namespace ub {
 // y (bf16) [M,N] = x (bf16) [M,K] . dequant(Wq)^T on tcgen05; K % 256 == 0, pointers 16-byte aligned.
 // Returns UB_ERR_UNSUPPORTED when the driver offers no tensor-map encoder (the caller falls back).
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
-  if (M <= 64) return launch_tc<64, 6>(y, x, wq, M, N, K, s);
-  if (M <= 128) return launch_tc<128, 6>(y, x, wq, M, N, K, s);
-  return launch_tc<256, 4>(y, x, wq, M, N, K, s);
+  const TcGroup none = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
+  if (M <= 64) return launch_tc<64, 6, 0>(y, x, wq, M, N, K, none, N, s);
+  if (M <= 128) return launch_tc<128, 6, 0>(y, x, wq, M, N, K, none, N, s);
+  return launch_tc<256, 4, 0>(y, x, wq, M, N, K, none, N, s);
+}
+
+// Limits of the grouped tcgen05 path; outside them the caller keeps the mma.sync kernels.
+bool q4k_moe_tc_supported(int positions, int K, int N, int block) {
+  return encode_tiled_fn() != nullptr && block > 0 && block % 16 == 0 && block <= 128 && K % UB_QK_K == 0 &&
+         N % 8 == 0 && (positions + block - 1) / block <= kTcMaxRuns;
+}
+
+// Gathers hidden rows into aligned order: xg[positions, H].
+int moe_gather_rows(void* xg, const void* hidden, const int32_t* sorted_ids, const int32_t* num_post_pad, int positions,
+                    int num_valid, int top_k, int H, cudaStream_t s) {
+  if (positions <= 0) return UB_OK;
+  moe_gather_rows_kernel<<<positions, 256, 0, s>>>(static_cast<__nv_bfloat16*>(xg),
+                                                   static_cast<const __nv_bfloat16*>(hidden), sorted_ids, num_post_pad,
+                                                   num_valid, top_k, H);
+  return ub::check_launch();
+}
+
+// Grouped expert GEMM over rows in aligned order (A[positions, K] bf16).
+//   act_silu_mul != 0: Bq = [E][2N rows: gate then up][K], C[position, N] = silu(gate) * up
+//   else:              Bq = [E][N rows][K], C[sorted_ids[position], N] = (A . W^T) * topk_w[slot]
+int q4k_moe_gemm_tc(void* C, const void* A, const void* Bq, const float* topk_w, const int32_t* sorted_ids,
+                    const int32_t* experts_ids, const int32_t* num_post_pad, int positions, int K, int N, int E,
+                    int num_valid, int block, int act_silu_mul, cudaStream_t s) {
+  if (!q4k_moe_tc_supported(positions, K, N, block)) return UB_ERR_UNSUPPORTED;
+  TcGroup g;
+  g.experts_ids = experts_ids, g.num_post_pad = num_post_pad, g.sorted_ids = sorted_ids, g.topk_w = topk_w;
+  g.block = block, g.num_valid = num_valid, g.rows_per_expert = act_silu_mul ? 2 * N : N;
+  const int rows_total = E * g.rows_per_expert;
+  // token runs are capped at the tile's token count: short runs (few tokens per expert) take the 128 tile
+  const bool small = num_valid / (E > 0 ? E : 1) <= 128;
+  if (act_silu_mul)
+    return small ? launch_tc<128, 6, 1>(C, A, Bq, positions, N, K, g, rows_total, s)
+                 : launch_tc<256, 4, 1>(C, A, Bq, positions, N, K, g, rows_total, s);
+  return small ? launch_tc<128, 6, 2>(C, A, Bq, positions, N, K, g, rows_total, s)
+               : launch_tc<256, 4, 2>(C, A, Bq, positions, N, K, g, rows_total, s);
 }
 
 }  // namespace ub

@@ -130,6 +130,9 @@ class TPLinearStack:
         self.ws_bytes = max(ops.qmatmul_workspace_bytes(max_m, n, k, True) for n, k in shapes)
         self.ws = dev.alloc(max(self.ws_bytes, 256))
 
+    # kernels of this library per forward(): four matmuls (one launch each for M <= 8 or M > 16) + SiLU.up
+    launches_per_forward = 5
+
     def _mm(self, y, x, w, M, N, K):
         ops.qmatmul(y, x, w, M, N, K, is_q4k=True, x_dtype=DTYPE_BF16, out_dtype=DTYPE_BF16, workspace=self.ws,
                     ws_bytes=self.ws_bytes, stream=self.dev.stream)
@@ -175,6 +178,9 @@ class EPMoELayer:
         self.ws_bytes = ops.moe_layer_q4k_workspace_bytes(T, H, I, E, top_k, block)
         self.ws = dev.alloc(self.ws_bytes)
         self.out = dev.alloc(T * H * 2)
+
+    # kernels per forward(): router, weight conversion, alignment, two grouped GEMMs, top-k sum
+    launches_per_forward = 6
 
     def forward(self, hidden, logits, norm_topk_prob: bool = True):
         ops.moe_layer_q4k(self.out, hidden, logits, self.w13, self.w2, self.T, self.H, self.I, self.E, self.top_k,
