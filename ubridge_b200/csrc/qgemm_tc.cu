@@ -41,8 +41,11 @@ namespace {
 
 using namespace ub;
 
-constexpr int kTcThreads = 14 * 32;
-constexpr int kTcProducerWarps = 8;
+constexpr int kTcProducerWarps = 8;   // warps that dequantise one K step (128 rows x 2 nibble halves)
+// Sets of such warps; set i takes the K steps with step % sets == i.  Measured on B200: a second set does
+// not help (C3 204 us against 191 us with one), the producers are not bound by their own latency chain.
+constexpr int kTcProducerSets = 1;
+constexpr int kTcThreads = (5 + kTcProducerWarps * kTcProducerSets + 1) * 32;
 constexpr int kTcBK = 64;
 constexpr uint32_t kTcWaitLimit = 2000000;
 
@@ -138,7 +141,11 @@ __device__ __forceinline__ uint32_t deq_pair(uint32_t w4, __nv_bfloat162 dsc, __
 }
 
 constexpr int kTcMaxStages = 8;
-constexpr int kTcWStages = 3;                        // ring of packed weight tiles (one super-block column each)
+constexpr int kTcWStages = 3;                        // most slots a ring of packed weight tiles has
+// Shared-memory plan per token-tile size: the 256-token tile spends its memory on token stages (the
+// copies' latency, not their bandwidth, bounds a K step) and keeps the other two areas small.
+constexpr int tc_wstages(int tok) { return tok > 128 ? 2 : 3; }      // slots of the packed weight ring
+constexpr int tc_stage_tok(int tok) { return tok > 128 ? 64 : (tok < 128 ? tok : 128); }  // staging rows
 constexpr uint32_t kTcWBytes = 128 * UB_Q4K_BYTES;   // 128 rows x 144 bytes
 
 constexpr int kTcMaxRuns = 256;  // token runs (consecutive alignment blocks of one expert) a grouped launch handles
@@ -183,7 +190,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   __shared__ int run_dst[MODE == 2 ? TOK : 1];
   static_assert(STAGES <= kTcMaxStages, "barrier arrays");
   constexpr uint32_t kBBytes = TOK * 128;              // TOK token rows x 64 bf16
-  constexpr int kStageTok = TOK < 128 ? TOK : 128;     // tokens the output staging tile holds
+  constexpr int kStageTok = tc_stage_tok(TOK);         // tokens the output staging tile holds
+  constexpr int kWStages = tc_wstages(TOK);
   constexpr uint32_t kStagingOff = STAGES * kBBytes;   // [kStageTok tokens][128 weight rows] bf16
   constexpr uint32_t kWOff = kStagingOff + kStageTok * 256;  // packed weight ring: [128 rows][144 bytes] each
   constexpr int kAccBufs = TOK > 128 ? 1 : 2;          // accumulator buffers in TMEM columns 0..255
@@ -255,9 +263,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
       tc_mbar_init(tfull_bar(b), 1);
       tc_mbar_init(tempty_bar(b), 4);
     }
-    for (int b = 0; b < kTcWStages; b++) {
+    for (int b = 0; b < kWStages; b++) {
       tc_mbar_init(wfull_bar(b), 1);
-      tc_mbar_init(wempty_bar(b), kTcProducerWarps);
+      tc_mbar_init(wempty_bar(b), kTcProducerWarps * kTcProducerSets);
     }
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -417,24 +425,24 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
         acc_phase ^= 1;
       }
     }
-  } else if (warp <= 4 + kTcProducerWarps) {
-    // ------------------------------------------------------------ weight producers (256 threads)
-    // One flat loop over (tile, super-block), four K steps (the super-block's four 64-value groups) per
-    // iteration.  Packed weights arrive in shared memory as [128 rows][144 bytes] per super-block; a
-    // thread owns one weight row (= its TMEM lane) and one nibble half and reads its row's header and
-    // 32-byte pieces from there (rows are 144 bytes apart, so a quarter-warp's 16-byte reads hit all
-    // 32 banks once).
-    const int p = threadIdx.x - 5 * 32;  // 0..255
+  } else if (warp <= 4 + kTcProducerWarps * kTcProducerSets) {
+    // ------------------------------------------------------------ weight producers (256 threads per set)
+    // One flat loop over (tile, super-block); the super-block's four K steps (its four 64-value groups) are
+    // dealt round robin to the producer sets.  Packed weights arrive in shared memory as
+    // [128 rows][144 bytes] per super-block; a thread owns one weight row (= its TMEM lane) and one nibble
+    // half and reads its row's header and 32-byte pieces from there (rows are 144 bytes apart, so a
+    // quarter-warp's 16-byte reads hit all 32 banks once).
+    static_assert(STAGES % kTcProducerSets == 0, "a set must return to the same stages every ring turn");
     // weight row inside the tile = the TMEM lane this warp may access (32 * (warp % 4) + lane);
     // half: 0 = low nibbles (even sub-blocks), 1 = high nibbles
-    const int wrow = 32 * (warp & 3) + lane, half = p >> 7;
+    const int wrow = 32 * (warp & 3) + lane, half = ((warp - 5) >> 2) & 1, set = (warp - 5) >> 3;
     const int nsb = K >> 8;
     const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const int total_sb = my_tiles * nsb;  // super-block iterations
     const unsigned char* const w_ring = tiles + kWOff + wrow * UB_Q4K_BYTES;
     const uint32_t a_lane = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kATmemCol;
 
-    int s = 0;  // stage of the step being dequantised
+    int s = set;  // stage of the step being dequantised
     uint32_t phase = 0;
     int ws = 0;  // packed-weight ring slot
     uint32_t wphase = 0;
@@ -442,8 +450,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
 
     // one super-block (four K steps); HALF is a compile-time copy of `half` so that nibble selection and
     // the scale bytes' positions are immediate operands
-    auto super_block = [&](auto half_c) {
-      constexpr int HALF = decltype(half_c)::value;
+    auto super_block = [&](auto half_c, auto set_c) {
+      constexpr int HALF = decltype(half_c)::value, SET = decltype(set_c)::value;
       ok = __all_sync(0xFFFFFFFFu, tc_wait(wfull_bar(ws), wphase, abort_flag));
       if (!ok) return;
       const unsigned char* blk = w_ring + ws * kTcWBytes;
@@ -452,7 +460,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
       uint32_t scw[2], mnw[2];
       q4k_unpack_scales(hdr.y, hdr.z, hdr.w, scw[0], scw[1], mnw[0], mnw[1]);
 #pragma unroll
-      for (int G = 0; G < 4; G++) {
+      for (int Gi = 0; Gi < 4 / kTcProducerSets; Gi++) {
+        constexpr int kSets = kTcProducerSets;
+        const int G = kSets * Gi + SET;
         const int j = 2 * G + HALF;
         const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
         const __nv_bfloat162 dsc = __float2bfloat162_rn(d * static_cast<float>(sc));
@@ -479,27 +489,38 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) tc_mbar_arrive(full_bar(s));
-        if (++s == STAGES) {
-          s = 0;
+        s += kTcProducerSets;
+        if (s >= STAGES) {
+          s -= STAGES;
           phase ^= 1;
         }
       }
       __syncwarp();
       if (lane == 0) tc_mbar_arrive(wempty_bar(ws));  // this warp has read all it needs from the slot
-      if (++ws == kTcWStages) {
+      if (++ws == kWStages) {
         ws = 0;
         wphase ^= 1;
       }
     };
-    if (half) {
-      for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 1>{});
+    using I0 = std::integral_constant<int, 0>;
+    using I1 = std::integral_constant<int, 1>;
+    if (set == 0) {
+      if (half) {
+        for (int q = 0; q < total_sb && ok; q++) super_block(I1{}, I0{});
+      } else {
+        for (int q = 0; q < total_sb && ok; q++) super_block(I0{}, I0{});
+      }
     } else {
-      for (int q = 0; q < total_sb && ok; q++) super_block(std::integral_constant<int, 0>{});
+      if (half) {
+        for (int q = 0; q < total_sb && ok; q++) super_block(I1{}, I1{});
+      } else {
+        for (int q = 0; q < total_sb && ok; q++) super_block(I0{}, I1{});
+      }
     }
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
   } else {
     // ------------------------------------------------------------ bulk copies (one lane)
-    // Packed weight tiles run kTcWStages - 1 super-blocks ahead of the token tiles; token tiles run as far
+    // Packed weight tiles run kWStages - 1 super-blocks ahead of the token tiles; token tiles run as far
     // ahead of the MMA as the ring allows.
     if (lane == 0) {
       const int nsb = K >> 8;
@@ -529,12 +550,12 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
               "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * UB_Q4K_BYTES), "r"(wrow0 + N)
               : "memory");
         wq_next++;
-        if (++ws == kTcWStages) {
+        if (++ws == kWStages) {
           ws = 0;
           wphase ^= 1;
         }
       };
-      for (int i = 0; i < kTcWStages - 1 && wq_next < total_sb && ok; i++) issue_w();
+      for (int i = 0; i < kWStages - 1 && wq_next < total_sb && ok; i++) issue_w();
       for (int q = 0; q < total_sb && ok; q++) {
         if (wq_next < total_sb) issue_w();
         if (!ok) break;
@@ -593,8 +614,8 @@ EncodeTiledFn encode_tiled_fn() {
 template <int TOK, int STAGES, int MODE>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const TcGroup& grp, int w_rows_total,
               cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(TOK < 128 ? TOK : 128) * 256 +
-                      static_cast<size_t>(kTcWStages) * kTcWBytes + 1024;
+  const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(tc_stage_tok(TOK)) * 256 +
+                      static_cast<size_t>(tc_wstages(TOK)) * kTcWBytes + 1024;
   const int sms = ub::num_sms();
   int grid = sms;  // grouped launches learn their tile count on the device; idle CTAs leave at once
   if (MODE == 0) {
@@ -662,7 +683,7 @@ int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cud
   const TcGroup none = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
   if (M <= 64) return launch_tc<64, 6, 0>(y, x, wq, M, N, K, none, N, s);
   if (M <= 128) return launch_tc<128, 6, 0>(y, x, wq, M, N, K, none, N, s);
-  return launch_tc<256, 4, 0>(y, x, wq, M, N, K, none, N, s);
+  return launch_tc<256, 5, 0>(y, x, wq, M, N, K, none, N, s);
 }
 
 // Limits of the grouped tcgen05 path; outside them the caller keeps the mma.sync kernels.
@@ -696,9 +717,9 @@ int q4k_moe_gemm_tc(void* C, const void* A, const void* Bq, const float* topk_w,
   const bool small = num_valid / (E > 0 ? E : 1) <= 128;
   if (act_silu_mul)
     return small ? launch_tc<128, 6, 1>(C, A, Bq, positions, N, K, g, rows_total, s)
-                 : launch_tc<256, 4, 1>(C, A, Bq, positions, N, K, g, rows_total, s);
+                 : launch_tc<256, 5, 1>(C, A, Bq, positions, N, K, g, rows_total, s);
   return small ? launch_tc<128, 6, 2>(C, A, Bq, positions, N, K, g, rows_total, s)
-               : launch_tc<256, 4, 2>(C, A, Bq, positions, N, K, g, rows_total, s);
+               : launch_tc<256, 5, 2>(C, A, Bq, positions, N, K, g, rows_total, s);
 }
 
 }  // namespace ub
