@@ -111,6 +111,38 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+# ----------------------------------------------------------------------------- rank rendezvous
+class Control:
+    """Host-side rendezvous of the ranks over a CPU (gloo) group: barriers, max-over-ranks of timings and
+    the hand-over of the collective library's unique id.  The data path's collectives are NCCL, through
+    the eccl entry points; keeping the control plane off the GPU means no second NCCL communicator shares
+    the device with them."""
+
+    def __init__(self, torch, dist, world: int):
+        self.torch, self.dist, self.world = torch, dist, world
+        self.group = dist.new_group(backend="gloo") if world > 1 else None
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier(group=self.group)
+
+    def max(self, value: float) -> float:
+        if self.world == 1:
+            return value
+        t = self.torch.tensor([value], dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX, group=self.group)
+        return float(t.item())
+
+    def broadcast(self, obj):
+        box = [obj]
+        if self.world > 1:
+            self.dist.broadcast_object_list(box, src=0, group=self.group)
+        return box[0]
+
+
+CTL = None  # set by main()
+
+
 # ----------------------------------------------------------------------------- CPU arm
 class CpuArm:
     """The CPU restatement (oracle/ub_oracle.c, OpenMP over weight rows) on this workload's matrix:
@@ -237,8 +269,7 @@ def run_linear(args, wl, rank, world, torch, dist):
         for _ in range(args.warmup):
             graph.replay()
         stream.synchronize()
-        if world > 1:
-            dist.barrier()
+        CTL.barrier()
         torch.cuda.synchronize()
         sampler = ClockSampler(dev_index)
         if rank == 0:
@@ -252,10 +283,7 @@ def run_linear(args, wl, rank, world, torch, dist):
         torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else None
     ms_total = ev0.elapsed_time(ev1)
-    if world > 1:
-        t = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    ms_total = CTL.max(ms_total)
     ms_step = ms_total / args.steps
 
     # Q8_0 decode kernel: M rows are processed 4/2/1 at a time, one launch each
@@ -306,16 +334,12 @@ def run_linear(args, wl, rank, world, torch, dist):
 
         for _ in range(max(3, args.warmup)):
             e2e_step()
-        if world > 1:
-            dist.barrier()
+        CTL.barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             e2e_step()
         el = time.perf_counter() - t0
-        if world > 1:
-            t = torch.tensor([el], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            el = float(t.item())
+        el = CTL.max(el)
         s_step = el / args.steps
         ev = calls * w_bytes / s_step / 1e9 if wl["unit"] == "GB/s" else calls * 2.0 * M * N * K / s_step / 1e12
         e2e = {"value": ev, "unit": wl["unit"], "h2d_bytes_per_step": int(host_x.numel()),
@@ -358,10 +382,17 @@ def run_sharded(args, wl, rank, world, torch, dist):
     dev.bind_to_thread()
     ext = torch.cuda.ExternalStream(dev.stream.value)
     comm, all_reduce = None, None
+
+    def note(msg):
+        if os.environ.get("UB_BENCH_VERBOSE"):
+            print("[rank %d] %s" % (rank, msg), file=sys.stderr, flush=True)
+
     if world > 1:
-        box = [eccl.Id().internal() if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        comm = eccl.Comm.from_rank(rank, world, eccl.Id(box[0]))
+        # the 128-byte unique id travels out of band (the CPU group), as it does in the reference
+        uid = CTL.broadcast(eccl.Id().internal() if rank == 0 else None)
+        note("unique id exchanged")
+        comm = eccl.Comm.from_rank(rank, world, eccl.Id(uid))
+        note("communicator ready")
 
         def all_reduce(buf, count):
             comm.all_reduce(buf, buf, count, eccl.Bfloat16, eccl.ReduceOp.Sum, stream=dev.stream)
@@ -409,22 +440,35 @@ def run_sharded(args, wl, rank, world, torch, dist):
     def forward(layer):
         return layer.forward(d_x, wl["M"]) if kind == "tp" else layer.forward(d_x, d_logits)
 
-    # one eager pass per copy (resolves symbols, sets attributes), then one graph per copy
+    # one eager pass per copy (resolves symbols, sets attributes), then one CUDA graph per copy; with several
+    # GPUs the graphs contain the NCCL all-reduces
+    note("weights resident, %d copies" % ncopies)
     for layer in layers:
         forward(layer)
     dev.synchronize()
+    note("eager pass done")
+    use_graph = True
     graphs = []
     with torch.cuda.stream(ext):
-        for layer in layers:
-            g_ = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_, stream=ext):
-                forward(layer)
-            graphs.append(g_)
+        if use_graph:
+            for layer in layers:
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=ext, capture_error_mode="thread_local"):
+                    forward(layer)
+                graphs.append(g_)
+            note("graphs captured")
+
+        def step(i):
+            if use_graph:
+                graphs[i % ncopies].replay()
+            else:
+                forward(layers[i % ncopies])
+
         for i in range(args.warmup):
-            graphs[i % ncopies].replay()
+            step(i)
         ext.synchronize()
-        if world > 1:
-            dist.barrier()
+        note("warm-up done")
+        CTL.barrier()
         torch.cuda.synchronize()
         sampler = ClockSampler(dev_index)
         if rank == 0:
@@ -432,16 +476,14 @@ def run_sharded(args, wl, rank, world, torch, dist):
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(ext)
         for i in range(args.steps):
-            graphs[i % ncopies].replay()
+            step(i)
         ev1.record(ext)
         ext.synchronize()
         torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else None
     ms_total = ev0.elapsed_time(ev1)
-    if world > 1:
-        t = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    note("timed region done: %.3f ms" % ms_total)
+    ms_total = CTL.max(ms_total)
     ms_step = ms_total / args.steps
     s_step = ms_step * 1e-3
 
@@ -458,26 +500,34 @@ def run_sharded(args, wl, rank, world, torch, dist):
     host_y = torch.empty((out_elems * 2,), dtype=torch.uint8).pin_memory()
     lib = ub.lib()
 
+    # A single GPU launches the layer eagerly through the API.  With several GPUs the step replays the
+    # captured graph between the two copies, so that host launch cost does not hide the collectives.
+    e2e_graph = world > 1
+
     def e2e_step(i):
         lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), ctypes.c_void_p(host_x.data_ptr()), host_x.numel())
-        out = forward(layers[i % ncopies])
+        if e2e_graph:
+            with torch.cuda.stream(ext):
+                graphs[i % ncopies].replay()
+            out = layers[i % ncopies].out
+        else:
+            out = forward(layers[i % ncopies])
         lib.ub_memcpy_dtoh(dev._handle, ctypes.c_void_p(host_y.data_ptr()), ctypes.c_void_p(out.ptr), host_y.numel())
         dev.synchronize()
 
+    note("end-to-end loop starts")
     for i in range(max(3, args.warmup)):
         e2e_step(i)
-    if world > 1:
-        dist.barrier()
+    note("end-to-end warm-up done")
+    CTL.barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
         e2e_step(i)
     el_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([el_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        el_s = float(t.item())
+    el_s = CTL.max(el_s)
+    note("end-to-end loop done")
     e2e = {"value": metric_value(el_s / args.steps), "unit": wl["unit"], "h2d_bytes_per_step": int(host_x.numel()),
-           "d2h_bytes_per_step": int(host_y.numel())}
+           "d2h_bytes_per_step": int(host_y.numel()), "launch_mode": "cuda graph" if e2e_graph else "eager"}
 
     peaks = measured_peaks()
     # per-GPU roofline: this rank's shard bytes (or flop) per step against one GPU's measured peak
@@ -495,10 +545,20 @@ def run_sharded(args, wl, rank, world, torch, dist):
     # kernels of ours per step: tp = 4 matmuls (+ conversions none: bf16) + copy + SiLU.up; ep = the fused layer
     launches = args.steps * layers[0].launches_per_forward
     if comm is not None:
+        # NCCL keeps a communicator alive while a CUDA graph that captured its collectives exists, and
+        # ncclCommDestroy waits for those references: release the graphs first
         dev.synchronize()
+        graphs.clear()
+        g_ = None
+        import gc
+        gc.collect()
+        CTL.barrier()
+        note("graphs released")
         comm.destroy()
+        note("communicator destroyed")
     return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
-                dtype="u4+f16 scales -> f32 accumulate", ncopies=ncopies)
+                dtype="u4+f16 scales -> f32 accumulate", ncopies=ncopies,
+                launch_mode="cuda graph" if use_graph else "eager")
 
 
 def main():
@@ -559,7 +619,11 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        # torch's own NCCL communicator is created lazily and never used: every collective of the control
+        # plane goes through the CPU group of Control
         dist.init_process_group("nccl")
+    global CTL
+    CTL = Control(torch, dist, world)
     try:
         res = (run_sharded if sharded else run_linear)(args, wl, rank, world, torch, dist)
         if rank == 0:
@@ -568,6 +632,9 @@ def main():
                 arm = CpuArm(wl)
                 v, sample = arm.run(args.cpu_seconds)
                 cpu = {"value": v, "unit": wl["unit"], "cores": arm.cores, "kind": "port", "sample": sample}
+            if "launch_mode" in res:
+                config["launch_mode"] = res["launch_mode"]
+                config["weight_copies"] = res["ncopies"]
             line = {"metric": metric, "value": res["value"], "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
                     "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
                     "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": res["dtype"],
