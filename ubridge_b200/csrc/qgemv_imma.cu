@@ -70,8 +70,7 @@ __device__ __forceinline__ void ib_copy(uint32_t dst, const void* src, uint32_t 
 
 // d += A(16x32 u8, row) . B(32x8 s8, col)
 __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
 }
@@ -151,6 +150,17 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
   const int nrows = base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
   const int nbatches = (nrows + 16 * kMT - 1) / (16 * kMT);
 
+  // the first activation piece of this warp is requested before anything else: its latency is on the
+  // critical path of the whole launch
+  float v_first[8];
+  const bool first_live = warp < kCW && warp < 2 * MP * nsb && warp / nsb < M;
+  if (first_live) {
+    ld_x8<XT>(x + static_cast<size_t>(warp / nsb) * K + (warp % nsb) * 256 + 8 * lane, v_first);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; e++) v_first[e] = 0.f;
+  }
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) {
       ib_init(bars_s + 8 * s, 1);
@@ -167,12 +177,25 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
     // ---- activations -> fragments of the B operand, once per launch ----
     for (int u = warp; u < 2 * MP * nsb; u += kCW) {
       const int m = u / nsb, sb = u - m * nsb;
+      const int p = m >> 1, cb = 4 * (m & 1);
+      const int j = lane >> 2, tt = lane & 3, G = j >> 1;
+      uint2* f1 = reinterpret_cast<uint2*>(bfrag) + ((static_cast<size_t>(p) * nsb + sb) * 4 + G) * 64;  // MMA 1
+      uint2* f2 = f1 + 32;                                                                                // MMA 2
+      if (m >= M) {
+        // a token this launch does not have: its columns multiply by zero
+        const int c0 = cb + 2 * (j & 1);
+        f1[c0 * 4 + tt] = f1[(c0 + 1) * 4 + tt] = f2[c0 * 4 + tt] = f2[(c0 + 1) * 4 + tt] = make_uint2(0, 0);
+        if (lane < 2)
+          reinterpret_cast<uint4*>(meta)[(static_cast<size_t>(p) * nsb + sb) * 4 + 2 * (m & 1) + lane] =
+              make_uint4(0, 0, 0, 0);
+        continue;
+      }
       float v[8];
-      if (m < M) {
-        ld_x8<XT>(x + static_cast<size_t>(m) * K + sb * 256 + 8 * lane, v);
-      } else {
+      if (u == warp) {
 #pragma unroll
-        for (int e = 0; e < 8; e++) v[e] = 0.f;
+        for (int e = 0; e < 8; e++) v[e] = v_first[e];
+      } else {
+        ld_x8<XT>(x + static_cast<size_t>(m) * K + sb * 256 + 8 * lane, v);
       }
       float amax = 0.f;
 #pragma unroll
@@ -195,10 +218,6 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
       const uint2 lv = make_uint2(pack4(lo[0], lo[1], lo[2], lo[3]), pack4(lo[4], lo[5], lo[6], lo[7]));
       const uint2 nhv = make_uint2(pack4(-hi[0], -hi[1], -hi[2], -hi[3]), pack4(-hi[4], -hi[5], -hi[6], -hi[7]));
       const uint2 nlv = make_uint2(pack4(-lo[0], -lo[1], -lo[2], -lo[3]), pack4(-lo[4], -lo[5], -lo[6], -lo[7]));
-      const int p = m >> 1, cb = 4 * (m & 1);
-      const int j = lane >> 2, tt = lane & 3, G = j >> 1;
-      uint2* f1 = reinterpret_cast<uint2*>(bfrag) + ((static_cast<size_t>(p) * nsb + sb) * 4 + G) * 64;  // MMA 1
-      uint2* f2 = f1 + 32;                                                                                // MMA 2
       if ((j & 1) == 0) {
         f1[(cb + 0) * 4 + tt] = hv;
         f1[(cb + 1) * 4 + tt] = lv;
@@ -228,6 +247,19 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
   }
 
   const int par = t & 1;
+  // B fragments and activation metadata of this warp's super-block: constant over the launch when K fits one
+  // chunk and there is one token pair, then kept in registers
+  const bool hoist = MP == 1 && nchunks == 1;
+  uint2 bq1[4], bq2[4];
+  uint4 mt4 = make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int G = 0; G < 4; G++) bq1[G] = bq2[G] = make_uint2(0, 0);
+  if (hoist && warp < nsb) {
+    const uint2* f1 = reinterpret_cast<const uint2*>(bfrag) + static_cast<size_t>(warp) * 256 + lane;
+#pragma unroll
+    for (int G = 0; G < 4; G++) bq1[G] = f1[G * 64], bq2[G] = f1[G * 64 + 32];
+    mt4 = reinterpret_cast<const uint4*>(meta)[static_cast<size_t>(warp) * 4 + t];
+  }
   for (int b = 0; b < nbatches; b++) {
     const int rb0 = r0 + b * 16 * kMT;
     const int brow = min(16 * kMT, nrows - b * 16 * kMT);
@@ -281,6 +313,10 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
                 wA[G] = *reinterpret_cast<const uint2*>(rowA + 16 + 32 * G + 8 * t);
                 wB[G] = *reinterpret_cast<const uint2*>(rowB + 16 + 32 * G + 8 * t);
               }
+              // everything this warp needs from the stage is in registers: hand the slot back now (the
+              // arrive is a release, so the loads above are performed before the producer sees it)
+              __syncwarp();
+              if (lane == 0) ib_arrive(bars_s + 8 * (kMaxStages + slot));
               uint32_t scA[2], mnA[2], scB[2], mnB[2];
               q4k_unpack_scales(hA.y, hA.z, hA.w, scA[0], scA[1], mnA[0], mnA[1]);
               q4k_unpack_scales(hB.y, hB.z, hB.w, scB[0], scB[1], mnB[0], mnB[1]);
@@ -292,19 +328,30 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
               const float dB = half_bits_to_f32(hB.x), dminB = half_bits_to_f32(hB.x >> 16);
 #pragma unroll
               for (int p = 0; p < MP; p++) {
-                const uint2* f1 = reinterpret_cast<const uint2*>(bfrag) + (static_cast<size_t>(p) * nsb + sb) * 256 + lane;
-                const uint4 mt4 = reinterpret_cast<const uint4*>(meta)[(static_cast<size_t>(p) * nsb + sb) * 4 + t];
+                if (!hoist) {
+                  const uint2* f1 =
+                      reinterpret_cast<const uint2*>(bfrag) + (static_cast<size_t>(p) * nsb + sb) * 256 + lane;
+#pragma unroll
+                  for (int G = 0; G < 4; G++) bq1[G] = f1[G * 64], bq2[G] = f1[G * 64 + 32];
+                  mt4 = reinterpret_cast<const uint4*>(meta)[(static_cast<size_t>(p) * nsb + sb) * 4 + t];
+                }
+                // all eight MMAs first (four independent chains of two), then the scale arithmetic
+                int d[4][4];
+#pragma unroll
+                for (int G = 0; G < 4; G++) {
+                  d[G][0] = d[G][1] = d[G][2] = d[G][3] = 0;
+                  imma_u8s8(d[G], wA[G].x, wB[G].x, wA[G].y, wB[G].y, bq1[G]);
+                }
+#pragma unroll
+                for (int G = 0; G < 4; G++)
+                  imma_u8s8(d[G], wA[G].x & 0xF0F0F0F0u, wB[G].x & 0xF0F0F0F0u, wA[G].y & 0xF0F0F0F0u,
+                            wB[G].y & 0xF0F0F0F0u, bq2[G]);
                 int hiA = 0, loA = 0, hiB = 0, loB = 0;
 #pragma unroll
                 for (int G = 0; G < 4; G++) {
-                  const uint2 b1 = f1[G * 64], b2 = f1[G * 64 + 32];
-                  int d[4] = {0, 0, 0, 0};
-                  imma_u8s8(d, wA[G].x, wB[G].x, wA[G].y, wB[G].y, b1);
-                  imma_u8s8(d, wA[G].x & 0xF0F0F0F0u, wB[G].x & 0xF0F0F0F0u, wA[G].y & 0xF0F0F0F0u,
-                            wB[G].y & 0xF0F0F0F0u, b2);
                   const int sa = (G & 1) ? __byte_perm(scA[G >> 1], 0, 0x4442) : (scA[G >> 1] & 0xFF);
                   const int sbv = (G & 1) ? __byte_perm(scB[G >> 1], 0, 0x4442) : (scB[G >> 1] & 0xFF);
-                  hiA += d[0] * sa, loA += d[1] * sa, hiB += d[2] * sbv, loB += d[3] * sbv;
+                  hiA += d[G][0] * sa, loA += d[G][1] * sa, hiB += d[G][2] * sbv, loB += d[G][3] * sbv;
                 }
                 const float xs = __uint_as_float(mt4.w);
                 const float xsm = par ? xs * 0.0625f : xs;  // odd lanes carry 16 x the high nibbles
@@ -317,9 +364,10 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
                 acc[mt][p][0] += fmaf(dA * xsm, fA, -(dminA * xs) * static_cast<float>(tA));
                 acc[mt][p][1] += fmaf(dB * xsm, fB, -(dminB * xs) * static_cast<float>(tB));
               }
+            } else {
+              __syncwarp();
+              if (lane == 0) ib_arrive(bars_s + 8 * (kMaxStages + slot));
             }
-            __syncwarp();
-            if (lane == 0) ib_arrive(bars_s + 8 * (kMaxStages + slot));
           }
         }
       }
