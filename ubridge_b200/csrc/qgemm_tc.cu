@@ -677,6 +677,10 @@ __global__ void __launch_bounds__(256) moe_gather_rows_kernel(__nv_bfloat16* __r
 
 namespace ub {
 
+// cuTensorMapEncodeTiled of the running driver as an untyped pointer (null when unavailable), for the other
+// kernels of this library that build tensor maps.
+void* tensor_map_encoder() { return reinterpret_cast<void*>(encode_tiled_fn()); }
+
 // y (bf16) [M,N] = x (bf16) [M,K] . dequant(Wq)^T on tcgen05; K % 256 == 0, pointers 16-byte aligned.
 // Returns UB_ERR_UNSUPPORTED when the driver offers no tensor-map encoder (the caller falls back).
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {

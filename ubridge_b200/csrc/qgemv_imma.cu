@@ -19,12 +19,23 @@
 // sub-block sums of q, and turn into f32 once per (row, super-block).
 //
 // Data movement.  One persistent CTA per SM owns a contiguous range of rows.  A producer warp streams 16-row
-// tiles (one bulk copy per row, rows padded to a bank-conflict-free stride) into an mbarrier ring; 16 compute
-// warps each own one super-block column of the tile.  Per-row partial sums stay in registers for up to seven
+// tiles into an mbarrier ring; 16 compute warps each own one super-block column of the tile.  A tile is ONE
+// tensor-map copy (rows viewed as lines of 128 bytes, 128-byte swizzle, so that the reads of eight rows fall
+// into distinct banks); issuing a bulk copy costs about 70 ns, so one copy per row would take longer to
+// issue than the data takes to arrive.  Rows that are not a multiple of 128 bytes fall back to per-row
+// copies into a padded layout.  Per-row partial sums stay in registers for up to seven
 // tiles and are added across warps once at the end, in a fixed order.
 // Every mbarrier wait is bounded: on expiry the kernel records UB_ERR_TIMEOUT in the device error word,
 // stops waiting and runs out its loops.
+#include <cuda.h>  // CUtensorMap type and enums only; the encoder is resolved at run time
+
+#include <string.h>
+
 #include "common.cuh"
+
+namespace ub {
+void* tensor_map_encoder();
+}
 
 namespace {
 
@@ -37,7 +48,7 @@ constexpr int kChunkSb = 16;                // super-blocks of K per ring stage 
 constexpr int kMaxStages = 8;
 constexpr uint32_t kSpinLimit = 400000;
 constexpr float kXQMax = 32258.f;           // 127 * 254
-constexpr size_t kSmemBudget = 220 * 1024;
+constexpr size_t kSmemBudget = 219 * 1024;  // ring + fragments; 1 KB more goes to the alignment slack
 
 __device__ __forceinline__ void ib_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -115,11 +126,18 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 struct ImmaGeom {
   int nsb, nchunks, row_stride, stage_bytes;
 };
-__host__ __device__ inline ImmaGeom imma_geom(int K) {
+// use_tm: tiles arrive by tensor-map copies (dense rows of whole 128-byte lines, swizzled)
+__host__ __device__ inline bool imma_tm_ok(int K) { return ((K >> 8) % 8) == 0; }
+__host__ __device__ inline ImmaGeom imma_geom(int K, bool use_tm) {
   ImmaGeom g;
   g.nsb = K >> 8;
   g.nchunks = (g.nsb + kChunkSb - 1) / kChunkSb;
   const int cs = g.nsb < kChunkSb ? g.nsb : kChunkSb;
+  if (use_tm) {
+    g.row_stride = cs * UB_Q4K_BYTES;  // a multiple of 128 bytes (cs is a multiple of 8)
+    g.stage_bytes = 16 * g.row_stride;
+    return g;
+  }
   // 16-byte loads of eight rows must fall into distinct banks: stride = 32 bytes modulo 128
   g.row_stride = (cs * UB_Q4K_BYTES + 127) / 128 * 128 + 32;
   g.stage_bytes = 16 * g.row_stride;
@@ -130,12 +148,15 @@ __host__ __device__ inline ImmaGeom imma_geom(int K) {
 template <typename XT, int MP>
 __global__ void __launch_bounds__(kImmaThreads, 1)
 qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void* __restrict__ y, int M, int N,
-                      int K, int y_dtype, int S, int* err_word) {
-  extern __shared__ __align__(128) unsigned char ismem[];
+                      int K, int y_dtype, int S, int* err_word, int use_tm, const __grid_constant__ CUtensorMap w_map) {
+  extern __shared__ __align__(128) unsigned char ismem_raw[];
+  // swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this round-up
+  unsigned char* const ismem =
+      ismem_raw + ((1024u - (static_cast<uint32_t>(__cvta_generic_to_shared(ismem_raw)) & 1023u)) & 1023u);
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStages];  // full[S], empty[S]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const ImmaGeom geo = imma_geom(K);
+  const ImmaGeom geo = imma_geom(K, use_tm != 0);
   const int nsb = geo.nsb, nchunks = geo.nchunks;
   const size_t row_bytes = static_cast<size_t>(nsb) * UB_Q4K_BYTES;
   const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ismem));
@@ -247,6 +268,16 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
   }
 
   const int par = t & 1;
+  // byte offsets of this lane's header and nibble pieces inside a stage (row g, super-block `warp` of the
+  // chunk); with tensor-map tiles the 16-byte unit index is XORed with the 128-byte line index modulo 8
+  uint32_t off_h, off_q[4];
+  {
+    auto swz = [&](uint32_t L) { return use_tm ? (L ^ (((L >> 7) & 7u) << 4)) : L; };
+    const uint32_t L0 = static_cast<uint32_t>(g * geo.row_stride + warp * UB_Q4K_BYTES);
+    off_h = swz(L0);
+#pragma unroll
+    for (int G = 0; G < 4; G++) off_q[G] = swz(L0 + 16 + 32 * G + 8 * t);
+  }
   // B fragments and activation metadata of this warp's super-block: constant over the launch when K fits one
   // chunk and there is one token pair, then kept in registers
   const bool hoist = MP == 1 && nchunks == 1;
@@ -278,6 +309,20 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
           const int cs = min(kChunkSb, nsb - c * kChunkSb);
           const uint32_t cbytes = static_cast<uint32_t>(cs * UB_Q4K_BYTES);
           const uint32_t full = bars_s + 8 * slot;
+          if (use_tm) {
+            // one copy: 16 rows x (row_stride / 128) lines of 128 bytes; rows past N arrive as zeros, rows of
+            // the next CTA's range are simply not used
+            if (lane == 0) {
+              ib_expect_tx(full, static_cast<uint32_t>(geo.stage_bytes));
+              asm volatile(
+                  "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
+                  "%5}], [%2];" ::"r"(ring_s + slot * geo.stage_bytes),
+                  "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(full), "r"(0), "r"(c * (geo.row_stride >> 7)),
+                  "r"(rb0 + 16 * mt)
+                  : "memory");
+            }
+            continue;
+          }
           if (lane == 0) ib_expect_tx(full, cbytes * rows_here);
           __syncwarp();
           if (lane < rows_here)
@@ -303,15 +348,16 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
             const int cs = min(kChunkSb, nsb - c * kChunkSb);
             if (ok && warp < cs) {
               const int sb = c * kChunkSb + warp;
-              const unsigned char* rowA =
-                  ismem + static_cast<size_t>(slot) * geo.stage_bytes + g * geo.row_stride + warp * UB_Q4K_BYTES;
+              // rows g and g + 8 of the tile; offsets inside a row are swizzled identically for both
+              const unsigned char* rowA = ismem + static_cast<size_t>(slot) * geo.stage_bytes;
               const unsigned char* rowB = rowA + 8 * geo.row_stride;
-              const uint4 hA = *reinterpret_cast<const uint4*>(rowA), hB = *reinterpret_cast<const uint4*>(rowB);
+              const uint4 hA = *reinterpret_cast<const uint4*>(rowA + off_h);
+              const uint4 hB = *reinterpret_cast<const uint4*>(rowB + off_h);
               uint2 wA[4], wB[4];
 #pragma unroll
               for (int G = 0; G < 4; G++) {
-                wA[G] = *reinterpret_cast<const uint2*>(rowA + 16 + 32 * G + 8 * t);
-                wB[G] = *reinterpret_cast<const uint2*>(rowB + 16 + 32 * G + 8 * t);
+                wA[G] = *reinterpret_cast<const uint2*>(rowA + off_q[G]);
+                wB[G] = *reinterpret_cast<const uint2*>(rowB + off_q[G]);
               }
               // everything this warp needs from the stage is in registers: hand the slot back now (the
               // arrive is a release, so the loads above are performed before the producer sees it)
@@ -403,14 +449,33 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
 
 template <typename XT, int MP>
 int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
-  const ImmaGeom geo = imma_geom(K);
+  typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ub::tensor_map_encoder());
+  bool use_tm = enc != nullptr && imma_tm_ok(K);
+  CUtensorMap wmap;
+  memset(&wmap, 0, sizeof(wmap));
+  if (use_tm) {
+    // rows as lines of 128 bytes: {128 bytes, lines per row, N rows}; box = {128, lines per chunk, 16 rows}
+    const ImmaGeom gt = imma_geom(K, true);
+    const cuuint64_t row_bytes = static_cast<cuuint64_t>(gt.nsb) * UB_Q4K_BYTES;
+    const cuuint64_t dims[3] = {128, row_bytes / 128, static_cast<cuuint64_t>(N)};
+    const cuuint64_t strides[2] = {128, row_bytes};
+    const cuuint32_t box[3] = {128, static_cast<cuuint32_t>(gt.row_stride / 128), 16};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    use_tm = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(wq), dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  const ImmaGeom geo = imma_geom(K, use_tm);
   const size_t fixed = static_cast<size_t>(MP) * geo.nsb * (2048 + 64);
   if (fixed + 2 * static_cast<size_t>(geo.stage_bytes) > kSmemBudget) return UB_ERR_UNSUPPORTED;
   int S = static_cast<int>((kSmemBudget - fixed) / geo.stage_bytes);
   if (S > kMaxStages) S = kMaxStages;
   const size_t red_bytes = static_cast<size_t>(kCW) * kMT * MP * 32 * sizeof(float);
   if (static_cast<size_t>(S) * geo.stage_bytes < red_bytes) return UB_ERR_UNSUPPORTED;
-  const size_t smem = static_cast<size_t>(S) * geo.stage_bytes + fixed;
+  const size_t smem = static_cast<size_t>(S) * geo.stage_bytes + fixed + 1024;
   auto kernel = qgemv_q4k_imma_kernel<XT, MP>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
@@ -420,7 +485,8 @@ int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, in
   const int sms = ub::num_sms();
   const int tiles = (N + 15) / 16;
   const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, kImmaThreads, smem, s>>>(wq, x, y, M, N, K, y_dtype, S, ub::device_error_word());
+  kernel<<<grid, kImmaThreads, smem, s>>>(wq, x, y, M, N, K, y_dtype, S, ub::device_error_word(), use_tm ? 1 : 0,
+                                          wmap);
   return ub::check_launch();
 }
 
