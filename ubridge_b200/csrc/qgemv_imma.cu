@@ -171,6 +171,12 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
   const int nrows = base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
   const int nbatches = (nrows + 16 * kMT - 1) / (16 * kMT);
 
+  // Programmatic dependent launch: the next kernel in the stream may start as soon as every CTA of this
+  // grid has passed this point (its CTAs take over SMs as ours retire, instead of waiting for the whole grid
+  // to drain), and this kernel may itself have been started early: everything up to the wait below touches
+  // only shared memory; the weights, which no kernel writes, are requested by the producer warp right away.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (warp < kCW) asm volatile("griddepcontrol.wait;" ::: "memory");  // activations may come from the previous kernel
   // the first activation piece of this warp is requested before anything else: its latency is on the
   // critical path of the whole launch
   float v_first[8];
@@ -432,6 +438,7 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
           }
     }
     __syncthreads();  // (B) partial sums visible
+    if (b == 0 && warp == kCW) asm volatile("griddepcontrol.wait;" ::: "memory");  // before this warp's stores
     for (int o = threadIdx.x; o < n_mt * 16 * 2 * MP; o += kImmaThreads) {
       const int rl = o / (2 * MP), tok = o - rl * (2 * MP);
       if (rl < brow && tok < M) {
@@ -485,8 +492,18 @@ int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, in
   const int sms = ub::num_sms();
   const int tiles = (N + 15) / 16;
   const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, kImmaThreads, smem, s>>>(wq, x, y, M, N, K, y_dtype, S, ub::device_error_word(), use_tm ? 1 : 0,
-                                          wmap);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kImmaThreads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, wq, x, y, M, N, K, y_dtype, S, ub::device_error_word(), use_tm ? 1 : 0, wmap);
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
   return ub::check_launch();
 }
 
