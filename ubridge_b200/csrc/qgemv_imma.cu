@@ -43,7 +43,9 @@ using namespace ub;
 
 constexpr int kCW = 16;                     // compute warps; warp kCW is the producer
 constexpr int kImmaThreads = (kCW + 1) * 32;
-constexpr int kMT = 7;                      // 16-row tiles whose partial sums a lane keeps in registers
+// 16-row tiles whose partial sums a lane keeps in registers between two cross-warp reductions: seven cover the
+// 97 rows per SM of a 14336-row matrix in one batch; with four token pairs that many accumulators spill
+constexpr int imma_mt(int mp) { return mp >= 4 ? 4 : 7; }
 constexpr int kChunkSb = 16;                // super-blocks of K per ring stage (one per compute warp)
 constexpr int kMaxStages = 8;
 constexpr uint32_t kSpinLimit = 400000;
@@ -69,8 +71,10 @@ __device__ __forceinline__ bool ib_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 __device__ __forceinline__ bool ib_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; i++)
+  for (uint32_t i = 0; i < kSpinLimit; i++) {
     if (ib_try(bar, parity)) return true;
+    if (i >= 2) __nanosleep(40);  // waiting warps would otherwise take issue slots from the working ones
+  }
   return false;
 }
 __device__ __forceinline__ void ib_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -149,6 +153,7 @@ template <typename XT, int MP>
 __global__ void __launch_bounds__(kImmaThreads, 1)
 qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void* __restrict__ y, int M, int N,
                       int K, int y_dtype, int S, int* err_word, int use_tm, const __grid_constant__ CUtensorMap w_map) {
+  constexpr int kMT = imma_mt(MP);
   extern __shared__ __align__(128) unsigned char ismem_raw[];
   // swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this round-up
   unsigned char* const ismem =
@@ -480,7 +485,7 @@ int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, in
   if (fixed + 2 * static_cast<size_t>(geo.stage_bytes) > kSmemBudget) return UB_ERR_UNSUPPORTED;
   int S = static_cast<int>((kSmemBudget - fixed) / geo.stage_bytes);
   if (S > kMaxStages) S = kMaxStages;
-  const size_t red_bytes = static_cast<size_t>(kCW) * kMT * MP * 32 * sizeof(float);
+  const size_t red_bytes = static_cast<size_t>(kCW) * imma_mt(MP) * MP * 32 * sizeof(float);
   if (static_cast<size_t>(S) * geo.stage_bytes < red_bytes) return UB_ERR_UNSUPPORTED;
   const size_t smem = static_cast<size_t>(S) * geo.stage_bytes + fixed + 1024;
   auto kernel = qgemv_q4k_imma_kernel<XT, MP>;
