@@ -1,0 +1,129 @@
+"""GPU, two or more devices: the tensor-parallel linear stack and the expert-parallel MoE layer, threads as
+ranks (one device each, the pattern of the reference's collective tests, src/eccl.rs:428-492), partial
+outputs summed with ecclAllReduce, against the oracle's unsharded result."""
+import threading
+
+import numpy as np
+import pytest
+
+import ubridge_b200 as ub
+from oracle import oracle as o
+from ubridge_b200 import eccl, parallel as par
+
+pytestmark = pytest.mark.gpu
+
+
+def _world():
+    n = ub.lib().ub_device_count()
+    if n < 2:
+        pytest.skip("needs 2+ GPUs")
+    return 2
+
+
+def _bf16(x):
+    return o.bf16_bits_to_f32(o.f32_to_bf16_bits(np.asarray(x, dtype=np.float32)))
+
+
+def _run_ranks(world, rank_main):
+    errors, results = [None] * world, [None] * world
+
+    def wrap(r):
+        try:
+            results[r] = rank_main(r)
+        except Exception as e:  # noqa: BLE001 - reported below, in the main thread
+            errors[r] = e
+
+    threads = [threading.Thread(target=wrap, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=300)
+    for e in errors:
+        if e is not None:
+            raise e
+    assert all(r is not None for r in results), "a rank did not finish"
+    return results
+
+
+@pytest.mark.parametrize("M", [1, 40])
+def test_tp_stack_matches_the_unsharded_oracle(M):
+    world = _world()
+    hidden, inter, nq, nkv, hd = 1024, 2048, 8, 2, 128
+    rng = np.random.default_rng(300)
+    x = o.gen_activation(rng, M, hidden, True)
+    w_qkv = o.gen_q4k_weight(rng, (nq + 2 * nkv) * hd, hidden)
+    w_o = o.gen_q4k_weight(rng, hidden, nq * hd)
+    w_gate, w_up = o.gen_q4k_weight(rng, inter, hidden), o.gen_q4k_weight(rng, inter, hidden)
+    w_down = o.gen_q4k_weight(rng, hidden, inter)
+    uid = eccl.Id()
+
+    def rank_main(r):
+        d = ub.GcuDevice(r)
+        d.bind_to_thread()
+        comm = eccl.Comm.from_rank(r, world, uid)
+
+        def all_reduce(buf, count):
+            comm.all_reduce(buf, buf, count, eccl.Bfloat16, eccl.ReduceOp.Sum, stream=d.stream)
+
+        stack = par.TPLinearStack(
+            d, hidden, inter, nq, nkv, hd, world,
+            par.qkv_column_split(w_qkv, nq, nkv, hd, hidden, True, r, world),
+            par.row_split(w_o, hidden, nq * hd, True, r, world)[0],
+            par.gate_up_column_split(w_gate, w_up, inter, hidden, True, r, world),
+            par.row_split(w_down, hidden, inter, True, r, world)[0], M, all_reduce)
+        d_x = d.htod_sync_copy(o.f32_to_bf16_bits(x).reshape(-1))
+        out = stack.forward(d_x, M)
+        d.synchronize()
+        y = o.bf16_bits_to_f32(d.dtoh_sync_copy(out, np.uint16)[:M * hidden]).reshape(M, hidden)
+        comm.destroy()
+        return y
+
+    got = _run_ranks(world, rank_main)
+    # unsharded restatement with the same roundings to bf16 between the matmuls
+    q = _bf16(o.qmatmul_exact(x, o.dequant_q4k(w_qkv).reshape(-1, hidden)))[:, :nq * hd]
+    h1 = _bf16(o.qmatmul_exact(q, o.dequant_q4k(w_o).reshape(hidden, nq * hd)))
+    g = _bf16(o.qmatmul_exact(h1, o.dequant_q4k(w_gate).reshape(inter, hidden)))
+    u = _bf16(o.qmatmul_exact(h1, o.dequant_q4k(w_up).reshape(inter, hidden)))
+    act = o.silu_and_mul(np.concatenate([g, u], axis=1), o.UB_BF16)
+    want = o.qmatmul_exact(act, o.dequant_q4k(w_down).reshape(hidden, inter))
+    for r in range(world):
+        # bf16 partial sums are rounded before the all-reduce: 1e-2 is the tensor-core tolerance of the path
+        assert o.rel_l2(got[r], want) < 1e-2
+    assert np.array_equal(got[0], got[1])  # all ranks hold the same reduced result
+
+
+def test_ep_layer_matches_the_unsharded_oracle():
+    world = _world()
+    T, H, I, E, k, block = 48, 512, 768, 4, 2, 16
+    rng = np.random.default_rng(400)
+    hidden = o.gen_activation(rng, T, H, True)
+    logits = o.gen_activation(rng, T, E, True)
+    w13_blocks, w2_blocks = o.gen_q4k_weight(rng, E * 2 * I, H), o.gen_q4k_weight(rng, E * H, I)
+    w13, w2 = w13_blocks.reshape(E, -1), w2_blocks.reshape(E, -1)  # bytes of each expert
+    uid = eccl.Id()
+
+    def rank_main(r):
+        d = ub.GcuDevice(r)
+        d.bind_to_thread()
+        comm = eccl.Comm.from_rank(r, world, uid)
+
+        def all_reduce(buf, count):
+            comm.all_reduce(buf, buf, count, eccl.Bfloat16, eccl.ReduceOp.Sum, stream=d.stream)
+
+        e0, e1 = par.expert_range(E, r, world)
+        layer = par.EPMoELayer(d, T, H, I, E, k, block, r, world, w13[e0:e1].reshape(-1), w2[e0:e1].reshape(-1),
+                               all_reduce)
+        d_h = d.htod_sync_copy(o.f32_to_bf16_bits(hidden).reshape(-1))
+        d_l = d.htod_sync_copy(o.f32_to_bf16_bits(logits).reshape(-1))
+        out = layer.forward(d_h, d_l)
+        d.synchronize()
+        y = o.bf16_bits_to_f32(d.dtoh_sync_copy(out, np.uint16)[:T * H]).reshape(T, H)
+        comm.destroy()
+        return y
+
+    got = _run_ranks(world, rank_main)
+    want, _ = o.moe_layer_exact(hidden, logits, o.dequant_q4k(w13_blocks).reshape(E, 2 * I, H),
+                                o.dequant_q4k(w2_blocks).reshape(E, H, I), k, block, True)
+    for r in range(world):
+        assert o.rel_l2(got[r], want) < 1e-2
+    assert np.array_equal(got[0], got[1])
