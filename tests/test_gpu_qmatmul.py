@@ -44,7 +44,8 @@ def test_config1_q8_0_decode(dev):
     got = _run(dev, w, x, 1, N, K, False, DTYPE_F32, DTYPE_F32)
     want = o.c_qmatmul(x, w, N, K, False)
     assert o.rel_l2(got, want) < TOL_DECODE
-    assert o.rel_l2(got, want) < 1e-5  # f32 accumulation of exact products: far inside the tolerance
+    # exact integer dots of 15-bit block fixed-point activations (relative step 2^-15): far inside the tolerance
+    assert o.rel_l2(got, want) < 1e-4
 
 
 @pytest.mark.parametrize("M", [1, 4, 16])

@@ -925,6 +925,8 @@ namespace ub {
 
 template <typename XT>
 int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s);
+template <typename XT>
+int q8_0_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s);
 
 // Q4_K: up to eight rows of x per pass on the integer tensor-core kernel when its shared-memory plan fits.
 // Otherwise rows of x are processed four (then two, then one) at a time; each pass streams W once.
@@ -938,9 +940,10 @@ int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K
     const XT* xp = x + static_cast<size_t>(m0) * K;
     void* yp = static_cast<char*>(y) + static_cast<size_t>(m0) * N * dtype_size(y_dtype);
     int st;
-    if (is_q4k && (reinterpret_cast<uintptr_t>(wq) & 15) == 0) {
+    if ((reinterpret_cast<uintptr_t>(wq) & 15) == 0) {
       const int mi = left >= 8 ? 8 : left;
-      st = q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, s);
+      st = is_q4k ? q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, s)
+                  : q8_0_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, s);
       if (st == UB_OK) {
         m0 += mi;
         continue;

@@ -512,6 +512,266 @@ int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, in
   return ub::check_launch();
 }
 
+
+// =====================================================================================================
+// Q8_0 on the same scheme.  A block is 34 bytes: an f16 scale and 32 signed bytes, which are the MMA's A
+// operand as they lie in memory (s8 x s8 -> s32); activations are quantised per 32-value block to the same
+// two signed-byte limbs, so a token takes two of the eight B columns and a launch carries token QUADS.
+// Replaces the reference's decode matmul for block_q8_0 weights (kernels/quant.cpp:98-104, dequantisation
+// :188-268).  Tiles are 16 rows x 64 blocks (2176 bytes = 17 lines of 128 bytes per row), one swizzled
+// tensor-map copy each; warp w owns blocks 4w .. 4w+3 of the chunk.  The 32 weight bytes of a block start
+// 2 bytes after a 4-byte boundary in every other block: those are read as three aligned words and funnel
+// shifted.
+constexpr int kQ8ChunkBlocks = 64;
+constexpr int kQ8RowStride = kQ8ChunkBlocks * UB_Q8_0_BYTES;  // 2176
+constexpr int kQ8StageBytes = 16 * kQ8RowStride;              // 34816 = 34 KB
+
+__device__ __forceinline__ void imma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
+}
+__device__ __forceinline__ uint32_t swz128(uint32_t L) { return L ^ (((L >> 7) & 7u) << 4); }
+
+// MQ: token quads per launch (M <= 4 MQ, missing tokens are zeros).
+template <typename XT, int MQ>
+__global__ void __launch_bounds__(kImmaThreads, 1)
+qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, int N, int K, int y_dtype, int S,
+                       int* err_word, const __grid_constant__ CUtensorMap w_map) {
+  constexpr int kMT = 7;
+  extern __shared__ __align__(128) unsigned char ismem_raw[];
+  unsigned char* const ismem =
+      ismem_raw + ((1024u - (static_cast<uint32_t>(__cvta_generic_to_shared(ismem_raw)) & 1023u)) & 1023u);
+  __shared__ __align__(8) unsigned long long bars[2 * kMaxStages];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int nblk = K >> 5, nchunks = nblk / kQ8ChunkBlocks;
+  const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ismem));
+  const uint32_t bars_s = static_cast<uint32_t>(__cvta_generic_to_shared(bars));
+  unsigned char* const bfrag = ismem + static_cast<size_t>(S) * kQ8StageBytes;  // [MQ][nblk][32 lanes] uint2
+  float* const xscale = reinterpret_cast<float*>(bfrag + static_cast<size_t>(MQ) * nblk * 256);  // [MQ][nblk][4]
+  float* const red = reinterpret_cast<float*>(ismem);
+
+  const int base = N / gridDim.x, rem = N % gridDim.x;
+  const int r0 = blockIdx.x * base + min(static_cast<int>(blockIdx.x), rem);
+  const int nrows = base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
+  const int nbatches = (nrows + 16 * kMT - 1) / (16 * kMT);
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (warp < kCW) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      ib_init(bars_s + 8 * s, 1);
+      ib_init(bars_s + 8 * (kMaxStages + s), kCW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  bool ok = true;
+  int it = 0;
+
+  if (warp < kCW) {
+    // ---- activations -> B fragments: unit = (token, 256 values); lane i holds 8 values of block i / 4 ----
+    const int groups = K >> 8;
+    for (int u = warp; u < 4 * MQ * groups; u += kCW) {
+      const int m = u / groups, grp = u - m * groups;
+      const int quad = m >> 2, col = 2 * (m & 3);
+      const int blk = grp * 8 + (lane >> 2), tt = lane & 3;
+      uint2* f = reinterpret_cast<uint2*>(bfrag) + (static_cast<size_t>(quad) * nblk + blk) * 32;
+      float* xsp = xscale + (static_cast<size_t>(quad) * nblk + blk) * 4 + (m & 3);
+      if (m >= M) {
+        f[col * 4 + tt] = f[(col + 1) * 4 + tt] = make_uint2(0, 0);
+        if (tt == 0) *xsp = 0.f;
+        continue;
+      }
+      float v[8];
+      ld_x8<XT>(x + static_cast<size_t>(m) * K + grp * 256 + 8 * lane, v);
+      float amax = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));  // over the block's four lanes
+      const float inv = amax > 0.f ? kXQMax / amax : 0.f;
+      int hi[8], lo[8];
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        const int q = __float2int_rn(v[e] * inv);
+        hi[e] = __float2int_rn(static_cast<float>(q) * (1.f / 254.f));
+        lo[e] = q - 254 * hi[e];
+      }
+      f[col * 4 + tt] = make_uint2(pack4(hi[0], hi[1], hi[2], hi[3]), pack4(hi[4], hi[5], hi[6], hi[7]));
+      f[(col + 1) * 4 + tt] = make_uint2(pack4(lo[0], lo[1], lo[2], lo[3]), pack4(lo[4], lo[5], lo[6], lo[7]));
+      if (tt == 0) *xsp = amax * (1.f / kXQMax);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kCW * 32) : "memory");
+  }
+
+  for (int b = 0; b < nbatches; b++) {
+    const int rb0 = r0 + b * 16 * kMT;
+    const int brow = min(16 * kMT, nrows - b * 16 * kMT);
+    const int n_mt = (brow + 15) >> 4;
+    float acc[kMT][MQ][2];
+    if (warp == kCW) {
+      for (int mt = 0; mt < n_mt; mt++) {
+        for (int c = 0; c < nchunks; c++, it++) {
+          const int slot = it % S, round = it / S;
+          if (ok && round > 0) ok = ib_wait(bars_s + 8 * (kMaxStages + slot), (round - 1) & 1);
+          ok = __all_sync(0xFFFFFFFFu, ok);
+          if (!ok) continue;
+          if (lane == 0) {
+            const uint32_t full = bars_s + 8 * slot;
+            ib_expect_tx(full, kQ8StageBytes);
+            asm volatile(
+                "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
+                "%5}], [%2];" ::"r"(ring_s + slot * kQ8StageBytes),
+                "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(full), "r"(0), "r"(c * (kQ8RowStride >> 7)),
+                "r"(rb0 + 16 * mt)
+                : "memory");
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int mt = 0; mt < kMT; mt++)
+#pragma unroll
+        for (int q = 0; q < MQ; q++) acc[mt][q][0] = acc[mt][q][1] = 0.f;
+#pragma unroll
+      for (int mt = 0; mt < kMT; mt++) {
+        if (mt < n_mt) {
+          for (int c = 0; c < nchunks; c++, it++) {
+            const int slot = it % S, round = it / S;
+            if (ok) ok = __all_sync(0xFFFFFFFFu, ib_wait(bars_s + 8 * slot, round & 1));
+            if (ok) {
+              const unsigned char* st = ismem + static_cast<size_t>(slot) * kQ8StageBytes;
+              // this warp's four blocks of rows g and g + 8: scales and weight bytes into registers
+              uint32_t a[4][4];
+              float dA[4], dB[4];
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                const uint32_t L = static_cast<uint32_t>(g * kQ8RowStride + (warp * 4 + i) * UB_Q8_0_BYTES);
+                const uint32_t LB = L + 8 * kQ8RowStride;  // 8 rows = 136 lines further: same swizzle phase
+                dA[i] = half_bits_to_f32(*reinterpret_cast<const unsigned short*>(st + swz128(L)));
+                dB[i] = half_bits_to_f32(*reinterpret_cast<const unsigned short*>(st + swz128(LB)));
+                const uint32_t q0 = L + 2 + 8 * t;
+                if (i & 1) {  // 34 i + 2 is a multiple of 4 for odd i (warp * 4 is even): aligned words
+                  a[i][0] = *reinterpret_cast<const uint32_t*>(st + swz128(q0));
+                  a[i][2] = *reinterpret_cast<const uint32_t*>(st + swz128(q0 + 4));
+                  a[i][1] = *reinterpret_cast<const uint32_t*>(st + swz128(q0 + 8 * kQ8RowStride));
+                  a[i][3] = *reinterpret_cast<const uint32_t*>(st + swz128(q0 + 4 + 8 * kQ8RowStride));
+                } else {      // 2 bytes past a word boundary: three words, funnel shifted by 16 bits
+                  const uint32_t w0 = *reinterpret_cast<const uint32_t*>(st + swz128(q0 - 2));
+                  const uint32_t w1 = *reinterpret_cast<const uint32_t*>(st + swz128(q0 + 2));
+                  const uint32_t w2 = *reinterpret_cast<const uint32_t*>(st + swz128(q0 + 6));
+                  a[i][0] = __funnelshift_r(w0, w1, 16), a[i][2] = __funnelshift_r(w1, w2, 16);
+                  const uint32_t v0 = *reinterpret_cast<const uint32_t*>(st + swz128(q0 - 2 + 8 * kQ8RowStride));
+                  const uint32_t v1 = *reinterpret_cast<const uint32_t*>(st + swz128(q0 + 2 + 8 * kQ8RowStride));
+                  const uint32_t v2 = *reinterpret_cast<const uint32_t*>(st + swz128(q0 + 6 + 8 * kQ8RowStride));
+                  a[i][1] = __funnelshift_r(v0, v1, 16), a[i][3] = __funnelshift_r(v1, v2, 16);
+                }
+              }
+              __syncwarp();
+              if (lane == 0) ib_arrive(bars_s + 8 * (kMaxStages + slot));
+#pragma unroll
+              for (int q = 0; q < MQ; q++) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                  const int blk = c * kQ8ChunkBlocks + warp * 4 + i;
+                  const uint2 bf = reinterpret_cast<const uint2*>(bfrag)[(static_cast<size_t>(q) * nblk + blk) * 32 + lane];
+                  const float xs = xscale[(static_cast<size_t>(q) * nblk + blk) * 4 + t];
+                  int d[4] = {0, 0, 0, 0};
+                  imma_s8s8(d, a[i][0], a[i][1], a[i][2], a[i][3], bf);
+                  // columns 2t, 2t+1 = token t's high and low limb
+                  acc[mt][q][0] = fmaf(static_cast<float>(d[0] * 254 + d[1]), dA[i] * xs, acc[mt][q][0]);
+                  acc[mt][q][1] = fmaf(static_cast<float>(d[2] * 254 + d[3]), dB[i] * xs, acc[mt][q][1]);
+                }
+              }
+            } else {
+              __syncwarp();
+              if (lane == 0) ib_arrive(bars_s + 8 * (kMaxStages + slot));
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();  // (A) every stage of this batch has been consumed: the ring may hold the partial sums
+    if (warp < kCW) {
+#pragma unroll
+      for (int mt = 0; mt < kMT; mt++)
+#pragma unroll
+        for (int q = 0; q < MQ; q++)
+#pragma unroll
+          for (int rs = 0; rs < 2; rs++)
+            red[((((warp * kMT + mt) * MQ + q) * 2 + rs) * 8 + g) * 4 + t] = acc[mt][q][rs];
+    }
+    __syncthreads();  // (B)
+    if (b == 0 && warp == kCW) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int o = threadIdx.x; o < n_mt * 16 * 4 * MQ; o += kImmaThreads) {
+      const int rl = o / (4 * MQ), tok = o - rl * (4 * MQ);
+      if (rl < brow && tok < M) {
+        const int mt = rl >> 4, rs = (rl >> 3) & 1, gg = rl & 7, q = tok >> 2, tk = tok & 3;
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kCW; w++) tot += red[((((w * kMT + mt) * MQ + q) * 2 + rs) * 8 + gg) * 4 + tk];
+        st_y(y, static_cast<size_t>(tok) * N + rb0 + rl, y_dtype, tot);
+      }
+    }
+    __syncthreads();  // (C)
+  }
+  if (!ok && lane == 0) report_device_error(err_word, UB_ERR_TIMEOUT);
+}
+
+template <typename XT, int MQ>
+int launch_q8_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
+  typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ub::tensor_map_encoder());
+  // whole 64-block chunks (rows are then whole 128-byte lines) and a 16-byte aligned base for the tensor map
+  if (!enc || K % (32 * kQ8ChunkBlocks) != 0 || (reinterpret_cast<uintptr_t>(wq) & 15)) return UB_ERR_UNSUPPORTED;
+  const int nblk = K / 32;
+  const size_t fixed = static_cast<size_t>(MQ) * nblk * (256 + 16);
+  if (fixed + 2 * static_cast<size_t>(kQ8StageBytes) > kSmemBudget) return UB_ERR_UNSUPPORTED;
+  int S = static_cast<int>((kSmemBudget - fixed) / kQ8StageBytes);
+  if (S > kMaxStages) S = kMaxStages;
+  const size_t red_bytes = static_cast<size_t>(kCW) * 7 * MQ * 64 * sizeof(float);
+  if (static_cast<size_t>(S) * kQ8StageBytes < red_bytes) return UB_ERR_UNSUPPORTED;
+  CUtensorMap wmap;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(nblk) * UB_Q8_0_BYTES;
+  const cuuint64_t dims[3] = {128, row_bytes / 128, static_cast<cuuint64_t>(N)};
+  const cuuint64_t strides[2] = {128, row_bytes};
+  const cuuint32_t box[3] = {128, static_cast<cuuint32_t>(kQ8RowStride / 128), 16};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(wq), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return UB_ERR_UNSUPPORTED;
+  const size_t smem = static_cast<size_t>(S) * kQ8StageBytes + fixed + 1024;
+  auto kernel = qgemv_q8_0_imma_kernel<XT, MQ>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  const int sms = ub::num_sms();
+  const int tiles = (N + 15) / 16;
+  const int grid = tiles < sms ? tiles : sms;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kImmaThreads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, x, y, M, N, K, y_dtype, S, ub::device_error_word(), wmap);
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  return ub::check_launch();
+}
+
 }  // namespace
 
 namespace ub {
@@ -526,6 +786,16 @@ int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int
   return launch_imma<XT, 4>(w, x, y, M, N, K, y_dtype, s);
 }
 
+// Q8_0 flavour, same contract.
+template <typename XT>
+int q8_0_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
+  const uint8_t* w = static_cast<const uint8_t*>(wq);
+  if (M <= 4) return launch_q8_imma<XT, 1>(w, x, y, M, N, K, y_dtype, s);
+  return launch_q8_imma<XT, 2>(w, x, y, M, N, K, y_dtype, s);
+}
+
+template int q8_0_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, cudaStream_t);
+template int q8_0_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, cudaStream_t);
 template int q4k_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, cudaStream_t);
 template int q4k_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, cudaStream_t);
 
