@@ -133,6 +133,13 @@ class Control:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX, group=self.group)
         return float(t.item())
 
+    def all_gather(self, obj):
+        if self.world == 1:
+            return [obj]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, obj, group=self.group)
+        return out
+
     def broadcast(self, obj):
         box = [obj]
         if self.world > 1:
@@ -394,8 +401,18 @@ def run_sharded(args, wl, rank, world, torch, dist):
         comm = eccl.Comm.from_rank(rank, world, eccl.Id(uid))
         note("communicator ready")
 
+        # messages of a few KB (the decode path) go through the one-shot peer-memory kernel, larger ones
+        # through NCCL; UB_BENCH_ALLREDUCE=nccl forces NCCL for comparison
+        oneshot_limit = 0 if os.environ.get("UB_BENCH_ALLREDUCE") == "nccl" else 65536
+        oneshot = eccl.OneShotAllReduce(dev, rank, world, oneshot_limit, CTL.all_gather) if oneshot_limit else None
+        CTL.barrier()
+        note("peer staging buffers open")
+
         def all_reduce(buf, count):
-            comm.all_reduce(buf, buf, count, eccl.Bfloat16, eccl.ReduceOp.Sum, stream=dev.stream)
+            if oneshot is not None and count * 2 <= oneshot_limit and count % 8 == 0:
+                oneshot.all_reduce(buf, count)
+            else:
+                comm.all_reduce(buf, buf, count, eccl.Bfloat16, eccl.ReduceOp.Sum, stream=dev.stream)
 
     rng = np.random.default_rng(wl["seed"] + 17 * rank)
     q4 = lambda n, k: o.gen_q4k_weight(rng, n, k).reshape(-1)  # noqa: E731
@@ -554,11 +571,15 @@ def run_sharded(args, wl, rank, world, torch, dist):
         gc.collect()
         CTL.barrier()
         note("graphs released")
+        if oneshot is not None:
+            oneshot.close()
         comm.destroy()
         note("communicator destroyed")
     return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
                 dtype="u4+f16 scales -> f32 accumulate", ncopies=ncopies,
-                launch_mode="cuda graph" if use_graph else "eager")
+                launch_mode="cuda graph" if use_graph else "eager",
+                allreduce=("one-shot peer-memory kernel up to 64 KB, NCCL above" if world > 1 and oneshot_limit
+                           else ("NCCL" if world > 1 else "none")))
 
 
 def main():
@@ -635,6 +656,7 @@ def main():
             if "launch_mode" in res:
                 config["launch_mode"] = res["launch_mode"]
                 config["weight_copies"] = res["ncopies"]
+                config["allreduce"] = res["allreduce"]
             line = {"metric": metric, "value": res["value"], "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
                     "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
                     "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": res["dtype"],

@@ -208,6 +208,25 @@ int ub_fused_moe_q4k_gemm(void* C, const void* A, const void* Bq, const float* t
 size_t ub_moe_layer_q4k_workspace_bytes(int T, int H, int I, int E, int top_k, int block_size);
 int ub_moe_layer_q4k(void* out, const void* hidden, const void* router_logits, const void* w13q, const void* w2q, const int32_t* expert_map, int T, int H, int I, int E, int top_k, int block_size, int norm_topk_prob, void* workspace, size_t ws_bytes, void* stream);
 
+/* ------------------------------------------------------------------ one-shot all-reduce over peer memory
+ * No reference counterpart as an entry point: it stands where the reference's caller issues ecclAllReduce
+ * (src/eccl.rs:209-245) after a row-split matmul, for messages of a few KB where a library all-reduce is
+ * latency bound.  Every rank allocates one staging buffer of
+ * ub_allreduce_oneshot_staging_bytes(world, max_bytes) with ub_p2p_alloc and makes it reachable from its peers: other processes
+ * open it through ub_ipc_get_handle / ub_ipc_open_handle (64-byte handle shipped out of band), threads of one
+ * process call ub_enable_peer_access and use the pointer itself.  `staging` is a host array of `world` device
+ * pointers in rank order (own buffer at [rank]).  data (bf16, count % 8 == 0, 16-byte aligned, count*2 <=
+ * max_bytes) is summed in place over the ranks, in rank order, on every rank.  All ranks must issue the same
+ * sequence of calls.  The wait for the peers is bounded (UB_ERR_TIMEOUT in the device error word). */
+int ub_p2p_alloc(size_t bytes, void** out_ptr);   /* zero-filled, mappable by peers (cudaMalloc, synchronous) */
+int ub_p2p_free(void* ptr);
+int ub_ipc_get_handle(void* dev_ptr, void* handle64);
+int ub_ipc_open_handle(const void* handle64, void** out_ptr);
+int ub_ipc_close_handle(void* ptr);
+int ub_enable_peer_access(int peer_device);
+size_t ub_allreduce_oneshot_staging_bytes(int world, size_t max_bytes);
+int ub_allreduce_oneshot_bf16(void* data, size_t count, void* const* staging, int rank, int world, size_t max_bytes, void* stream);
+
 /* ------------------------------------------------------------------ collectives
  * ECCL-shaped surface (src/eccllib.rs:7-169, src/eccl.rs:14-426) forwarding to NCCL over
  * NVLink.  Types and enum values below are ECCL's names with NCCL's layout.  The NCCL

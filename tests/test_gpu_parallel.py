@@ -127,3 +127,52 @@ def test_ep_layer_matches_the_unsharded_oracle():
     for r in range(world):
         assert o.rel_l2(got[r], want) < 1e-2
     assert np.array_equal(got[0], got[1])
+
+
+def test_oneshot_all_reduce_matches_rank_ordered_sum():
+    """Peer-memory all-reduce: every rank ends with the f32 sum of the ranks' bf16 vectors in rank order,
+    rounded once, over several rounds (both slot sets are reused) and two sizes."""
+    world = _world()
+    barrier = threading.Barrier(world)
+    shared = [None] * world
+    rng = np.random.default_rng(500)
+    rounds, counts = 5, [8192, 64]
+    data = [[[o.gen_activation(rng, 1, c, True).reshape(-1) for _ in range(world)] for c in counts]
+            for _ in range(rounds)]
+
+    def rank_main(r):
+        d = ub.GcuDevice(r)
+        d.bind_to_thread()
+
+        def exchange(obj):
+            shared[r] = obj
+            barrier.wait()
+            out = list(shared)
+            barrier.wait()
+            return out
+
+        ar = eccl.OneShotAllReduce(d, r, world, 16384, exchange, same_process=True)
+        barrier.wait()  # every staging buffer is zeroed and every peer enabled
+        outs = []
+        for k in range(rounds):
+            for ci, c in enumerate(counts):
+                buf = d.htod_sync_copy(o.f32_to_bf16_bits(data[k][ci][r]))
+                ar.all_reduce(buf, c)
+                d.synchronize()
+                outs.append(d.dtoh_sync_copy(buf, np.uint16))
+        assert d.device_status() == 0
+        barrier.wait()
+        ar.close()
+        return outs
+
+    got = _run_ranks(world, rank_main)
+    i = 0
+    for k in range(rounds):
+        for ci, c in enumerate(counts):
+            acc = np.zeros(c, dtype=np.float32)
+            for r in range(world):
+                acc = acc + _bf16(data[k][ci][r])
+            want = o.f32_to_bf16_bits(acc)
+            for r in range(world):
+                assert np.array_equal(got[r][i][:c], want)
+            i += 1

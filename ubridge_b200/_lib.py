@@ -70,6 +70,14 @@ _SIGS = {
     "ub_memcpy_dtoh": (c_int, [_P, _P, _P, c_size_t]),
     "ub_memcpy_dtod": (c_int, [_P, _P, _P, c_size_t]),
     "ub_memcpy_dtod_2d": (c_int, [_P, _P, c_size_t, _P, c_size_t, c_size_t, c_size_t]),
+    "ub_p2p_alloc": (c_int, [c_size_t, ctypes.POINTER(_P)]),
+    "ub_p2p_free": (c_int, [_P]),
+    "ub_ipc_get_handle": (c_int, [_P, _P]),
+    "ub_ipc_open_handle": (c_int, [_P, ctypes.POINTER(_P)]),
+    "ub_ipc_close_handle": (c_int, [_P]),
+    "ub_enable_peer_access": (c_int, [c_int]),
+    "ub_allreduce_oneshot_staging_bytes": (c_size_t, [c_int, c_size_t]),
+    "ub_allreduce_oneshot_bf16": (c_int, [_P, c_size_t, ctypes.POINTER(_P), c_int, c_int, c_size_t, _P]),
     "ub_synchronize": (c_int, [_P]),
     "ub_get_function": (_P, [c_char_p, c_char_p]),
     "ub_has_function": (c_int, [c_char_p, c_char_p]),

@@ -147,3 +147,61 @@ class Comm:
         if self._comm:
             lib().ecclCommAbort(self._comm)
             self._comm = None
+
+
+class OneShotAllReduce:
+    """In-place bf16 sum over the ranks for small vectors, pushed over peer memory in one kernel
+    (``ub_allreduce_oneshot_bf16``): the exchange after a row-split decode matmul, where the reference calls
+    ``all_reduce`` (src/eccl.rs:209-245) and a library all-reduce is latency bound.
+
+    ``exchange(obj)`` must return the list of every rank's ``obj`` in rank order (an all-gather over any
+    out-of-band channel: a CPU process group, a shared list between threads).  With ``same_process`` the
+    ranks are threads of one process: the peers' pointers are used directly after enabling peer access;
+    otherwise the staging buffers are opened through IPC handles.  After construction every rank must pass
+    a barrier of the caller's before the first ``all_reduce`` (all staging buffers zeroed and mapped)."""
+
+    def __init__(self, dev, rank: int, world: int, max_bytes: int, exchange, same_process: bool = False):
+        self.dev, self.rank, self.world, self.max_bytes = dev, rank, world, (max_bytes + 15) // 16 * 16
+        nbytes = lib().ub_allreduce_oneshot_staging_bytes(world, self.max_bytes)
+        if nbytes == 0:
+            raise EcclError(4, "ub_allreduce_oneshot_staging_bytes")
+        ptr = ctypes.c_void_p()
+        _lib.check(lib().ub_p2p_alloc(nbytes, ctypes.byref(ptr)), "ub_p2p_alloc")  # on the thread's current device
+        self._staging_ptr = ptr.value
+        self._opened = []
+        if same_process:
+            infos = exchange((dev.ordinal, self._staging_ptr))
+            ptrs = []
+            for r, (ordinal, ptr) in enumerate(infos):
+                if r != rank:
+                    _lib.check(lib().ub_enable_peer_access(ordinal), "ub_enable_peer_access")
+                ptrs.append(ptr)
+        else:
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(lib().ub_ipc_get_handle(ctypes.c_void_p(self._staging_ptr), handle), "ub_ipc_get_handle")
+            handles = exchange(handle.raw)
+            ptrs = []
+            for r, raw in enumerate(handles):
+                if r == rank:
+                    ptrs.append(self._staging_ptr)
+                    continue
+                out = ctypes.c_void_p()
+                _lib.check(lib().ub_ipc_open_handle(ctypes.create_string_buffer(raw, 64), ctypes.byref(out)),
+                           "ub_ipc_open_handle")
+                self._opened.append(out.value)
+                ptrs.append(out.value)
+        self._table = (ctypes.c_void_p * world)(*ptrs)
+
+    def all_reduce(self, buf, count: int, stream=None) -> None:
+        _lib.check(lib().ub_allreduce_oneshot_bf16(_p(buf), count, self._table, self.rank, self.world, self.max_bytes,
+                                                   _p(stream if stream is not None else self.dev.stream)),
+                   "ub_allreduce_oneshot_bf16")
+
+    def close(self) -> None:
+        """Call after a barrier: no peer may still be pushing into this rank's buffer."""
+        for p in self._opened:
+            lib().ub_ipc_close_handle(ctypes.c_void_p(p))
+        self._opened = []
+        if self._staging_ptr:
+            lib().ub_p2p_free(ctypes.c_void_p(self._staging_ptr))
+            self._staging_ptr = None
