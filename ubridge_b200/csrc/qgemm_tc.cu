@@ -144,8 +144,11 @@ constexpr int kTcMaxStages = 8;
 constexpr int kTcWStages = 3;                        // most slots a ring of packed weight tiles has
 // Shared-memory plan per token-tile size: the 256-token tile spends its memory on token stages (the
 // copies' latency, not their bandwidth, bounds a K step) and keeps the other two areas small.
-constexpr int tc_wstages(int tok) { return tok > 128 ? 2 : 3; }      // slots of the packed weight ring
-constexpr int tc_stage_tok(int tok) { return tok > 128 ? 64 : (tok < 128 ? tok : 128); }  // staging rows
+// With two CTAs per SM (the producer-bound MoE tiles of up to 128 tokens) every area is halved again.
+constexpr int tc_wstages(int tok, int ctas) { return (tok > 128 || ctas > 1) ? 2 : 3; }  // packed weight ring
+constexpr int tc_stage_tok(int tok, int ctas) {  // staging rows
+  return (tok > 128 || ctas > 1) ? 64 : (tok < 128 ? tok : 128);
+}
 constexpr uint32_t kTcWBytes = 128 * UB_Q4K_BYTES;   // 128 rows x 144 bytes
 
 constexpr int kTcMaxRuns = 256;  // token runs (consecutive alignment blocks of one expert) a grouped launch handles
@@ -178,8 +181,9 @@ struct TcShared {
 // MODE 0: dense y[M,N].  MODE 1 (grouped): weight tile = 64 gate rows + the 64 matching up rows of the run's
 // expert, output act[position, N] = silu(gate) * up.  MODE 2 (grouped): output row sorted_ids[position],
 // multiplied by the routed weight.  In the grouped modes M is the number of positions of A.
-template <int TOK, int STAGES, int MODE>
-__global__ void __launch_bounds__(kTcThreads, 1)
+// CTAS: CTAs per SM the launch is planned for (2: each takes half of the SM's tensor memory and shared memory).
+template <int TOK, int STAGES, int MODE, int CTAS>
+__global__ void __launch_bounds__(kTcThreads, CTAS)
 qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err_word,
                     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                     const TcGroup grp) {
@@ -190,13 +194,15 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   __shared__ int run_dst[MODE == 2 ? TOK : 1];
   static_assert(STAGES <= kTcMaxStages, "barrier arrays");
   constexpr uint32_t kBBytes = TOK * 128;              // TOK token rows x 64 bf16
-  constexpr int kStageTok = tc_stage_tok(TOK);         // tokens the output staging tile holds
-  constexpr int kWStages = tc_wstages(TOK);
+  constexpr int kStageTok = tc_stage_tok(TOK, CTAS);   // tokens the output staging tile holds
+  constexpr int kWStages = tc_wstages(TOK, CTAS);
   constexpr uint32_t kStagingOff = STAGES * kBBytes;   // [kStageTok tokens][128 weight rows] bf16
   constexpr uint32_t kWOff = kStagingOff + kStageTok * 256;  // packed weight ring: [128 rows][144 bytes] each
-  constexpr int kAccBufs = TOK > 128 ? 1 : 2;          // accumulator buffers in TMEM columns 0..255
+  constexpr int kAccBufs = (TOK > 128 || CTAS > 1) ? 1 : 2;  // accumulator buffers at the start of the allocation
   constexpr uint32_t kAccStride = 128;
-  constexpr uint32_t kATmemCol = 256;                  // first TMEM column of the weight stages (32 each)
+  constexpr uint32_t kTmemCols = CTAS > 1 ? 256 : 512;        // columns this CTA allocates
+  constexpr uint32_t kATmemCol = CTAS > 1 ? 128 : 256;        // first column of the weight stages (32 each)
+  static_assert(TOK * kAccBufs <= static_cast<int>(kATmemCol) && kATmemCol + 32 * STAGES <= kTmemCols, "TMEM plan");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this round-up
   const uint32_t smem_raw = static_cast<uint32_t>(__cvta_generic_to_shared(tc_smem));
@@ -273,7 +279,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   __syncthreads();
   if (warp == 0) {
     const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(&sh.tmem_base));
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(512u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -587,7 +593,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   if (threadIdx.x == 0 && sh.abort_flag) report_device_error(err_word, UB_ERR_TIMEOUT);
   if (warp == 0) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -611,13 +617,13 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int TOK, int STAGES, int MODE>
+template <int TOK, int STAGES, int MODE, int CTAS = 1>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const TcGroup& grp, int w_rows_total,
               cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(tc_stage_tok(TOK)) * 256 +
-                      static_cast<size_t>(tc_wstages(TOK)) * kTcWBytes + 1024;
+  const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(tc_stage_tok(TOK, CTAS)) * 256 +
+                      static_cast<size_t>(tc_wstages(TOK, CTAS)) * kTcWBytes + 1024;
   const int sms = ub::num_sms();
-  int grid = sms;  // grouped launches learn their tile count on the device; idle CTAs leave at once
+  int grid = sms * CTAS;  // grouped launches learn their tile count on the device; idle CTAs leave at once
   if (MODE == 0) {
     const int tiles = ((N + 127) / 128) * ((M + TOK - 1) / TOK);
     grid = tiles < sms ? tiles : sms;
@@ -647,7 +653,7 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ub::fail(UB_ERR_UNSUPPORTED);
-  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE>;
+  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
@@ -720,9 +726,9 @@ int q4k_moe_gemm_tc(void* C, const void* A, const void* Bq, const float* topk_w,
   // token runs are capped at the tile's token count: short runs (few tokens per expert) take the 128 tile
   const bool small = num_valid / (E > 0 ? E : 1) <= 128;
   if (act_silu_mul)
-    return small ? launch_tc<128, 6, 1>(C, A, Bq, positions, N, K, g, rows_total, s)
+    return small ? launch_tc<128, 3, 1, 2>(C, A, Bq, positions, N, K, g, rows_total, s)
                  : launch_tc<256, 5, 1>(C, A, Bq, positions, N, K, g, rows_total, s);
-  return small ? launch_tc<128, 6, 2>(C, A, Bq, positions, N, K, g, rows_total, s)
+  return small ? launch_tc<128, 3, 2, 2>(C, A, Bq, positions, N, K, g, rows_total, s)
                : launch_tc<256, 5, 2>(C, A, Bq, positions, N, K, g, rows_total, s);
 }
 
