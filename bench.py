@@ -228,7 +228,7 @@ WORKLOADS = {
 def run_linear(args, wl, rank, world, torch, dist):
     """Replicated (data-parallel, weak scaling) linear workloads: every rank streams its own copies."""
     import ubridge_b200 as ub
-    from oracle import oracle as o  # input generation only; nothing of it is timed here
+    from ubridge_b200 import synth as o  # seeded synthetic inputs
     from ubridge_b200 import ops
 
     dev_index = int(os.environ.get("LOCAL_RANK", "0"))
@@ -380,7 +380,7 @@ def run_sharded(args, wl, rank, world, torch, dist):
     """Tensor-parallel (c5) and expert-parallel (c4) workloads: the matrices are split over the ranks, every
     rank streams its shard and the partial outputs meet in NCCL all-reduces (strong scaling)."""
     import ubridge_b200 as ub
-    from oracle import oracle as o  # input generation only
+    from ubridge_b200 import synth as o  # seeded synthetic inputs
     from ubridge_b200 import eccl, parallel
 
     dev_index = int(os.environ.get("LOCAL_RANK", "0"))
