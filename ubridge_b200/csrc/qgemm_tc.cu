@@ -204,7 +204,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   constexpr uint32_t kATmemCol = CTAS > 1 ? 128 : 256;        // first column of the weight stages (32 each)
   static_assert(TOK * kAccBufs <= static_cast<int>(kATmemCol) && kATmemCol + 32 * STAGES <= kTmemCols, "TMEM plan");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this round-up
+  // the swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for rounding the base up
   const uint32_t smem_raw = static_cast<uint32_t>(__cvta_generic_to_shared(tc_smem));
   const uint32_t smem_base = (smem_raw + 1023u) & ~1023u;
   unsigned char* const tiles = tc_smem + (smem_base - smem_raw);

@@ -155,7 +155,7 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
                       int K, int y_dtype, int S, int* err_word, int use_tm, const __grid_constant__ CUtensorMap w_map) {
   constexpr int kMT = imma_mt(MP);
   extern __shared__ __align__(128) unsigned char ismem_raw[];
-  // swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this round-up
+  // swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for rounding the base up
   unsigned char* const ismem =
       ismem_raw + ((1024u - (static_cast<uint32_t>(__cvta_generic_to_shared(ismem_raw)) & 1023u)) & 1023u);
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStages];  // full[S], empty[S]
