@@ -18,7 +18,7 @@
 // dots are exact; they meet the 6-bit scales in integer arithmetic, the mins through dp4a against the
 // sub-block sums of q, and turn into f32 once per (row, super-block).
 //
-// Data movement.  One persistent CTA per SM owns a contiguous range of rows.  A producer warp streams 16-row
+// Data movement.  One persistent CTA per SM takes the 16-row tiles blockIdx.x, blockIdx.x + gridDim.x, ...  A producer warp streams 16-row
 // tiles into an mbarrier ring; 16 compute warps each own one super-block column of the tile.  A tile is ONE
 // tensor-map copy (rows viewed as lines of 128 bytes, 128-byte swizzle, so that the reads of eight rows fall
 // into distinct banks); issuing a bulk copy costs about 70 ns, so one copy per row would take longer to
@@ -170,11 +170,11 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
   unsigned char* const meta = bfrag + static_cast<size_t>(MP) * nsb * 2048;        // [MP][nsb][4 t] uint4
   float* const red = reinterpret_cast<float*>(ismem);  // aliases the ring between batches
 
-  // rows of this CTA: contiguous, near-even split of N over the grid
-  const int base = N / gridDim.x, rem = N % gridDim.x;
-  const int r0 = blockIdx.x * base + min(static_cast<int>(blockIdx.x), rem);
-  const int nrows = base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
-  const int nbatches = (nrows + 16 * kMT - 1) / (16 * kMT);
+  // 16-row tiles of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
+  const int total_tiles = (N + 15) >> 4;
+  const int my_tiles =
+      static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int nbatches = (my_tiles + kMT - 1) / kMT;
 
   // Programmatic dependent launch: the next kernel in the stream may start as soon as every CTA of this
   // grid has passed this point (its CTAs take over SMs as ours retire, instead of waiting for the whole grid
@@ -303,15 +303,16 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
     mt4 = reinterpret_cast<const uint4*>(meta)[static_cast<size_t>(warp) * 4 + t];
   }
   for (int b = 0; b < nbatches; b++) {
-    const int rb0 = r0 + b * 16 * kMT;
-    const int brow = min(16 * kMT, nrows - b * 16 * kMT);
-    const int n_mt = (brow + 15) >> 4;
+    const int n_mt = min(kMT, my_tiles - b * kMT);
+    // first row of this batch's tile `mt`: tiles are dealt round robin, so that at any moment the grid as a
+    // whole reads one contiguous window of the matrix
+    auto tile_row0 = [&](int mt) { return 16 * (static_cast<int>(blockIdx.x) + (b * kMT + mt) * static_cast<int>(gridDim.x)); };
 
     float acc[kMT][MP][2];  // consumers: partial sums of rows (g, g + 8) of each tile, per token pair
     if (warp == kCW) {
       // ---- producer: 16-row tiles, one bulk copy per row ----
       for (int mt = 0; mt < n_mt; mt++) {
-        const int rows_here = min(16, brow - 16 * mt);
+        const int rows_here = min(16, N - tile_row0(mt));
         for (int c = 0; c < nchunks; c++, it++) {
           const int slot = it % S, round = it / S;
           if (ok && round > 0) ok = ib_wait(bars_s + 8 * (kMaxStages + slot), (round - 1) & 1);
@@ -329,7 +330,7 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
                   "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
                   "%5}], [%2];" ::"r"(ring_s + slot * geo.stage_bytes),
                   "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(full), "r"(0), "r"(c * (geo.row_stride >> 7)),
-                  "r"(rb0 + 16 * mt)
+                  "r"(tile_row0(mt))
                   : "memory");
             }
             continue;
@@ -338,7 +339,7 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
           __syncwarp();
           if (lane < rows_here)
             ib_copy(ring_s + slot * geo.stage_bytes + lane * geo.row_stride,
-                    wq + static_cast<size_t>(rb0 + 16 * mt + lane) * row_bytes +
+                    wq + static_cast<size_t>(tile_row0(mt) + lane) * row_bytes +
                         static_cast<size_t>(c) * kChunkSb * UB_Q4K_BYTES,
                     cbytes, full);
         }
@@ -446,12 +447,13 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
     if (b == 0 && warp == kCW) asm volatile("griddepcontrol.wait;" ::: "memory");  // before this warp's stores
     for (int o = threadIdx.x; o < n_mt * 16 * 2 * MP; o += kImmaThreads) {
       const int rl = o / (2 * MP), tok = o - rl * (2 * MP);
-      if (rl < brow && tok < M) {
+      const int row = tile_row0(rl >> 4) + (rl & 15);
+      if (row < N && tok < M) {
         const int mt = rl >> 4, rs = (rl >> 3) & 1, gg = rl & 7, p = tok >> 1, tk = tok & 1;
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < kCW; w++) tot += red[((((w * kMT + mt) * MP + p) * 2 + rs) * 8 + gg) * 2 + tk];
-        st_y(y, static_cast<size_t>(tok) * N + rb0 + rl, y_dtype, tot);
+        st_y(y, static_cast<size_t>(tok) * N + row, y_dtype, tot);
       }
     }
     __syncthreads();  // (C) the ring is free again
@@ -552,10 +554,10 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
   float* const xscale = reinterpret_cast<float*>(bfrag + static_cast<size_t>(MQ) * nblk * 256);  // [MQ][nblk][4]
   float* const red = reinterpret_cast<float*>(ismem);
 
-  const int base = N / gridDim.x, rem = N % gridDim.x;
-  const int r0 = blockIdx.x * base + min(static_cast<int>(blockIdx.x), rem);
-  const int nrows = base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
-  const int nbatches = (nrows + 16 * kMT - 1) / (16 * kMT);
+  const int total_tiles = (N + 15) >> 4;
+  const int my_tiles =
+      static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int nbatches = (my_tiles + kMT - 1) / kMT;
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (warp < kCW) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -609,9 +611,10 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
   }
 
   for (int b = 0; b < nbatches; b++) {
-    const int rb0 = r0 + b * 16 * kMT;
-    const int brow = min(16 * kMT, nrows - b * 16 * kMT);
-    const int n_mt = (brow + 15) >> 4;
+    const int n_mt = min(kMT, my_tiles - b * kMT);
+    // first row of this batch's tile `mt`: tiles are dealt round robin, so that at any moment the grid as a
+    // whole reads one contiguous window of the matrix
+    auto tile_row0 = [&](int mt) { return 16 * (static_cast<int>(blockIdx.x) + (b * kMT + mt) * static_cast<int>(gridDim.x)); };
     float acc[kMT][MQ][2];
     if (warp == kCW) {
       for (int mt = 0; mt < n_mt; mt++) {
@@ -627,7 +630,7 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
                 "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
                 "%5}], [%2];" ::"r"(ring_s + slot * kQ8StageBytes),
                 "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(full), "r"(0), "r"(c * (kQ8RowStride >> 7)),
-                "r"(rb0 + 16 * mt)
+                "r"(tile_row0(mt))
                 : "memory");
           }
         }
@@ -709,12 +712,13 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
     if (b == 0 && warp == kCW) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int o = threadIdx.x; o < n_mt * 16 * 4 * MQ; o += kImmaThreads) {
       const int rl = o / (4 * MQ), tok = o - rl * (4 * MQ);
-      if (rl < brow && tok < M) {
+      const int row = tile_row0(rl >> 4) + (rl & 15);
+      if (row < N && tok < M) {
         const int mt = rl >> 4, rs = (rl >> 3) & 1, gg = rl & 7, q = tok >> 2, tk = tok & 3;
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < kCW; w++) tot += red[((((w * kMT + mt) * MQ + q) * 2 + rs) * 8 + gg) * 4 + tk];
-        st_y(y, static_cast<size_t>(tok) * N + rb0 + rl, y_dtype, tot);
+        st_y(y, static_cast<size_t>(tok) * N + row, y_dtype, tot);
       }
     }
     __syncthreads();  // (C)
