@@ -122,8 +122,9 @@ __device__ __forceinline__ void st_y(void* y, size_t idx, int dtype, float v) {
     static_cast<__half*>(y)[idx] = __float2half_rn(v);
 }
 
+// low bytes of four integers -> one word (three byte permutes)
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-  return (a & 255) | ((b & 255) << 8) | ((c & 255) << 16) | (static_cast<uint32_t>(d & 255) << 24);
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 // Shared-memory geometry shared by host and device.
@@ -236,11 +237,15 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
       for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
       const float inv = amax > 0.f ? kXQMax / amax : 0.f;
       const float xs = amax * (1.f / kXQMax);
+      // Round through the mantissa of 1.5 * 2^23 (no conversion instructions: their pipe is narrow and all
+      // sixteen warps are here at once).  q = rint(v inv); hi = rint(v inv / 254) differs from rint(q / 254)
+      // only where q / 254 is within 0.002 of a half, and there both choices leave |lo| <= 127.
+      const float inv254 = inv * (1.f / 254.f);
       int hi[8], lo[8], sum = 0;
 #pragma unroll
       for (int e = 0; e < 8; e++) {
-        const int q = __float2int_rn(v[e] * inv);
-        hi[e] = __float2int_rn(static_cast<float>(q) * (1.f / 254.f));
+        const int q = __float_as_int(fmaf(v[e], inv, 12582912.f)) - 0x4B400000;
+        hi[e] = __float_as_int(fmaf(v[e], inv254, 12582912.f)) - 0x4B400000;
         lo[e] = q - 254 * hi[e];
         sum += q;
       }
@@ -248,8 +253,8 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
       sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);  // sum of q over this lane's 32-value sub-block
       const uint2 hv = make_uint2(pack4(hi[0], hi[1], hi[2], hi[3]), pack4(hi[4], hi[5], hi[6], hi[7]));
       const uint2 lv = make_uint2(pack4(lo[0], lo[1], lo[2], lo[3]), pack4(lo[4], lo[5], lo[6], lo[7]));
-      const uint2 nhv = make_uint2(pack4(-hi[0], -hi[1], -hi[2], -hi[3]), pack4(-hi[4], -hi[5], -hi[6], -hi[7]));
-      const uint2 nlv = make_uint2(pack4(-lo[0], -lo[1], -lo[2], -lo[3]), pack4(-lo[4], -lo[5], -lo[6], -lo[7]));
+      // per-byte negation (no limb is -128, so nothing overflows)
+      const uint2 nhv = make_uint2(__vneg4(hv.x), __vneg4(hv.y)), nlv = make_uint2(__vneg4(lv.x), __vneg4(lv.y));
       if ((j & 1) == 0) {
         f1[(cb + 0) * 4 + tt] = hv;
         f1[(cb + 1) * 4 + tt] = lv;
@@ -596,11 +601,12 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
       amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
       amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));  // over the block's four lanes
       const float inv = amax > 0.f ? kXQMax / amax : 0.f;
+      const float inv254 = inv * (1.f / 254.f);  // rounding through the mantissa of 1.5 * 2^23, as above
       int hi[8], lo[8];
 #pragma unroll
       for (int e = 0; e < 8; e++) {
-        const int q = __float2int_rn(v[e] * inv);
-        hi[e] = __float2int_rn(static_cast<float>(q) * (1.f / 254.f));
+        const int q = __float_as_int(fmaf(v[e], inv, 12582912.f)) - 0x4B400000;
+        hi[e] = __float_as_int(fmaf(v[e], inv254, 12582912.f)) - 0x4B400000;
         lo[e] = q - 254 * hi[e];
       }
       f[col * 4 + tt] = make_uint2(pack4(hi[0], hi[1], hi[2], hi[3]), pack4(hi[4], hi[5], hi[6], hi[7]));
