@@ -176,3 +176,33 @@ def test_oneshot_all_reduce_matches_rank_ordered_sum():
             for r in range(world):
                 assert np.array_equal(got[r][i][:c], want)
             i += 1
+
+
+@pytest.mark.parametrize("M", [1, 5])
+def test_linear_stack_on_one_gpu_chains_dependent_launches(dev, M):
+    """World size 1: four matmuls back to back on one stream, each consuming the previous one's output (the
+    decode kernels start early under programmatic dependent launch and must wait before touching activations)."""
+    hidden, inter, nq, nkv, hd = 2048, 4096, 16, 2, 128
+    rng = np.random.default_rng(600 + M)
+    x = o.gen_activation(rng, M, hidden, True)
+    w_qkv = o.gen_q4k_weight(rng, (nq + 2 * nkv) * hd, hidden)
+    w_o = o.gen_q4k_weight(rng, hidden, nq * hd)
+    w_gate, w_up = o.gen_q4k_weight(rng, inter, hidden), o.gen_q4k_weight(rng, inter, hidden)
+    w_down = o.gen_q4k_weight(rng, hidden, inter)
+    stack = par.TPLinearStack(dev, hidden, inter, nq, nkv, hd, 1, w_qkv.reshape(-1), w_o.reshape(-1),
+                              par.gate_up_column_split(w_gate, w_up, inter, hidden, True, 0, 1), w_down.reshape(-1), M)
+    d_x = dev.htod_sync_copy(o.f32_to_bf16_bits(x).reshape(-1))
+    outs = []
+    for _ in range(3):  # repeated: any race between consecutive launches would show as a difference
+        out = stack.forward(d_x, M)
+        dev.synchronize()
+        outs.append(o.bf16_bits_to_f32(dev.dtoh_sync_copy(out, np.uint16)[:M * hidden]).reshape(M, hidden))
+    assert dev.device_status() == 0
+    q = _bf16(o.qmatmul_exact(x, o.dequant_q4k(w_qkv).reshape(-1, hidden)))[:, :nq * hd]
+    h1 = _bf16(o.qmatmul_exact(q, o.dequant_q4k(w_o).reshape(hidden, nq * hd)))
+    g = _bf16(o.qmatmul_exact(h1, o.dequant_q4k(w_gate).reshape(inter, hidden)))
+    u = _bf16(o.qmatmul_exact(h1, o.dequant_q4k(w_up).reshape(inter, hidden)))
+    act = o.silu_and_mul(np.concatenate([g, u], axis=1), o.UB_BF16)
+    want = o.qmatmul_exact(act, o.dequant_q4k(w_down).reshape(hidden, inter))
+    assert o.rel_l2(outs[0], want) < 1e-2
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
