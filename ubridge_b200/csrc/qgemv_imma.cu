@@ -204,7 +204,15 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
   __syncthreads();
 
   bool ok = true;
-  int it = 0;  // ring items issued / consumed so far (same sequence on both sides)
+  // ring position of the next item (same sequence on the producer and the consumer side), kept as counters:
+  // a division by the run-time ring depth per item would cost more than the item's address arithmetic
+  int slot = 0, round = 0;
+  auto ring_next = [&]() {
+    if (++slot == S) {
+      slot = 0;
+      round++;
+    }
+  };
 
   if (warp < kCW) {
     // ---- activations -> fragments of the B operand, once per launch ----
@@ -318,8 +326,7 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
       // ---- producer: 16-row tiles, one bulk copy per row ----
       for (int mt = 0; mt < n_mt; mt++) {
         const int rows_here = min(16, N - tile_row0(mt));
-        for (int c = 0; c < nchunks; c++, it++) {
-          const int slot = it % S, round = it / S;
+        for (int c = 0; c < nchunks; c++, ring_next()) {
           if (ok && round > 0) ok = ib_wait(bars_s + 8 * (kMaxStages + slot), (round - 1) & 1);
           ok = __all_sync(0xFFFFFFFFu, ok);
           if (!ok) continue;
@@ -359,9 +366,8 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
 #pragma unroll
       for (int mt = 0; mt < kMT; mt++) {
         if (mt < n_mt) {
-          for (int c = 0; c < nchunks; c++, it++) {
-            const int slot = it % S, round = it / S;
-            if (ok) ok = __all_sync(0xFFFFFFFFu, ib_wait(bars_s + 8 * slot, round & 1));
+          for (int c = 0; c < nchunks; c++, ring_next()) {
+              if (ok) ok = __all_sync(0xFFFFFFFFu, ib_wait(bars_s + 8 * slot, round & 1));
             const int cs = min(kChunkSb, nsb - c * kChunkSb);
             if (ok && warp < cs) {
               const int sb = c * kChunkSb + warp;
@@ -577,7 +583,15 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
   __syncthreads();
 
   bool ok = true;
-  int it = 0;
+  // ring position of the next item (same sequence on the producer and the consumer side), kept as counters:
+  // a division by the run-time ring depth per item would cost more than the item's address arithmetic
+  int slot = 0, round = 0;
+  auto ring_next = [&]() {
+    if (++slot == S) {
+      slot = 0;
+      round++;
+    }
+  };
 
   if (warp < kCW) {
     // ---- activations -> B fragments: unit = (token, 256 values); lane i holds 8 values of block i / 4 ----
@@ -624,8 +638,7 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
     float acc[kMT][MQ][2];
     if (warp == kCW) {
       for (int mt = 0; mt < n_mt; mt++) {
-        for (int c = 0; c < nchunks; c++, it++) {
-          const int slot = it % S, round = it / S;
+        for (int c = 0; c < nchunks; c++, ring_next()) {
           if (ok && round > 0) ok = ib_wait(bars_s + 8 * (kMaxStages + slot), (round - 1) & 1);
           ok = __all_sync(0xFFFFFFFFu, ok);
           if (!ok) continue;
@@ -649,9 +662,8 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
 #pragma unroll
       for (int mt = 0; mt < kMT; mt++) {
         if (mt < n_mt) {
-          for (int c = 0; c < nchunks; c++, it++) {
-            const int slot = it % S, round = it / S;
-            if (ok) ok = __all_sync(0xFFFFFFFFu, ib_wait(bars_s + 8 * slot, round & 1));
+          for (int c = 0; c < nchunks; c++, ring_next()) {
+              if (ok) ok = __all_sync(0xFFFFFFFFu, ib_wait(bars_s + 8 * slot, round & 1));
             if (ok) {
               const unsigned char* st = ismem + static_cast<size_t>(slot) * kQ8StageBytes;
               // this warp's four blocks of rows g and g + 8: scales and weight bytes into registers
