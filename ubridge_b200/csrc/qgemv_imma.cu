@@ -89,6 +89,13 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1,
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
 }
+// d = A . B (no accumulator to clear beforehand)
+__device__ __forceinline__ void imma_u8s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint2 b) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "r"(0));
+}
 __device__ __forceinline__ int dp4a_u_s(uint32_t a, uint32_t b, int c) {
   int d;
   asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -408,8 +415,7 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
                 int d[4][4];
 #pragma unroll
                 for (int G = 0; G < 4; G++) {
-                  d[G][0] = d[G][1] = d[G][2] = d[G][3] = 0;
-                  imma_u8s8(d[G], wA[G].x, wB[G].x, wA[G].y, wB[G].y, bq1[G]);
+                  imma_u8s8_first(d[G], wA[G].x, wB[G].x, wA[G].y, wB[G].y, bq1[G]);
                 }
 #pragma unroll
                 for (int G = 0; G < 4; G++)
@@ -539,10 +545,11 @@ constexpr int kQ8ChunkBlocks = 64;
 constexpr int kQ8RowStride = kQ8ChunkBlocks * UB_Q8_0_BYTES;  // 2176
 constexpr int kQ8StageBytes = 16 * kQ8RowStride;              // 34816 = 34 KB
 
+// d = A(16x32 s8, row) . B(32x8 s8, col)
 __device__ __forceinline__ void imma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "r"(0));
 }
 __device__ __forceinline__ uint32_t swz128(uint32_t L) { return L ^ (((L >> 7) & 7u) << 4); }
 
@@ -701,7 +708,7 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
                   const int blk = c * kQ8ChunkBlocks + warp * 4 + i;
                   const uint2 bf = reinterpret_cast<const uint2*>(bfrag)[(static_cast<size_t>(q) * nblk + blk) * 32 + lane];
                   const float xs = xscale[(static_cast<size_t>(q) * nblk + blk) * 4 + t];
-                  int d[4] = {0, 0, 0, 0};
+                  int d[4];
                   imma_s8s8(d, a[i][0], a[i][1], a[i][2], a[i][3], bf);
                   // columns 2t, 2t+1 = token t's high and low limb
                   acc[mt][q][0] = fmaf(static_cast<float>(d[0] * 254 + d[1]), dA[i] * xs, acc[mt][q][0]);
