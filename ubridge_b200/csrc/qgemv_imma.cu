@@ -18,8 +18,9 @@
 // dots are exact; they meet the 6-bit scales in integer arithmetic, the mins through dp4a against the
 // sub-block sums of q, and turn into f32 once per (row, super-block).
 //
-// Data movement.  One persistent CTA per SM takes the 16-row tiles blockIdx.x, blockIdx.x + gridDim.x, ...  A producer warp streams 16-row
-// tiles into an mbarrier ring; 16 compute warps each own one super-block column of the tile.  A tile is ONE
+// Data movement.  One persistent CTA per SM takes the 16-row tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+// (the grid as a whole sweeps the matrix linearly).  A producer warp streams the tiles into an mbarrier
+// ring; 16 compute warps each own one super-block column of the tile.  A tile is ONE
 // tensor-map copy (rows viewed as lines of 128 bytes, 128-byte swizzle, so that the reads of eight rows fall
 // into distinct banks); issuing a bulk copy costs about 70 ns, so one copy per row would take longer to
 // issue than the data takes to arrive.  Rows that are not a multiple of 128 bytes fall back to per-row
