@@ -190,6 +190,16 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
   // to drain), and this kernel may itself have been started early: everything up to the wait below touches
   // only shared memory; the weights, which no kernel writes, are requested by the producer warp right away.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // The ring's barriers come first, and with them the only CTA-wide barrier before the main loop: the
+  // producer warp must not be held back by the compute warps' wait for the previous kernel.
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      ib_init(bars_s + 8 * s, 1);
+      ib_init(bars_s + 8 * (kMaxStages + s), kCW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
   if (warp < kCW) asm volatile("griddepcontrol.wait;" ::: "memory");  // activations may come from the previous kernel
   // the first activation piece of this warp is requested before anything else: its latency is on the
   // critical path of the whole launch
@@ -202,14 +212,6 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
     for (int e = 0; e < 8; e++) v_first[e] = 0.f;
   }
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < S; s++) {
-      ib_init(bars_s + 8 * s, 1);
-      ib_init(bars_s + 8 * (kMaxStages + s), kCW);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
 
   bool ok = true;
   // ring position of the next item (same sequence on the producer and the consumer side), kept as counters:
@@ -579,8 +581,7 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
   const int nbatches = (my_tiles + kMT - 1) / kMT;
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (warp < kCW) asm volatile("griddepcontrol.wait;" ::: "memory");
-
+  // barriers first (see the Q4_K kernel): the producer warp starts streaming while the compute warps wait
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) {
       ib_init(bars_s + 8 * s, 1);
@@ -589,6 +590,7 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (warp < kCW) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   bool ok = true;
   // ring position of the next item (same sequence on the producer and the consumer side), kept as counters:
