@@ -302,7 +302,8 @@ def run_linear(args, wl, rank, world, torch, dist):
             n += 1
         return n
     if is_q4k:
-        launches_per_call = (M + 7) // 8 if M <= 16 else 1  # decode kernel: up to eight rows per pass
+        # decode kernel: up to eight rows per pass; bf16 in and out from nine rows on: one tensor-core launch
+        launches_per_call = 1 if M > 16 or (M > 8 and wl["x_bf16"]) else (M + 7) // 8
     else:
         launches_per_call = decode_launches(M)
     launches = args.steps * copies * passes * launches_per_call

@@ -139,8 +139,9 @@ int ub_repack_to_interleaved(void* interleaved, const void* split, size_t nblock
  * matmul_* (kernels/matmul.cpp:1143-1184; small-M shape in
  * kernels/third_party/matmul_decoding.h:12-570).  The suffix names the activation type;
  * out_dtype is UB_DTYPE_F32 / UB_DTYPE_BF16 / UB_DTYPE_F16.  M <= 16 runs the
- * bandwidth-bound decode kernel, larger M the tensor-core kernel (Q4_K) — see
- * ub_qmatmul_workspace_bytes for the scratch each needs (0 for the decode kernel). */
+ * bandwidth-bound decode kernel (Q4_K with bf16 activations and bf16 output: M <= 8), larger M
+ * the tensor-core kernel (Q4_K) — see ub_qmatmul_workspace_bytes for the scratch each needs
+ * (0 whenever M <= 16). */
 size_t ub_qmatmul_workspace_bytes(int M, int N, int K, int is_q4k);
 int ub_qmatmul_q8_0_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 int ub_qmatmul_q8_0_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);

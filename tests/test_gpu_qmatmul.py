@@ -59,8 +59,12 @@ def test_config2_q4k_small_batch(dev, M):
     got32 = _run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_F32)
     assert o.rel_l2(got32, want) < TOL_DECODE
     got16 = _run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_BF16)
-    assert np.array_equal(got16, o.round_through(got32, o.UB_BF16))  # output rounding is the only difference
-    assert o.rel_l2(got16, want) < 4e-3  # bf16 storage of y alone costs ~2e-3
+    if M <= 8:
+        assert np.array_equal(got16, o.round_through(got32, o.UB_BF16))  # output rounding is the only difference
+        assert o.rel_l2(got16, want) < 4e-3  # bf16 storage of y alone costs ~2e-3
+    else:  # bf16 in and out from nine tokens on: the tensor-core kernel (weights rounded to bf16 once)
+        assert o.rel_l2(got16, want) < TOL_TENSOR
+        assert o.rel_l2(got16, want) < 5e-3
 
 
 @pytest.mark.parametrize("is_q4k", [False, True])
@@ -72,6 +76,18 @@ def test_decode_odd_shapes(dev, is_q4k, x_dtype, M, N, K):
     x = o.gen_activation(rng, M, K, x_dtype == DTYPE_BF16)
     got = _run(dev, w, x, M, N, K, is_q4k, x_dtype, DTYPE_F32)
     assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, is_q4k)) < TOL_DECODE
+
+
+@pytest.mark.parametrize("M,N,K", [(9, 33, 768), (12, 257, 2048), (16, 130, 1024)])
+def test_q4k_bf16_nine_to_sixteen_tokens(dev, M, N, K):
+    """bf16 in and out with 9..16 tokens: one tensor-core launch, no workspace; other types keep the decode kernel."""
+    rng = np.random.default_rng(M * 1000 + N)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    want = o.c_qmatmul(x, w, N, K, True)
+    assert ops.qmatmul_workspace_bytes(M, N, K, True) == 0
+    assert o.rel_l2(_run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_BF16), want) < TOL_TENSOR
+    assert o.rel_l2(_run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_F32), want) < TOL_DECODE
 
 
 def test_q8_0_k_not_multiple_of_256(dev):

@@ -4,6 +4,8 @@
 // small-M special cases :502-514) and kernels/matmul.cpp:1197-1208 (LHS-resident decode kernel when it
 // fits, batched kernel otherwise).  The same idea here is a three-way split on M:
 //   M <= 16           bandwidth-bound decode GEMV (qgemv.cu), f32 or bf16 activations, no workspace;
+//                     from M = 9 on, Q4_K with bf16 activations AND bf16 output takes the tensor-core kernel
+//                     instead (one pass of it is faster than two passes of eight tokens; no workspace either);
 //   M  > 16, Q4_K     tcgen05 tensor-core GEMM with in-kernel dequantisation (bf16 activations and output;
 //                     other types are converted through the caller's workspace);
 //   M  > 16, Q8_0     the decode kernel in passes of four rows.
@@ -21,6 +23,7 @@ int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cud
 namespace {
 
 constexpr int kDecodeMaxM = 16;
+constexpr int kDecodeOnePassM = 8;  // tokens one launch of the decode kernel covers
 
 __global__ void convert_f32_to_bf16_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ in, size_t n) {
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
@@ -58,6 +61,10 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
     return ub::fail(UB_ERR_INVALID_ARG);
   cudaStream_t s = ub::as_stream(stream);
 
+  if (is_q4k && M > kDecodeOnePassM && M <= kDecodeMaxM && x_dtype == UB_DTYPE_BF16 && out_dtype == UB_DTYPE_BF16) {
+    const int st = ub::q4k_gemm_tc(y, x, wq, M, N, K, s);
+    if (st != UB_ERR_UNSUPPORTED) return st;  // unsupported shape or driver: the decode kernel below
+  }
   if (M <= kDecodeMaxM || !is_q4k) {
     if (x_dtype == UB_DTYPE_F32)
       return ub::qgemv<float>(is_q4k, y, static_cast<const float*>(x), wq, M, N, K, out_dtype, s);
