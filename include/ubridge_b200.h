@@ -132,6 +132,17 @@ int ub_quantize_q8_0(void* blocks, const void* x, size_t numel, int in_dtype, vo
 int ub_repack_to_split(void* split, const void* interleaved, size_t nblocks, int is_q4k, void* stream);
 int ub_repack_to_interleaved(void* interleaved, const void* split, size_t nblocks, int is_q4k, void* stream);
 
+/* ------------------------------------------------------------------ GGUF Q6_K
+ * The reference declares block_q6_K (kernels/quant.cpp:170-177: ql[128], qh[64], int8 scales[16],
+ * f16 d; 210 bytes per 256 weights) and ships no kernel for it; Q4_K_M model files hold their
+ * output and embedding matrices in it.  Blocks are interleaved as in a .gguf file, 2-byte aligned.
+ * ub_dequant_q6k: the f32 value (d*scale)*(q-32) rounded once to out_dtype, bit-exact.
+ * ub_qmatmul_q6k_*: y[M,N] = x[M,K] . W^T with W = N rows of K/256 blocks, f32 accumulation, a
+ * weight-streaming decode kernel that takes the tokens four at a time (any M, no workspace). */
+int ub_dequant_q6k(void* out, const void* blocks, size_t numel, int out_dtype, void* stream);
+int ub_qmatmul_q6k_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* stream);
+int ub_qmatmul_q6k_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* stream);
+
 /* ------------------------------------------------------------------ fused quantized matmul
  * y[M,N] = x[M,K] . W^T, W given as N rows of K/32 (Q8_0) or K/256 (Q4_K) interleaved GGUF
  * blocks; f32 accumulation.  The reference reaches the same result with two kernels and a

@@ -17,6 +17,8 @@ pinned bit-exactly against ``gguf.quants.dequantize`` and hand-computed blocks.
 
 Reference locations (paths inside the reference project):
   formats               kernels/quant.cpp:50-51,98-104,145-150,356-363,392-412
+  Q6_K block layout     kernels/quant.cpp:170-177 (declared there, never implemented: the arithmetic is the
+                        published GGML one, pinned against the ``gguf`` python package)
   q8_0 quantize         kernels/quant.cpp:270-292
   topk_softmax          kernels/topk_softmax_host.cpp:121-172
   moe_align_block_size  kernels/moe_align_host.cpp:51-58,587-764,766-935
@@ -36,6 +38,7 @@ QK8_0 = 32
 QK_K = 256
 Q8_0_BYTES = 34
 Q4K_BYTES = 144
+Q6K_BYTES = 210
 
 # dtype codes of the reference's DATATYPE enum (src/lib.rs:87-106)
 UB_F16, UB_BF16, UB_F32 = 4, 5, 8
@@ -134,6 +137,38 @@ def dequant_q4k(blocks: np.ndarray) -> np.ndarray:
     qs = b[..., 16:].reshape(lead + (4, 1, 32))
     q = np.concatenate([qs & 0xF, qs >> 4], axis=-2).astype(np.float32)  # [..., 4, 2, 32]
     return (dsc * q - dmn).reshape(lead + (QK_K,)).astype(np.float32)
+
+
+def pack_q6k(d_f16: np.ndarray, scales_i8: np.ndarray, q: np.ndarray) -> np.ndarray:
+    """d [...] f16, scales [..., 16] int8, q [..., 256] in 0..63 -> bytes [..., 210] = ql[128] qh[64] scales[16] d.
+    Value i of a super-block (half h = i // 128, j = (i % 128) // 32, l = i % 32): low nibble in
+    ql[64h + 32(j & 1) + l] (high half of the byte when j >= 2), upper two bits at bit 2j of qh[32h + l]."""
+    q = np.asarray(q, dtype=np.uint8)
+    lead = q.shape[:-1]
+    qv = q.reshape(lead + (2, 4, 32))
+    ql = np.zeros(lead + (2, 2, 32), dtype=np.uint8)
+    qh = np.zeros(lead + (2, 32), dtype=np.uint8)
+    for j in range(4):
+        ql[..., :, j & 1, :] |= (qv[..., :, j, :] & 0xF) << (4 if j >= 2 else 0)
+        qh |= (qv[..., :, j, :] >> 4) << (2 * j)
+    d = np.ascontiguousarray(d_f16, dtype=np.float16).reshape(lead + (1,)).view(np.uint8)
+    sc = np.ascontiguousarray(scales_i8, dtype=np.int8).view(np.uint8).reshape(lead + (16,))
+    return np.concatenate([ql.reshape(lead + (128,)), qh.reshape(lead + (64,)), sc, d], axis=-1)
+
+
+def dequant_q6k(blocks: np.ndarray) -> np.ndarray:
+    """bytes [..., 210] -> f32 [..., 256]; y = (d * scale[i // 16]) * (q - 32), q the 6-bit value."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8)
+    lead = b.shape[:-1]
+    ql = b[..., 0:128].reshape(lead + (2, 2, 32))
+    qh = b[..., 128:192].reshape(lead + (2, 1, 32))
+    sc = b[..., 192:208].copy().view(np.int8).astype(np.float32)
+    d = b[..., 208:210].copy().view(np.float16).astype(np.float32)
+    lo = np.concatenate([ql & 0xF, ql >> 4], axis=-2)  # [..., 2, 4, 32]: j = 0..3
+    hi = (qh >> np.array([0, 2, 4, 6], dtype=np.uint8).reshape(4, 1)) & 3
+    q = (lo | (hi << 4)).astype(np.int8).astype(np.float32) - np.float32(32)
+    dsc = (d * sc).reshape(lead + (16, 1))
+    return (dsc * q.reshape(lead + (16, 16))).reshape(lead + (QK_K,)).astype(np.float32)
 
 
 def split_layout(inter: np.ndarray, is_q4k: bool) -> np.ndarray:
@@ -311,6 +346,16 @@ def gen_q4k_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
     mn = rng.integers(0, 64, size=(N, nb, 8), dtype=np.uint8)
     q = rng.integers(0, 16, size=(N, nb, QK_K), dtype=np.uint8)
     return pack_q4k(d, dm, sc, mn, q)
+
+
+def gen_q6k_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    """d f16 uniform in [1e-4,1e-3]; int8 scales uniform in [-128,127]; 6-bit quants uniform in [0,63]
+    -> bytes [N, K/256, 210]."""
+    nb = K // QK_K
+    d = rng.uniform(1e-4, 1e-3, size=(N, nb)).astype(np.float16)
+    sc = rng.integers(-128, 128, size=(N, nb, 16), dtype=np.int8)
+    q = rng.integers(0, 64, size=(N, nb, QK_K), dtype=np.uint8)
+    return pack_q6k(d, sc, q)
 
 
 def gen_activation(rng: np.random.Generator, M: int, K: int, bf16: bool) -> np.ndarray:

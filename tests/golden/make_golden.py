@@ -56,6 +56,23 @@ def hand_q4k():
     return blk, expect
 
 
+def hand_q6k():
+    """One super-block: d = 0.5, scales[k] = k - 8 (both signs), 6-bit value of element i = (5 i + 3) % 64.
+    Element i (h = i // 128, j = (i % 128) // 32, l = i % 32): low nibble in ql[64h + 32(j & 1) + l] (upper half
+    of the byte for j >= 2), top two bits at bit 2j of qh[32h + l]; y = d * scales[i // 16] * (q - 32)."""
+    q = (5 * np.arange(256) + 3) % 64
+    sc = (np.arange(16) - 8).astype(np.int8)
+    ql = np.zeros(128, dtype=np.uint8)
+    qh = np.zeros(64, dtype=np.uint8)
+    for i in range(256):
+        h, j, l = i // 128, (i % 128) // 32, i % 32
+        ql[64 * h + 32 * (j & 1) + l] |= (q[i] & 0xF) << (4 if j >= 2 else 0)
+        qh[32 * h + l] |= (q[i] >> 4) << (2 * j)
+    blk = np.frombuffer(ql.tobytes() + qh.tobytes() + sc.tobytes() + f16_bytes(0.5), dtype=np.uint8).copy()
+    expect = np.array([np.float32(0.5 * sc[i // 16]) * np.float32(q[i] - 32) for i in range(256)], dtype=np.float32)
+    return blk, expect
+
+
 def main() -> None:
     rng = np.random.default_rng(20240601)
     out = {}
@@ -98,6 +115,20 @@ def main() -> None:
         out[name + "_w"] = w
         out[name + "_x"] = xx
         out[name + "_y"] = (xx.astype(np.float64) @ wd.T).astype(np.float32)
+
+    # Q6_K (drawn after everything above, so the earlier fixtures keep their bytes)
+    b, e = hand_q6k()
+    out["hand_q6k_block"], out["hand_q6k_expect"] = b, e
+    assert np.array_equal(quants.dequantize(b, QT.Q6_K).reshape(-1), e)
+    q6 = random_blocks(24, 210, (208,))
+    out["rand_q6k_blocks"] = q6
+    out["rand_q6k_expect"] = quants.dequantize(q6.reshape(-1), QT.Q6_K).reshape(-1).astype(np.float32)
+    N, K = 24, 512
+    w = random_blocks(N * K // 256, 210, (208,))
+    xx = rng.standard_normal((5, K)).astype(np.float32)
+    out["mm_q6k_w"], out["mm_q6k_x"] = w, xx
+    out["mm_q6k_y"] = (xx.astype(np.float64) @ quants.dequantize(w.reshape(-1), QT.Q6_K).reshape(N, K)
+                       .astype(np.float64).T).astype(np.float32)
 
     np.savez_compressed(os.path.join(HERE, "blocks.npz"), **out)
     print("wrote", os.path.join(HERE, "blocks.npz"), {k: v.shape for k, v in out.items()})

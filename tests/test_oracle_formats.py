@@ -33,6 +33,28 @@ def test_against_gguf_package_live():
     assert np.array_equal(o.c_dequant(w8, False).view(np.uint32), b.view(np.uint32))
 
 
+def test_q6k_against_fixtures_and_gguf_package(golden):
+    assert np.array_equal(o.dequant_q6k(golden["hand_q6k_block"]), golden["hand_q6k_expect"])
+    got = o.dequant_q6k(golden["rand_q6k_blocks"]).reshape(-1)
+    assert np.array_equal(got.view(np.uint32), golden["rand_q6k_expect"].view(np.uint32))
+    w = golden["mm_q6k_w"]
+    y = o.qmatmul_exact(golden["mm_q6k_x"], o.dequant_q6k(w).reshape(24, 512))
+    assert o.rel_l2(y, golden["mm_q6k_y"]) < 1e-6
+    # the generator's packing is the inverse of the unpacking
+    rng = np.random.default_rng(11)
+    d = rng.uniform(1e-3, 1e-2, size=(3, 2)).astype(np.float16)
+    sc = rng.integers(-128, 128, size=(3, 2, 16), dtype=np.int8)
+    q = rng.integers(0, 64, size=(3, 2, 256), dtype=np.uint8)
+    want = (d.astype(np.float32)[..., None] * np.repeat(sc, 16, axis=-1).astype(np.float32)) * \
+        (q.astype(np.float32) - np.float32(32))
+    assert np.array_equal(o.dequant_q6k(o.pack_q6k(d, sc, q)), want)
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    w6 = o.gen_q6k_weight(rng, 16, 1024)
+    a = quants.dequantize(w6.reshape(-1), gguf.GGMLQuantizationType.Q6_K).reshape(-1).astype(np.float32)
+    assert np.array_equal(o.dequant_q6k(w6).reshape(-1).view(np.uint32), a.view(np.uint32))
+
+
 def test_scale_packing_roundtrip():
     rng = np.random.default_rng(3)
     sc = rng.integers(0, 64, size=(100, 8), dtype=np.uint8)

@@ -90,6 +90,9 @@ _SIGS = {
     "ub_quantize_q8_0": (c_int, [_P, _P, c_size_t, c_int, _P]),
     "ub_repack_to_split": (c_int, [_P, _P, c_size_t, c_int, _P]),
     "ub_repack_to_interleaved": (c_int, [_P, _P, c_size_t, c_int, _P]),
+    "ub_dequant_q6k": (c_int, [_P, _P, c_size_t, c_int, _P]),
+    "ub_qmatmul_q6k_f32": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "ub_qmatmul_q6k_bf16": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "ub_qmatmul_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "ub_qmatmul_q8_0_f32": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "ub_qmatmul_q8_0_bf16": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),

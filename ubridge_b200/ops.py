@@ -39,6 +39,21 @@ def dequantize_q4k(out, blocks, numel: int, out_dtype: int, stream=None) -> None
     check(lib().ub_dequant_q4k(_p(out), _p(blocks), numel, out_dtype, _s(stream)), "ub_dequant_q4k")
 
 
+def dequantize_q6k(out, blocks, numel: int, out_dtype: int, stream=None) -> None:
+    check(lib().ub_dequant_q6k(_p(out), _p(blocks), numel, out_dtype, _s(stream)), "ub_dequant_q6k")
+
+
+def qmatmul_q6k(y, x, wq, M: int, N: int, K: int, *, x_dtype: int, out_dtype: int, stream=None) -> None:
+    """y[M,N] = x[M,K] . dequant(Wq)^T for Q6_K weights (decode kernel, no workspace)."""
+    if x_dtype == DTYPE_F32:
+        fn, name = lib().ub_qmatmul_q6k_f32, "ub_qmatmul_q6k_f32"
+    elif x_dtype == DTYPE_BF16:
+        fn, name = lib().ub_qmatmul_q6k_bf16, "ub_qmatmul_q6k_bf16"
+    else:
+        raise ValueError("activations must be f32 or bf16")
+    check(fn(_p(y), _p(x), _p(wq), M, N, K, out_dtype, _s(stream)), name)
+
+
 def quantize_q8_0(blocks, x, numel: int, in_dtype: int, stream=None) -> None:
     check(lib().ub_quantize_q8_0(_p(blocks), _p(x), numel, in_dtype, _s(stream)), "ub_quantize_q8_0")
 
