@@ -19,8 +19,8 @@ Printed JSON (one line, rank 0):
 `--impl reference` times that CPU path alone (the reference's own kernels need the vendor toolchain
 and device, so the CPU restatement is the only reference arm that can run).
 
-Other workloads (c1, c2_m4, c2_m16, c3, c4, c5_m1, c5_m512) print the same line for the other
-configurations.  The linear workloads run one replica per GPU (weak scaling); c4 (MoE layer) and c5
+Other workloads (c1, c2_m4, c2_m16, c3, c4, c5_m1, c5_m512; q6k_m1 for the Q6_K decode kernel) print the same
+line for the other configurations.  The linear workloads run one replica per GPU (weak scaling); c4 (MoE layer) and c5
 (70B-shaped linear stack) shard over the ranks (expert / tensor parallel, strong scaling) with NCCL
 all-reduces through the eccl entry points.
 """
@@ -47,6 +47,16 @@ NCU_TRAFFIC_BYTES = {"c1": 17896448, "c2_m1": 33104128, "c3": 66714368}
 
 Q4K_ROW_BYTES = lambda K: K // 256 * 144  # noqa: E731
 Q8_ROW_BYTES = lambda K: K // 32 * 34  # noqa: E731
+Q6K_ROW_BYTES = lambda K: K // 256 * 210  # noqa: E731
+
+
+def wl_format(wl) -> str:
+    """"Q8_0", "Q4_K" or "Q6_K" (key ``fmt`` overrides the is_q4k flag)."""
+    return wl.get("fmt", "Q4_K" if wl["is_q4k"] else "Q8_0")
+
+
+def wl_row_bytes(wl) -> int:
+    return {"Q8_0": Q8_ROW_BYTES, "Q4_K": Q4K_ROW_BYTES, "Q6_K": Q6K_ROW_BYTES}[wl_format(wl)](wl["K"])
 
 
 def measured_peaks():
@@ -161,7 +171,9 @@ class CpuArm:
         self.o, self.wl = o, workload
         N, K, M, is_q4k = workload["N"], workload["K"], workload["M"], workload["is_q4k"]
         rng = np.random.default_rng(workload["seed"])
-        self.w = (o.gen_q4k_weight if is_q4k else o.gen_q8_0_weight)(rng, N, K)
+        fmt = wl_format(workload)
+        self.w = {"Q8_0": o.gen_q8_0_weight, "Q4_K": o.gen_q4k_weight, "Q6_K": o.gen_q6k_weight}[fmt](rng, N, K)
+        self.fmt_code = {"Q8_0": o.FMT_Q8_0, "Q4_K": o.FMT_Q4K, "Q6_K": o.FMT_Q6K}[fmt]
         self.Ms = min(M, workload.get("cpu_rows", M))
         self.x = o.gen_activation(rng, self.Ms, K, workload["x_bf16"])
         self.y = np.empty((self.Ms, N), dtype=np.float32)
@@ -171,7 +183,7 @@ class CpuArm:
 
     def call(self):
         o, wl = self.o, self.wl
-        self.fn(o._p(self.x), o._p(self.w), o._p(self.y), self.Ms, wl["N"], wl["K"], int(wl["is_q4k"]))
+        self.fn(o._p(self.x), o._p(self.w), o._p(self.y), self.Ms, wl["N"], wl["K"], self.fmt_code)
 
     def run(self, budget_s: float):
         """Repeats the matmul for about budget_s seconds; returns (value in the metric's unit, sample text)."""
@@ -191,7 +203,7 @@ class CpuArm:
             value = 2.0 * self.Ms * wl["N"] * wl["K"] / per_call / wl["flop_per_token"]
         else:
             value = 2.0 * self.Ms * wl["N"] * wl["K"] / per_call / 1e12
-        sample = "%d x [%dx%d %s] . x[%d rows] in %.2f s" % (reps, wl["N"], wl["K"], "Q4_K" if wl["is_q4k"] else "Q8_0",
+        sample = "%d x [%dx%d %s] . x[%d rows] in %.2f s" % (reps, wl["N"], wl["K"], wl_format(wl),
                                                           self.Ms, el)
         return value, sample
 
@@ -207,6 +219,8 @@ WORKLOADS = {
                   desc="Q4_K 14336x4096 small-batch decode, M=4"),
     "c2_m16": dict(N=14336, K=4096, M=16, is_q4k=True, x_bf16=True, unit="GB/s", seed=1002, copies=32,
                    desc="Q4_K 14336x4096 small-batch decode, M=16"),
+    "q6k_m1": dict(N=14336, K=4096, M=1, is_q4k=False, fmt="Q6_K", x_bf16=True, unit="GB/s", seed=1006, copies=16,
+                   passes=4, desc="Q6_K 14336x4096 decode GEMV, bf16 activations, M=1"),
     "c3": dict(N=14336, K=4096, M=2048, is_q4k=True, x_bf16=True, unit="TFLOP/s", seed=1002, copies=2, cpu_rows=64,
                desc="Q4_K 14336x4096 prefill GEMM, M=2048"),
     "c3_m1024": dict(N=14336, K=4096, M=1024, is_q4k=True, x_bf16=True, unit="TFLOP/s", seed=1002, copies=2,
@@ -235,7 +249,8 @@ def run_linear(args, wl, rank, world, torch, dist):
     torch.cuda.set_device(dev_index)
     N, K, M, is_q4k = wl["N"], wl["K"], wl["M"], wl["is_q4k"]
     rng = np.random.default_rng(wl["seed"] + rank)
-    w_host = (o.gen_q4k_weight if is_q4k else o.gen_q8_0_weight)(rng, N, K).reshape(-1)
+    fmt = wl_format(wl)
+    w_host = {"Q8_0": o.gen_q8_0_weight, "Q4_K": o.gen_q4k_weight, "Q6_K": o.gen_q6k_weight}[fmt](rng, N, K).reshape(-1)
     w_bytes = w_host.nbytes
     copies = wl["copies"]
     x_dtype = ub.DTYPE_BF16 if wl["x_bf16"] else ub.DTYPE_F32
@@ -253,7 +268,14 @@ def run_linear(args, wl, rank, world, torch, dist):
     del base
     x_dev = torch.from_numpy(x_host.view(np.uint8).reshape(-1).copy()).cuda()
     y_dev = torch.empty((M * N * esz,), dtype=torch.uint8, device="cuda")
-    ws_bytes = ops.qmatmul_workspace_bytes(M, N, K, is_q4k)
+    ws_bytes = 0 if fmt == "Q6_K" else ops.qmatmul_workspace_bytes(M, N, K, is_q4k)
+
+    def matmul(y, x, w, workspace, stream):
+        if fmt == "Q6_K":
+            ops.qmatmul_q6k(y, x, w, M, N, K, x_dtype=x_dtype, out_dtype=y_dtype, stream=stream)
+        else:
+            ops.qmatmul(y, x, w, M, N, K, is_q4k=is_q4k, x_dtype=x_dtype, out_dtype=y_dtype, workspace=workspace,
+                        ws_bytes=ws_bytes, stream=stream)
     ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device="cuda")
 
     stream = torch.cuda.Stream()
@@ -264,8 +286,7 @@ def run_linear(args, wl, rank, world, torch, dist):
     def one_step():
         for _p in range(passes):
             for c in range(copies):
-                ops.qmatmul(y_dev.data_ptr(), x_dev.data_ptr(), w_dev[c].data_ptr(), M, N, K, is_q4k=is_q4k,
-                            x_dtype=x_dtype, out_dtype=y_dtype, workspace=ws.data_ptr(), ws_bytes=ws_bytes, stream=sp)
+                matmul(y_dev.data_ptr(), x_dev.data_ptr(), w_dev[c].data_ptr(), ws.data_ptr(), sp)
 
     with torch.cuda.stream(stream):
         one_step()  # first call resolves symbols and attributes outside any capture
@@ -304,7 +325,7 @@ def run_linear(args, wl, rank, world, torch, dist):
     if is_q4k:
         # decode kernel: up to eight rows per pass; bf16 in and out from nine rows on: one tensor-core launch
         launches_per_call = 1 if M > 16 or (M > 8 and wl["x_bf16"]) else (M + 7) // 8
-    else:
+    else:  # Q8_0 and Q6_K
         launches_per_call = decode_launches(M)
     launches = args.steps * copies * passes * launches_per_call
 
@@ -335,8 +356,7 @@ def run_linear(args, wl, rank, world, torch, dist):
             lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), ctypes.c_void_p(host_x.data_ptr()), host_x.numel())
             for _p in range(passes):
                 for c in range(copies):
-                    ops.qmatmul(d_y, d_x, w_e2e[c], M, N, K, is_q4k=is_q4k, x_dtype=x_dtype, out_dtype=y_dtype,
-                                workspace=d_ws, ws_bytes=ws_bytes, stream=dev.stream)
+                    matmul(d_y, d_x, w_e2e[c], d_ws, dev.stream)
             lib.ub_memcpy_dtoh(dev._handle, ctypes.c_void_p(host_y.data_ptr()), ctypes.c_void_p(d_y.ptr), host_y.numel())
             dev.synchronize()
 
@@ -374,7 +394,8 @@ def run_linear(args, wl, rank, world, torch, dist):
                 "algorithmic_flops_per_launch": 2.0 * M * N * K, "avg_launch_us": avg_launch_s * 1e6}
     roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
     return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
-                dtype="u4+f16 scales -> f32 accumulate" if is_q4k else "i8+f16 scales -> f32 accumulate")
+                dtype={"Q4_K": "u4+f16 scales -> f32 accumulate", "Q8_0": "i8+f16 scales -> f32 accumulate",
+                       "Q6_K": "u6+i8 scales+f16 -> f32 accumulate"}[fmt])
 
 
 def run_sharded(args, wl, rank, world, torch, dist):
@@ -606,9 +627,8 @@ def main():
     else:
         config = {"workload": "%s: %s; one step = %d matmuls over %d distinct weight copies (%.0f MB, larger than "
                               "L2)" % (args.workload, wl["desc"], wl["copies"] * wl.get("passes", 1), wl["copies"],
-                                       wl["copies"] * wl["N"] *
-                                       (Q4K_ROW_BYTES(wl["K"]) if wl["is_q4k"] else Q8_ROW_BYTES(wl["K"])) / 1e6),
-                  "N": wl["N"], "K": wl["K"], "M": wl["M"], "format": "Q4_K" if wl["is_q4k"] else "Q8_0",
+                                       wl["copies"] * wl["N"] * wl_row_bytes(wl) / 1e6),
+                  "N": wl["N"], "K": wl["K"], "M": wl["M"], "format": wl_format(wl),
                   "l2_policy": "inputs larger than L2", "parallelism": "replicas x%d" % args.gpus}
 
     if args.impl == "reference":

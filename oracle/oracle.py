@@ -403,6 +403,7 @@ def clib() -> ctypes.CDLL:
             "ub_oracle_f32_to_f16": [vp, vp, sz], "ub_oracle_f16_to_f32": [vp, vp, sz],
             "ub_oracle_f32_to_bf16": [vp, vp, sz], "ub_oracle_bf16_to_f32": [vp, vp, sz],
             "ub_oracle_dequant_q8_0": [vp, vp, sz], "ub_oracle_dequant_q4k": [vp, vp, sz],
+            "ub_oracle_dequant_q6k": [vp, vp, sz],
             "ub_oracle_dequant_to": [vp, vp, sz, i, i],
             "ub_oracle_split_layout": [vp, vp, sz, i], "ub_oracle_interleave_layout": [vp, vp, sz, i],
             "ub_oracle_quantize_q8_0": [vp, vp, sz],
@@ -437,7 +438,19 @@ def c_dequant(blocks: np.ndarray, is_q4k: bool) -> np.ndarray:
     return out
 
 
-def c_qmatmul(x_f32: np.ndarray, wq: np.ndarray, N: int, K: int, is_q4k: bool, exact: bool = True) -> np.ndarray:
+FMT_Q8_0, FMT_Q4K, FMT_Q6K = 0, 1, 2  # format codes of the C restatement's matmuls (bool is_q4k = 0 / 1)
+
+
+def c_dequant_q6k(blocks: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(blocks, dtype=np.uint8)
+    nb = b.size // Q6K_BYTES
+    out = np.empty((nb * QK_K,), dtype=np.float32)
+    clib().ub_oracle_dequant_q6k(_p(b), _p(out), ctypes.c_size_t(nb))
+    return out
+
+
+def c_qmatmul(x_f32: np.ndarray, wq: np.ndarray, N: int, K: int, is_q4k, exact: bool = True) -> np.ndarray:
+    """is_q4k: False / True, or one of the FMT_* codes."""
     x = np.ascontiguousarray(x_f32, dtype=np.float32)
     w = np.ascontiguousarray(wq, dtype=np.uint8)
     M = x.shape[0]

@@ -208,6 +208,48 @@ static void dequant_block_q4k(const uint8_t* blk, float* y) {
   }
 }
 
+/* One interleaved 210-byte Q6_K super-block -> 256 floats (layout declared at kernels/quant.cpp:170-177:
+ * ql[128] low nibbles, qh[64] upper two bits, int8 scales[16], f16 d; the reference has no kernel for it, the
+ * arithmetic is the published GGML one).  Element i = 128h + 32j + l: low nibble in ql[64h + 32(j&1) + l]
+ * (upper half of the byte when j >= 2), top two bits at bit 2j of qh[32h + l]; y = (d * scales[i/16]) * (q - 32). */
+#define Q6K_BYTES 210
+static void dequant_block_q6k(const uint8_t* blk, float* y) {
+  uint16_t dh;
+  memcpy(&dh, blk + 208, 2);
+  const float d = f16_to_f32(dh);
+  const int8_t* sc = (const int8_t*)(blk + 192);
+  for (int h = 0; h < 2; h++)
+    for (int j = 0; j < 4; j++) {
+      const uint8_t* ql = blk + 64 * h + 32 * (j & 1);
+      const uint8_t* qh = blk + 128 + 32 * h;
+      const int shift = j >= 2 ? 4 : 0;
+      for (int half = 0; half < 2; half++) { /* 16 positions share one scale */
+        const float ds = d * (float)sc[8 * h + 2 * j + half];
+        for (int l = 16 * half; l < 16 * half + 16; l++) {
+          const int q = ((ql[l] >> shift) & 0xF) | (((qh[l] >> (2 * j)) & 3) << 4);
+          y[128 * h + 32 * j + l] = ds * (float)(q - 32);
+        }
+      }
+    }
+}
+
+/* Format codes of the functions below: 0 = Q8_0, 1 = Q4_K, 2 = Q6_K. */
+static int fmt_per(int fmt) { return fmt == 0 ? QK8_0 : QK_K; }
+static int fmt_bytes(int fmt) { return fmt == 0 ? Q8_0_BYTES : (fmt == 1 ? Q4K_BYTES : Q6K_BYTES); }
+static void dequant_block(int fmt, const uint8_t* blk, float* y) {
+  if (fmt == 0)
+    dequant_block_q8_0(blk, y);
+  else if (fmt == 1)
+    dequant_block_q4k(blk, y);
+  else
+    dequant_block_q6k(blk, y);
+}
+
+void ub_oracle_dequant_q6k(const uint8_t* blocks, float* out, size_t nblocks) {
+#pragma omp parallel for schedule(static)
+  for (long b = 0; b < (long)nblocks; b++) dequant_block_q6k(blocks + (size_t)b * Q6K_BYTES, out + (size_t)b * QK_K);
+}
+
 void ub_oracle_dequant_q8_0(const uint8_t* blocks, float* out, size_t nblocks) {
 #pragma omp parallel for schedule(static)
   for (long b = 0; b < (long)nblocks; b++) dequant_block_q8_0(blocks + (size_t)b * Q8_0_BYTES, out + (size_t)b * QK8_0);
@@ -277,18 +319,14 @@ void ub_oracle_quantize_q8_0(const float* x, uint8_t* blocks, size_t nblocks) {
  * dequantised to f32 exactly as above, products and sums in double, one rounding
  * to f32 at the end.  This is the parity oracle (not a timed path). */
 void ub_oracle_qmatmul_exact(const float* x, const uint8_t* wq, float* y, int M, int N, int K, int is_q4k) {
-  const int per = is_q4k ? QK_K : QK8_0;
-  const int bytes = is_q4k ? Q4K_BYTES : Q8_0_BYTES;
+  const int per = fmt_per(is_q4k), bytes = fmt_bytes(is_q4k);  /* is_q4k is the format code (2 = Q6_K) */
   const int nb = K / per;
 #pragma omp parallel for schedule(static)
   for (int n = 0; n < N; n++) {
     float* wrow = (float*)malloc((size_t)K * sizeof(float));
     for (int b = 0; b < nb; b++) {
       const uint8_t* blk = wq + ((size_t)n * nb + b) * bytes;
-      if (is_q4k)
-        dequant_block_q4k(blk, wrow + (size_t)b * per);
-      else
-        dequant_block_q8_0(blk, wrow + (size_t)b * per);
+      dequant_block(is_q4k, blk, wrow + (size_t)b * per);
     }
     for (int m = 0; m < M; m++) {
       const float* xr = x + (size_t)m * K;
@@ -305,8 +343,7 @@ void ub_oracle_qmatmul_exact(const float* x, const uint8_t* wq, float* y, int M,
  * first and scaled once, the usual CPU formulation of a GGML-style vec-dot with a
  * floating-point activation row. */
 void ub_oracle_qmatmul_f32(const float* x, const uint8_t* wq, float* y, int M, int N, int K, int is_q4k) {
-  const int per = is_q4k ? QK_K : QK8_0;
-  const int bytes = is_q4k ? Q4K_BYTES : Q8_0_BYTES;
+  const int per = fmt_per(is_q4k), bytes = fmt_bytes(is_q4k);  /* is_q4k is the format code (2 = Q6_K) */
   const int nb = K / per;
 #pragma omp parallel for schedule(static)
   for (int n = 0; n < N; n++) {
@@ -317,10 +354,7 @@ void ub_oracle_qmatmul_f32(const float* x, const uint8_t* wq, float* y, int M, i
       for (int m = 0; m < mt; m++) acc[m] = 0.f;
       for (int b = 0; b < nb; b++) {
         const uint8_t* blk = wq + ((size_t)n * nb + b) * bytes;
-        if (is_q4k)
-          dequant_block_q4k(blk, wtmp);
-        else
-          dequant_block_q8_0(blk, wtmp);
+        dequant_block(is_q4k, blk, wtmp);
         for (int m = 0; m < mt; m++) {
           const float* xr = x + (size_t)(m0 + m) * K + (size_t)b * per;
           float s = 0.f;

@@ -37,9 +37,14 @@ def test_q6k_against_fixtures_and_gguf_package(golden):
     assert np.array_equal(o.dequant_q6k(golden["hand_q6k_block"]), golden["hand_q6k_expect"])
     got = o.dequant_q6k(golden["rand_q6k_blocks"]).reshape(-1)
     assert np.array_equal(got.view(np.uint32), golden["rand_q6k_expect"].view(np.uint32))
+    assert np.array_equal(o.c_dequant_q6k(golden["hand_q6k_block"]), golden["hand_q6k_expect"])
+    assert np.array_equal(o.c_dequant_q6k(golden["rand_q6k_blocks"]).view(np.uint32),
+                          golden["rand_q6k_expect"].view(np.uint32))
     w = golden["mm_q6k_w"]
     y = o.qmatmul_exact(golden["mm_q6k_x"], o.dequant_q6k(w).reshape(24, 512))
     assert o.rel_l2(y, golden["mm_q6k_y"]) < 1e-6
+    assert o.rel_l2(o.c_qmatmul(golden["mm_q6k_x"], w, 24, 512, o.FMT_Q6K), golden["mm_q6k_y"]) < 1e-6
+    assert o.rel_l2(o.c_qmatmul(golden["mm_q6k_x"], w, 24, 512, o.FMT_Q6K, exact=False), golden["mm_q6k_y"]) < 1e-5
     # the generator's packing is the inverse of the unpacking
     rng = np.random.default_rng(11)
     d = rng.uniform(1e-3, 1e-2, size=(3, 2)).astype(np.float16)

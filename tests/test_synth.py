@@ -38,6 +38,9 @@ def test_generators_match_the_oracle_generators_bit_for_bit():
     a8 = synth.gen_q8_0_weight(np.random.default_rng(6), 3, 64)
     b8 = o.gen_q8_0_weight(np.random.default_rng(6), 3, 64)
     assert np.array_equal(a8.reshape(-1), b8.reshape(-1))
+    a6 = synth.gen_q6k_weight(np.random.default_rng(8), 3, 512)
+    b6 = o.gen_q6k_weight(np.random.default_rng(8), 3, 512)
+    assert np.array_equal(a6.reshape(-1), b6.reshape(-1))
     xa = synth.gen_activation(np.random.default_rng(7), 2, 64, True)
     xb = o.gen_activation(np.random.default_rng(7), 2, 64, True)
     assert np.array_equal(xa, xb)

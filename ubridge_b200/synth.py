@@ -3,7 +3,7 @@ GGUF block-quantized weights packed from random fields, and activations.  Used b
 anything that needs plausible data without a model file; nothing here is a reference implementation.
 
 Block formats as in the reference (kernels/quant.cpp:98-104 ``block_q8_0``, :145-150 ``block_q4_K``,
-scale packing :356-363).
+scale packing :356-363, :170-177 ``block_q6_K``).
 """
 from __future__ import annotations
 
@@ -11,6 +11,7 @@ import numpy as np
 
 QK8_0, Q8_0_BYTES = 32, 34
 QK_K, Q4K_BYTES = 256, 144
+Q6K_BYTES = 210
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
@@ -69,6 +70,26 @@ def gen_q4k_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
     mn = rng.integers(0, 64, size=(N, nb, 8), dtype=np.uint8)
     q = rng.integers(0, 16, size=(N, nb, QK_K), dtype=np.uint8)
     return pack_q4k(d, dm, sc, mn, q)
+
+
+def gen_q6k_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    """d f16 uniform in [1e-4, 1e-3]; int8 scales uniform in [-128, 127]; 6-bit quants uniform in [0, 63]
+    -> bytes [N, K/256, 210] = ql[128] (low nibbles), qh[64] (upper two bits), scales[16], d.  Position
+    128h + 32j + l of a super-block keeps its nibble in ql[64h + 32(j & 1) + l] (upper half of the byte for
+    j >= 2) and its top two bits at bit 2j of qh[32h + l]."""
+    nb = K // QK_K
+    d = rng.uniform(1e-4, 1e-3, size=(N, nb)).astype(np.float16)
+    sc = rng.integers(-128, 128, size=(N, nb, 16), dtype=np.int8)
+    q = rng.integers(0, 64, size=(N, nb, 2, 4, 32), dtype=np.uint8)
+    out = np.zeros((N, nb, Q6K_BYTES), dtype=np.uint8)
+    ql = out[:, :, 0:128].reshape(N, nb, 2, 2, 32)
+    qh = out[:, :, 128:192].reshape(N, nb, 2, 32)
+    for j in range(4):
+        ql[:, :, :, j & 1, :] |= (q[:, :, :, j, :] & 0xF) << (4 * (j >> 1))
+        qh |= (q[:, :, :, j, :] >> 4) << (2 * j)
+    out[:, :, 192:208] = sc.view(np.uint8)
+    out[:, :, 208:210] = d.view(np.uint8).reshape(N, nb, 2)
+    return out
 
 
 def gen_activation(rng: np.random.Generator, M: int, K: int, bf16: bool) -> np.ndarray:
