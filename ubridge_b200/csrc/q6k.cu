@@ -42,6 +42,18 @@ __device__ __forceinline__ void q6k_lane_weights(const uint8_t* __restrict__ blk
   }
 }
 
+// Two neighbouring activations with one load (the pair starts at an even index of a 16-byte aligned row).
+__device__ __forceinline__ void load_pair(const float* p, float& a, float& b) {
+  const float2 v = __ldg(reinterpret_cast<const float2*>(p));
+  a = v.x;
+  b = v.y;
+}
+__device__ __forceinline__ void load_pair(const __nv_bfloat16* p, float& a, float& b) {
+  const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(p));
+  a = __uint_as_float(v << 16);
+  b = __uint_as_float(v & 0xFFFF0000u);
+}
+
 // One warp per super-block.
 template <typename T>
 __global__ void __launch_bounds__(256) dequant_q6k_kernel(const uint8_t* __restrict__ in, T* __restrict__ out,
@@ -99,8 +111,10 @@ __global__ void __launch_bounds__(256) qgemv_q6k_kernel(const uint8_t* __restric
         float part = 0.f;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-          part = fmaf(w[2 * j], to_f32(xt[32 * j]), part);
-          part = fmaf(w[2 * j + 1], to_f32(xt[32 * j + 1]), part);
+          float x0, x1;
+          load_pair(xt + 32 * j, x0, x1);
+          part = fmaf(w[2 * j], x0, part);
+          part = fmaf(w[2 * j + 1], x1, part);
         }
         acc[t] = fmaf(d, part, acc[t]);
       }
@@ -126,7 +140,7 @@ int q6k_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int ou
   if (!y || !x || !wq || M < 0 || N < 0 || K <= 0 || K % UB_QK_K) return ub::fail(UB_ERR_INVALID_ARG);
   if (out_dtype != UB_DTYPE_F32 && out_dtype != UB_DTYPE_BF16 && out_dtype != UB_DTYPE_F16)
     return ub::fail(UB_ERR_INVALID_ARG);
-  if ((reinterpret_cast<uintptr_t>(wq) & 1) || (reinterpret_cast<uintptr_t>(x) & (sizeof(XT) - 1)))
+  if ((reinterpret_cast<uintptr_t>(wq) & 1) || (reinterpret_cast<uintptr_t>(x) & 15))  // x rows: paired loads
     return ub::fail(UB_ERR_INVALID_ARG);
   const int esz = out_dtype == UB_DTYPE_F32 ? 4 : 2;
   const int blocks = (N + 7) / 8;
