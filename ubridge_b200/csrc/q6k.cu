@@ -7,9 +7,9 @@
 // ql[64h + 32(j & 1) + l] (upper half of the byte for j >= 2) and its top two bits at bit 2j of qh[32h + l];
 // y = (d * scales[i / 16]) * (q - 32).
 //
-// A block is 210 bytes, so nothing in it is better than 2-byte aligned.  Both kernels give a lane two
-// neighbouring l of one half (lanes 0-15: h = 0, lanes 16-31: h = 1): three 16-bit loads fetch its eight
-// weights (two per j), four byte loads its scales, and consecutive lanes read consecutive bytes.
+// A block is 210 bytes, so nothing in it is better than 2-byte aligned: all weight loads are 16-bit ones, and
+// consecutive lanes read consecutive bytes.  The dequantisation kernel gives a lane two neighbouring l of one
+// half (eight weights), the matmul kernel four (sixteen weights).
 #include "common.cuh"
 
 #define UB_Q6K_BYTES 210
@@ -20,38 +20,6 @@ using namespace ub;
 
 __device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) {
   return __ldg(reinterpret_cast<const unsigned short*>(p));
-}
-
-// The eight weights of one lane, without d: w[2 * j + e] = scales[8h + 2j + l / 16] * (q(j, l0 + e) - 32).
-__device__ __forceinline__ void q6k_lane_weights(const uint8_t* __restrict__ blk, int lane, float (&w)[8]) {
-  const int h = lane >> 4, l0 = (lane & 15) * 2;
-  const uint32_t qa = ldg_u16(blk + 64 * h + l0);        // low nibbles: j = 0, high: j = 2
-  const uint32_t qb = ldg_u16(blk + 64 * h + 32 + l0);   // low nibbles: j = 1, high: j = 3
-  const uint32_t qh = ldg_u16(blk + 128 + 32 * h + l0);
-  const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192) + 8 * h + (l0 >> 4);
-#pragma unroll
-  for (int j = 0; j < 4; j++) {
-    const float s = static_cast<float>(__ldg(sc + 2 * j));
-    const uint32_t src = (j & 1) ? qb : qa;
-#pragma unroll
-    for (int e = 0; e < 2; e++) {
-      const uint32_t lo = (src >> (8 * e + (j >= 2 ? 4 : 0))) & 0xF;
-      const uint32_t hi = (qh >> (8 * e + 2 * j)) & 3;
-      w[2 * j + e] = s * static_cast<float>(static_cast<int>(lo | (hi << 4)) - 32);
-    }
-  }
-}
-
-// Two neighbouring activations with one load (the pair starts at an even index of a 16-byte aligned row).
-__device__ __forceinline__ void load_pair(const float* p, float& a, float& b) {
-  const float2 v = __ldg(reinterpret_cast<const float2*>(p));
-  a = v.x;
-  b = v.y;
-}
-__device__ __forceinline__ void load_pair(const __nv_bfloat16* p, float& a, float& b) {
-  const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(p));
-  a = __uint_as_float(v << 16);
-  b = __uint_as_float(v & 0xFFFF0000u);
 }
 
 // One warp per super-block.
@@ -82,14 +50,32 @@ __global__ void __launch_bounds__(256) dequant_q6k_kernel(const uint8_t* __restr
   }
 }
 
+// Four neighbouring activations with one load (index a multiple of 4 in a 16-byte aligned row).
+__device__ __forceinline__ void load_quad(const float* p, float (&v)[4]) {
+  const float4 q = __ldg(reinterpret_cast<const float4*>(p));
+  v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+}
+__device__ __forceinline__ void load_quad(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 q = __ldg(reinterpret_cast<const uint2*>(p));
+  v[0] = __uint_as_float(q.x << 16), v[1] = __uint_as_float(q.x & 0xFFFF0000u);
+  v[2] = __uint_as_float(q.y << 16), v[3] = __uint_as_float(q.y & 0xFFFF0000u);
+}
+__device__ __forceinline__ uint32_t ldg_2x16(const uint8_t* p) {  // four bytes from a 2-byte aligned address
+  return ldg_u16(p) | (ldg_u16(p + 2) << 16);
+}
+
 // Decode matmul: one warp per weight row, MT tokens per pass; x is re-read through L1/L2 (it is K * MT values).
-// Per super-block a lane multiplies its eight weights with the eight activations at the same positions; d is
-// applied once per super-block.  The row's partial sums are added across the warp by shuffles, in a fixed order.
+// A warp takes two super-blocks per step (lanes 0-15 the even one, 16-31 the odd one); inside a super-block a
+// lane owns four neighbouring positions l of one 128-value half, i.e. 16 weights: their four 6-bit values per j
+// are assembled with byte-parallel masks (four values per instruction), turned into floats by placing each byte
+// in the mantissa of 2^23 (one byte permute) and subtracting 2^23 + 32, and multiplied with the activations at
+// the same positions; the int8 scale is applied once per j, d once per super-block.  The row's partial sums are
+// added across the warp by shuffles, in a fixed order.
 template <typename XT, int MT>
 __global__ void __launch_bounds__(256) qgemv_q6k_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x,
                                                         void* __restrict__ y, int y_dtype, int N, int K, int ldy) {
   const int lane = threadIdx.x & 31;
-  const int h = lane >> 4, l0 = (lane & 15) * 2;
+  const int sub = lane >> 4, h = (lane >> 3) & 1, l0 = (lane & 7) * 4;
   const int nsb = K / UB_QK_K;
   const size_t row_bytes = static_cast<size_t>(nsb) * UB_Q6K_BYTES;
   const int warps = gridDim.x * (blockDim.x >> 5);
@@ -99,25 +85,42 @@ __global__ void __launch_bounds__(256) qgemv_q6k_kernel(const uint8_t* __restric
 #pragma unroll
     for (int t = 0; t < MT; t++) acc[t] = 0.f;
 #pragma unroll 2
-    for (int sb = 0; sb < nsb; sb++) {
+    for (int sb = sub; sb < nsb; sb += 2) {
       const uint8_t* blk = row + static_cast<size_t>(sb) * UB_Q6K_BYTES;
-      float w[8];
-      q6k_lane_weights(blk, lane, w);
+      const uint32_t qa = ldg_2x16(blk + 64 * h + l0);       // low nibbles: j = 0, high: j = 2
+      const uint32_t qb = ldg_2x16(blk + 64 * h + 32 + l0);  // low nibbles: j = 1, high: j = 3
+      const uint32_t qh = ldg_2x16(blk + 128 + 32 * h + l0);
+      const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192) + 8 * h + (l0 >> 4);
       const float d = half_bits_to_f32(ldg_u16(blk + 208));
+      uint32_t q[4];
+      q[0] = (qa & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
+      q[1] = (qb & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
+      q[2] = ((qa >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
+      q[3] = ((qb >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
+      float part[MT];
+#pragma unroll
+      for (int t = 0; t < MT; t++) part[t] = 0.f;
       const int k0 = sb * UB_QK_K + 128 * h + l0;
 #pragma unroll
-      for (int t = 0; t < MT; t++) {
-        const XT* xt = x + static_cast<size_t>(t) * K + k0;
-        float part = 0.f;
+      for (int j = 0; j < 4; j++) {
+        const float s = static_cast<float>(__ldg(sc + 2 * j));
+        float w[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          float x0, x1;
-          load_pair(xt + 32 * j, x0, x1);
-          part = fmaf(w[2 * j], x0, part);
-          part = fmaf(w[2 * j + 1], x1, part);
+        for (int e = 0; e < 4; e++)  // 0x4B000000 | byte e of q[j] = 2^23 + q as a float
+          w[e] = __uint_as_float(__byte_perm(q[j], 0x4B000000u, 0x7440u | e)) - 8388640.f;
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+          float xv[4];
+          load_quad(x + static_cast<size_t>(t) * K + k0 + 32 * j, xv);
+          float pj = w[0] * xv[0];
+          pj = fmaf(w[1], xv[1], pj);
+          pj = fmaf(w[2], xv[2], pj);
+          pj = fmaf(w[3], xv[3], pj);
+          part[t] = fmaf(s, pj, part[t]);
         }
-        acc[t] = fmaf(d, part, acc[t]);
       }
+#pragma unroll
+      for (int t = 0; t < MT; t++) acc[t] = fmaf(d, part[t], acc[t]);
     }
 #pragma unroll
     for (int t = 0; t < MT; t++) {
@@ -143,9 +146,7 @@ int q6k_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int ou
   if ((reinterpret_cast<uintptr_t>(wq) & 1) || (reinterpret_cast<uintptr_t>(x) & 15))  // x rows: paired loads
     return ub::fail(UB_ERR_INVALID_ARG);
   const int esz = out_dtype == UB_DTYPE_F32 ? 4 : 2;
-  const int blocks = (N + 7) / 8;
-  const int cap = ub::num_sms() * 8;  // eight CTAs of eight warps per SM
-  const int grid = blocks < cap ? blocks : cap;
+  const int grid = (N + 7) / 8;  // one row per warp; the CTA scheduler evens out the load
   const uint8_t* w = static_cast<const uint8_t*>(wq);
   for (int m0 = 0; m0 < M;) {  // passes of up to four tokens: the weights are read once per pass
     const int left = M - m0;
