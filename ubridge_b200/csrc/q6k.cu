@@ -64,7 +64,9 @@ __device__ __forceinline__ uint32_t ldg_2x16(const uint8_t* p) {  // four bytes 
   return ldg_u16(p) | (ldg_u16(p + 2) << 16);
 }
 
-// Decode matmul: one warp per weight row, MT tokens per pass; x is re-read through L1/L2 (it is K * MT values).
+constexpr int kQ6kRowsPerWarp = 2;  // the activations a lane loads serve this many weight rows
+
+// Decode matmul: one warp per pair of weight rows, MT tokens per pass; x is re-read through L1/L2 (it is K * MT values).
 // A warp takes two super-blocks per step (lanes 0-15 the even one, 16-31 the odd one); inside a super-block a
 // lane owns four neighbouring positions l of one 128-value half, i.e. 16 weights: their four 6-bit values per j
 // are assembled with byte-parallel masks (four values per instruction), turned into floats by placing each byte
@@ -74,66 +76,86 @@ __device__ __forceinline__ uint32_t ldg_2x16(const uint8_t* p) {  // four bytes 
 template <typename XT, int MT>
 __global__ void __launch_bounds__(256) qgemv_q6k_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x,
                                                         void* __restrict__ y, int y_dtype, int N, int K, int ldy) {
+  constexpr int RW = kQ6kRowsPerWarp;
   const int lane = threadIdx.x & 31;
   const int sub = lane >> 4, h = (lane >> 3) & 1, l0 = (lane & 7) * 4;
   const int nsb = K / UB_QK_K;
   const size_t row_bytes = static_cast<size_t>(nsb) * UB_Q6K_BYTES;
   const int warps = gridDim.x * (blockDim.x >> 5);
-  for (int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < N; n += warps) {
-    const uint8_t* row = wq + static_cast<size_t>(n) * row_bytes;
-    float acc[MT];
+  for (int n0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RW; n0 < N; n0 += warps * RW) {
+    const uint8_t* row[RW];
 #pragma unroll
-    for (int t = 0; t < MT; t++) acc[t] = 0.f;
-#pragma unroll 2
+    for (int r = 0; r < RW; r++)  // rows beyond N repeat the last one; their sums are not written
+      row[r] = wq + static_cast<size_t>(n0 + r < N ? n0 + r : N - 1) * row_bytes;
+    float acc[RW][MT];
+#pragma unroll
+    for (int r = 0; r < RW; r++)
+#pragma unroll
+      for (int t = 0; t < MT; t++) acc[r][t] = 0.f;
     for (int sb = sub; sb < nsb; sb += 2) {
-      const uint8_t* blk = row + static_cast<size_t>(sb) * UB_Q6K_BYTES;
-      const uint32_t qa = ldg_2x16(blk + 64 * h + l0);       // low nibbles: j = 0, high: j = 2
-      const uint32_t qb = ldg_2x16(blk + 64 * h + 32 + l0);  // low nibbles: j = 1, high: j = 3
-      const uint32_t qh = ldg_2x16(blk + 128 + 32 * h + l0);
-      const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192) + 8 * h + (l0 >> 4);
-      const float d = half_bits_to_f32(ldg_u16(blk + 208));
-      uint32_t q[4];
-      q[0] = (qa & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
-      q[1] = (qb & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
-      q[2] = ((qa >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
-      q[3] = ((qb >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
-      float part[MT];
+      uint32_t q[RW][4];
+      float s[RW][4], d[RW];
 #pragma unroll
-      for (int t = 0; t < MT; t++) part[t] = 0.f;
+      for (int r = 0; r < RW; r++) {
+        const uint8_t* blk = row[r] + static_cast<size_t>(sb) * UB_Q6K_BYTES;
+        const uint32_t qa = ldg_2x16(blk + 64 * h + l0);       // low nibbles: j = 0, high: j = 2
+        const uint32_t qb = ldg_2x16(blk + 64 * h + 32 + l0);  // low nibbles: j = 1, high: j = 3
+        const uint32_t qh = ldg_2x16(blk + 128 + 32 * h + l0);
+        const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192) + 8 * h + (l0 >> 4);
+#pragma unroll
+        for (int j = 0; j < 4; j++) s[r][j] = static_cast<float>(__ldg(sc + 2 * j));
+        d[r] = half_bits_to_f32(ldg_u16(blk + 208));
+        q[r][0] = (qa & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
+        q[r][1] = (qb & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
+        q[r][2] = ((qa >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
+        q[r][3] = ((qb >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
+      }
+      float part[RW][MT];
+#pragma unroll
+      for (int r = 0; r < RW; r++)
+#pragma unroll
+        for (int t = 0; t < MT; t++) part[r][t] = 0.f;
       const int k0 = sb * UB_QK_K + 128 * h + l0;
 #pragma unroll
       for (int j = 0; j < 4; j++) {
-        const float s = static_cast<float>(__ldg(sc + 2 * j));
-        float w[4];
+        float xv[MT][4];
 #pragma unroll
-        for (int e = 0; e < 4; e++)  // 0x4B000000 | byte e of q[j] = 2^23 + q as a float
-          w[e] = __uint_as_float(__byte_perm(q[j], 0x4B000000u, 0x7440u | e)) - 8388640.f;
+        for (int t = 0; t < MT; t++) load_quad(x + static_cast<size_t>(t) * K + k0 + 32 * j, xv[t]);
 #pragma unroll
-        for (int t = 0; t < MT; t++) {
-          float xv[4];
-          load_quad(x + static_cast<size_t>(t) * K + k0 + 32 * j, xv);
-          float pj = w[0] * xv[0];
-          pj = fmaf(w[1], xv[1], pj);
-          pj = fmaf(w[2], xv[2], pj);
-          pj = fmaf(w[3], xv[3], pj);
-          part[t] = fmaf(s, pj, part[t]);
+        for (int r = 0; r < RW; r++) {
+          float w[4];
+#pragma unroll
+          for (int e = 0; e < 4; e++)  // 0x4B000000 | byte e of q = 2^23 + q as a float
+            w[e] = __uint_as_float(__byte_perm(q[r][j], 0x4B000000u, 0x7440u | e)) - 8388640.f;
+#pragma unroll
+          for (int t = 0; t < MT; t++) {
+            float pj = w[0] * xv[t][0];
+            pj = fmaf(w[1], xv[t][1], pj);
+            pj = fmaf(w[2], xv[t][2], pj);
+            pj = fmaf(w[3], xv[t][3], pj);
+            part[r][t] = fmaf(s[r][j], pj, part[r][t]);
+          }
         }
       }
 #pragma unroll
-      for (int t = 0; t < MT; t++) acc[t] = fmaf(d, part[t], acc[t]);
+      for (int r = 0; r < RW; r++)
+#pragma unroll
+        for (int t = 0; t < MT; t++) acc[r][t] = fmaf(d[r], part[r][t], acc[r][t]);
     }
 #pragma unroll
-    for (int t = 0; t < MT; t++) {
-      float v = acc[t];
+    for (int r = 0; r < RW; r++)
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0) {
-        const size_t at = static_cast<size_t>(t) * ldy + n;
-        if (y_dtype == UB_DTYPE_F32) static_cast<float*>(y)[at] = v;
-        else if (y_dtype == UB_DTYPE_BF16) static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(v);
-        else static_cast<__half*>(y)[at] = __float2half_rn(v);
+      for (int t = 0; t < MT; t++) {
+        float v = acc[r][t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && n0 + r < N) {
+          const size_t at = static_cast<size_t>(t) * ldy + n0 + r;
+          if (y_dtype == UB_DTYPE_F32) static_cast<float*>(y)[at] = v;
+          else if (y_dtype == UB_DTYPE_BF16) static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(v);
+          else static_cast<__half*>(y)[at] = __float2half_rn(v);
+        }
       }
-    }
   }
 }
 
@@ -146,7 +168,7 @@ int q6k_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int ou
   if ((reinterpret_cast<uintptr_t>(wq) & 1) || (reinterpret_cast<uintptr_t>(x) & 15))  // x rows: paired loads
     return ub::fail(UB_ERR_INVALID_ARG);
   const int esz = out_dtype == UB_DTYPE_F32 ? 4 : 2;
-  const int grid = (N + 7) / 8;  // one row per warp; the CTA scheduler evens out the load
+  const int grid = (N + 8 * kQ6kRowsPerWarp - 1) / (8 * kQ6kRowsPerWarp);  // the CTA scheduler evens out the load
   const uint8_t* w = static_cast<const uint8_t*>(wq);
   for (int m0 = 0; m0 < M;) {  // passes of up to four tokens: the weights are read once per pass
     const int left = M - m0;
