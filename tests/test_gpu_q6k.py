@@ -82,6 +82,24 @@ def test_matmul_odd_shapes(dev, x_dtype, M, N, K):
     assert o.rel_l2(got, want) < 1e-5  # f32 products of exact weights: only the summation order differs
 
 
+def test_matmul_weights_on_a_two_byte_boundary(dev):
+    """GGUF tensors inside a mapped file need not start on a 4-byte boundary: the kernel's 16-bit-load path."""
+    rng = np.random.default_rng(21)
+    M, N, K = 2, 40, 2048
+    w = o.gen_q6k_weight(rng, N, K).reshape(-1)
+    x = o.gen_activation(rng, M, K, True)
+    buf = dev.alloc(w.size + 16)
+    d_w = buf.slice(2, 2 + w.size)
+    dev.htod_copy_into(w, d_w)
+    d_x = dev.htod_sync_copy(to_storage(x, DTYPE_BF16))
+    d_y = dev.alloc(M * N * 4)
+    ops.qmatmul_q6k(d_y, d_x, d_w, M, N, K, x_dtype=DTYPE_BF16, out_dtype=DTYPE_F32, stream=dev.stream)
+    got = fetch(dev, d_y, DTYPE_F32, (M, N))
+    aligned = _matmul(dev, w, x, M, N, K, DTYPE_BF16, DTYPE_F32)
+    assert np.array_equal(got, aligned)  # same arithmetic, only the loads differ
+    assert o.rel_l2(got, o.qmatmul_exact(x, o.dequant_q6k(w.reshape(N, K // 256, 210)).reshape(N, K))) < 1e-5
+
+
 def test_matmul_full_size_decode(dev):
     """Q6_K 14336 x 4096, bf16 activations, M = 1 and 4, bf16 and f32 output; doubling x doubles y exactly."""
     rng = np.random.default_rng(1006)
