@@ -52,7 +52,10 @@ enum {
   UB_OP_FUSED_MOE = 122,
   UB_OP_MOE_COMBINE = 123,
   UB_OP_INDEXED_MOE = 124,
-  UB_OP_FUSED_MOE_Q4K = 125
+  UB_OP_FUSED_MOE_Q4K = 125,
+  UB_OP_MATMUL = 130,
+  UB_OP_MATMUL_W4 = 131,
+  UB_OP_MATMUL_W8 = 132
 };
 
 int ub_version(void);
@@ -94,7 +97,11 @@ int ub_synchronize(ub_device* dev);                                /* gcu_device
  * topsModuleLaunchKernel: params[i] points at the i-th kernel argument.  Grid, block and
  * shared-memory fields are accepted for source compatibility and ignored: each launcher
  * sizes its own grid.  Unlike the reference (silent no-op handle, gcu_device.rs:176-182)
- * an unknown name returns NULL and launching NULL returns UB_ERR_UNSUPPORTED. */
+ * an unknown name returns NULL and launching NULL returns UB_ERR_UNSUPPORTED.
+ * Registered: module "quant": dequantize_block_{q8_0,q4_k}_{f16,bf16,f32}, quantize_block_q8_0_{f16,bf16,f32}
+ * (kernels/quant.cpp:257-268,341-353,477-488); module "matmul": matmul_{f32,f16,bf16} with the reference's
+ * 20-parameter list and matmul_{f16,bf16}_{4bit,8bit} with its 23-parameter list
+ * (kernels/matmul.cpp:1143-1150,1186-1194; W4/W8 packing as documented at dequant_f16 below). */
 typedef struct ub_function ub_function;
 typedef struct {
   unsigned grid_dim[3];
@@ -152,7 +159,18 @@ int ub_qmatmul_q6k_bf16(void* y, const void* x, const void* wq, int M, int N, in
  * out_dtype is UB_DTYPE_F32 / UB_DTYPE_BF16 / UB_DTYPE_F16.  M <= 16 runs the
  * bandwidth-bound decode kernel (Q4_K with bf16 activations and bf16 output: M <= 8), larger M
  * the tensor-core kernel (Q4_K) — see ub_qmatmul_workspace_bytes for the scratch each needs
- * (0 whenever M <= 16). */
+ * (0 whenever M <= 16).
+ *
+ * Precondition on the weights.  The decode kernels (M <= 16) are launched with programmatic dependent launch
+ * and request their first weight tiles BEFORE they wait for the kernel in front of them on the stream.  The
+ * weight bytes must therefore be complete before that preceding kernel starts: uploaded by a copy, written
+ * by a kernel that is followed by an event / synchronisation / any non-kernel operation, or simply written
+ * long ago (model weights).  If the kernel launched immediately before the matmul on the same stream is the
+ * one that WRITES wq (a dequantise / upload / repack kernel of the caller), OR UB_QMATMUL_WEIGHTS_FRESH into
+ * out_dtype: the launch then requests nothing ahead of its dependency wait.  ub_quantize_q8_0 and
+ * ub_repack_to_interleaved set this for the next matmul on their stream by themselves.  x and y carry no
+ * such condition. */
+#define UB_QMATMUL_WEIGHTS_FRESH 0x100
 size_t ub_qmatmul_workspace_bytes(int M, int N, int K, int is_q4k);
 int ub_qmatmul_q8_0_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 int ub_qmatmul_q8_0_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
@@ -171,9 +189,9 @@ int ub_qmatmul_q4k_f32_static(void* y, const void* x, const void* wq, int M, int
 
 /* ------------------------------------------------------------------ MoE: reference-named host launchers */
 /* src/ffi.rs:205-236, kernels/topk_softmax_host.cpp:178-208 */
-void topk_softmax_f32(float* input, float* output, int* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
-void topk_softmax_f16(void* input, void* output, int* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
-void topk_softmax_bf16(void* input, void* output, int* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
+void topk_softmax_f32(float* input, float* output, int32_t* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
+void topk_softmax_f16(void* input, void* output, int32_t* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
+void topk_softmax_bf16(void* input, void* output, int32_t* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
 
 /* src/ffi.rs:149-161, kernels/moe_align_host.cpp:923-935.  sorted_ids holds
  * token_num*topk + num_experts*(block_size-1) ints, experts_ids that count / block_size.
@@ -182,21 +200,33 @@ void topk_softmax_bf16(void* input, void* output, int* index, int32_t num_tokens
 void moe_align_block_size(int32_t* sorted_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t* topk_ids, int32_t* real_token_num, int32_t* expert_map, int32_t num_experts, int32_t block_size, int32_t token_num, int32_t topk, void* stream);
 
 /* src/ffi.rs:163-203, kernels/fused_moe_host.cpp:504-536.  Dense expert weights B[E,N,K]. */
-void invoke_fused_moe_f16(void* C, void* A, void* B, void* bias, float* topk_weights, int32_t* sorted_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t M, int32_t K, int32_t N, int32_t E, int32_t topk_ids_size, int32_t top_k, int32_t block_size, int32_t mul_routed_weight, int32_t bias_flag, void* stream);
-void invoke_fused_moe_bf16(void* C, void* A, void* B, void* bias, float* topk_weights, int32_t* sorted_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t M, int32_t K, int32_t N, int32_t E, int32_t topk_ids_size, int32_t top_k, int32_t block_size, int32_t mul_routed_weight, int32_t bias_flag, void* stream);
+void invoke_fused_moe_f16(void* c, void* a, void* b, void* bias, float* topk_weights, int32_t* sorted_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t m, int32_t k, int32_t n, int32_t e, int32_t topk_ids_size, int32_t top_k, int32_t block_size, int32_t mul_routed_weight, int32_t bias_flag, void* stream);
+void invoke_fused_moe_bf16(void* c, void* a, void* b, void* bias, float* topk_weights, int32_t* sorted_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t m, int32_t k, int32_t n, int32_t e, int32_t topk_ids_size, int32_t top_k, int32_t block_size, int32_t mul_routed_weight, int32_t bias_flag, void* stream);
 
 /* src/ffi.rs:44-68, kernels/moe_host.cpp:83-94: y[idx[k],:] += e_out[k,:] * w[idx[k]*topk + top[k]] */
 void moe_f16(void* y, void* e_out, float* w, uint32_t* idx, uint32_t* top, int N, int K, int M, int topk, void* stream);
 void moe_bf16(void* y, void* e_out, float* w, uint32_t* idx, uint32_t* top, int N, int K, int M, int topk, void* stream);
 
 /* src/ffi.rs:121-147, kernels/moe_host.cpp:278-293: out[b,t,:] = in[b,(M==1?0:t),:] . w[indices[b,t]]^T */
-void indexed_moe_f16(void* in, void* w, void* out, uint32_t* indices, int N, int K, int M, int batch, int topk, int num_experts, void* stream);
-void indexed_moe_bf16(void* in, void* w, void* out, uint32_t* indices, int N, int K, int M, int batch, int topk, int num_experts, void* stream);
+void indexed_moe_f16(void* input, void* w, void* out, uint32_t* idx, int N, int K, int M, int batch, int topk, int num_experts, void* stream);
+void indexed_moe_bf16(void* input, void* w, void* out, uint32_t* idx, int N, int K, int M, int batch, int topk, int num_experts, void* stream);
 
-/* status-returning twins: src/ffi.rs:671-713, kernels/topsaten_moe_wrapper.cpp:80-213 */
+/* src/ffi.rs:70-92, kernels/dequant_host.cpp:298-306: Enflame W4A16 weights -> dense T [K, N].
+ * rhs is u8 [K/2, N] (weight_transpose != 0: [N, K/2]), scale / zeros are T [K/group_size, N] (group_size <= 0:
+ * one group; zeros may be NULL), out[k,n] = (q - zeros[k/g,n]) * scale[k/g,n].  ASSUMED packing (the reference
+ * unpacks inside a vendor routine outside its source tree, so parity with it is unpinned): the byte at
+ * packed row r holds reduction index 2r in its low nibble and 2r+1 in its high nibble; K counts dequantised
+ * rows.  The same convention serves the name-launched matmul_{f16,bf16}_{4bit,8bit} (module "matmul"). */
+void dequant_f16(void* out, uint8_t* rhs, void* scale, void* zeros, int K, int N, int weight_transpose, int group_size, void* stream);
+void dequant_bf16(void* out, uint8_t* rhs, void* scale, void* zeros, int K, int N, int weight_transpose, int group_size, void* stream);
+
+/* status-returning twins: src/ffi.rs:671-713, kernels/topsaten_moe_wrapper.cpp:80-213.  Argument order as
+ * declared there (the align twin takes num_tokens, topk BEFORE num_experts, block_size, unlike
+ * moe_align_block_size above).  token_expert_indices [num_tokens, topk] is written with
+ * slot (t, j) -> j * num_tokens + t (vLLM's source-row numbering, which the vendor op mirrors); NULL skips it. */
 int topsaten_topk_softmax_f32(float* gating_output, float* topk_weights, int32_t* topk_indices, int32_t* token_expert_indices, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
-int topsaten_moe_align_block_size(int32_t* sorted_token_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t* topk_ids, int32_t num_experts, int32_t block_size, int32_t num_tokens, int32_t topk, void* stream);
-int topsaten_fused_moe_gemm(void* c, void* a, void* b, float* topk_weights, int32_t* topk_ids, int32_t* sorted_token_ids, int32_t* expert_ids, int32_t* num_tokens_post_padded, int32_t mul_routed_weight, int32_t topk, int32_t block_size, int32_t num_tokens, int32_t hidden_dim, int32_t inter_dim, int32_t num_experts, int32_t dtype_code, void* stream);
+int topsaten_moe_align_block_size(int32_t* sorted_token_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad, int32_t* topk_ids, int32_t num_tokens, int32_t topk, int32_t num_experts, int32_t block_size, void* stream);
+int topsaten_fused_moe_gemm(void* c_ptr, void* a_ptr, void* b_ptr, float* topk_weights, int32_t* topk_ids, int32_t* sorted_token_ids, int32_t* expert_ids, int32_t* num_tokens_post_padded, int32_t mul_routed_weight, int32_t topk_val, int32_t block_size, int32_t num_tokens, int32_t hidden_dim, int32_t inter_dim, int32_t num_experts, int32_t dtype_code, void* stream);
 void topsaten_release_graph_workspace_pool(void* stream);
 
 /* ------------------------------------------------------------------ MoE: new fused entry points */
@@ -253,19 +283,19 @@ typedef enum { ecclInt8 = 0, ecclUint8 = 1, ecclInt32 = 2, ecclUint32 = 3, ecclI
 ecclResult_t ecclGetVersion(int* version);                                                              /* eccllib.rs:15-21 */
 ecclResult_t ecclGetUniqueId(ecclUniqueId* id);                                                         /* eccllib.rs:23-29 */
 ecclResult_t ecclCommInitRank(ecclComm_t* comm, int nranks, ecclUniqueId id, int rank);                 /* eccllib.rs:31-38 */
-ecclResult_t ecclCommInitAll(ecclComm_t* comms, int ndev, const int* devlist);                          /* eccllib.rs:40-46 */
+ecclResult_t ecclCommInitAll(ecclComm_t* comm, int ndev, const int* devlist);                          /* eccllib.rs:40-46 */
 ecclResult_t ecclCommDestroy(ecclComm_t comm);                                                          /* eccllib.rs:7-9  */
 ecclResult_t ecclCommAbort(ecclComm_t comm);                                                            /* eccllib.rs:11-13 */
 ecclResult_t ecclCommCount(ecclComm_t comm, int* count);                                                /* eccllib.rs:48-52 */
 ecclResult_t ecclCommDevice(ecclComm_t comm, int* device);                                              /* eccllib.rs:54-58 */
 ecclResult_t ecclCommUserRank(ecclComm_t comm, int* rank);                                              /* eccllib.rs:60-64 */
-ecclResult_t ecclReduce(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t dt, ecclRedOp_t op, int root, ecclComm_t comm, void* stream);          /* eccllib.rs:67-80 */
-ecclResult_t ecclBroadcast(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t dt, int root, ecclComm_t comm, void* stream);                      /* eccllib.rs:82-94 */
-ecclResult_t ecclAllReduce(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t dt, ecclRedOp_t op, ecclComm_t comm, void* stream);                /* eccllib.rs:96-108 */
-ecclResult_t ecclReduceScatter(const void* sendbuff, void* recvbuff, size_t recvcount, ecclDataType_t dt, ecclRedOp_t op, ecclComm_t comm, void* stream);        /* eccllib.rs:110-122 */
-ecclResult_t ecclAllGather(const void* sendbuff, void* recvbuff, size_t sendcount, ecclDataType_t dt, ecclComm_t comm, void* stream);                            /* eccllib.rs:124-135 */
-ecclResult_t ecclSend(const void* sendbuff, size_t count, ecclDataType_t dt, int peer, ecclComm_t comm, void* stream);                                           /* eccllib.rs:137-148 */
-ecclResult_t ecclRecv(void* recvbuff, size_t count, ecclDataType_t dt, int peer, ecclComm_t comm, void* stream);                                                 /* eccllib.rs:150-161 */
+ecclResult_t ecclReduce(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t datatype, ecclRedOp_t op, int root, ecclComm_t comm, void* stream);          /* eccllib.rs:67-80 */
+ecclResult_t ecclBroadcast(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t datatype, int root, ecclComm_t comm, void* stream);                      /* eccllib.rs:82-94 */
+ecclResult_t ecclAllReduce(const void* sendbuff, void* recvbuff, size_t count, ecclDataType_t datatype, ecclRedOp_t op, ecclComm_t comm, void* stream);                /* eccllib.rs:96-108 */
+ecclResult_t ecclReduceScatter(const void* sendbuff, void* recvbuff, size_t recvcount, ecclDataType_t datatype, ecclRedOp_t op, ecclComm_t comm, void* stream);        /* eccllib.rs:110-122 */
+ecclResult_t ecclAllGather(const void* sendbuff, void* recvbuff, size_t sendcount, ecclDataType_t datatype, ecclComm_t comm, void* stream);                            /* eccllib.rs:124-135 */
+ecclResult_t ecclSend(const void* sendbuff, size_t count, ecclDataType_t datatype, int peer, ecclComm_t comm, void* stream);                                           /* eccllib.rs:137-148 */
+ecclResult_t ecclRecv(void* recvbuff, size_t count, ecclDataType_t datatype, int peer, ecclComm_t comm, void* stream);                                                 /* eccllib.rs:150-161 */
 ecclResult_t ecclGroupStart(void);                                                                      /* eccllib.rs:167-169 */
 ecclResult_t ecclGroupEnd(void);                                                                        /* eccllib.rs:163-165 */
 

@@ -328,6 +328,46 @@ def moe_layer_exact(hidden_f32, logits_f32, w13_deq, w2_deq, top_k, block, norm,
     return topk_sum(c2, T, top_k, dtype), (tw, ti, sorted_ids, experts_ids, npp)
 
 
+# ----------------------------------------------------------------------------- dense and groupwise W4A16 / W8A16 matmul
+def w4a16_dequant(rhs_u8: np.ndarray, scale: np.ndarray, zeros, K: int, N: int, weight_transpose: bool, group_size: int,
+                  dtype: int) -> np.ndarray:
+    """Enflame W4A16 weights -> dense [K, N] values of `dtype` (kernels/dequant_host.cpp:19-306 is the tiling around a
+    vendor unpack routine that is not in the reference tree).  ASSUMED packing, parity unpinned: rhs is [K/2, N]
+    ([N, K/2] when transposed); the byte at packed row r holds reduction index 2r in its low nibble and 2r+1 in its
+    high nibble; w[k, n] = (q - zeros[k // g, n]) * scale[k // g, n], rounded once to `dtype`."""
+    g = group_size if group_size > 0 else K
+    rhs = np.asarray(rhs_u8, dtype=np.uint8)
+    rhs = rhs.reshape(N, K // 2).T if weight_transpose else rhs.reshape(K // 2, N)
+    q = np.empty((K, N), dtype=np.float32)
+    q[0::2] = rhs & 15
+    q[1::2] = rhs >> 4
+    sc = np.repeat(np.asarray(scale, dtype=np.float32).reshape(K // g, N), g, axis=0)
+    z = 0.0 if zeros is None else np.repeat(np.asarray(zeros, dtype=np.float32).reshape(K // g, N), g, axis=0)
+    return round_through((q - z) * sc, dtype)
+
+
+def w8a16_dequant(rhs_i8: np.ndarray, scale: np.ndarray, K: int, N: int, rhs_transpose: bool, group_size: int,
+                  dtype: int) -> np.ndarray:
+    """int8 weights x groupwise scales -> dense [K, N] values of `dtype` (kernels/matmul.cpp:1046-1066)."""
+    g = group_size if group_size > 0 else K
+    w = np.asarray(rhs_i8, dtype=np.int8)
+    w = w.reshape(N, K).T if rhs_transpose else w.reshape(K, N)
+    sc = np.repeat(np.asarray(scale, dtype=np.float32).reshape(K // g, N), g, axis=0)
+    return round_through(w.astype(np.float32) * sc, dtype)
+
+
+def dense_matmul(lhs: np.ndarray, rhs: np.ndarray, lhs_transpose: bool, rhs_transpose: bool, dtype: int) -> np.ndarray:
+    """out[B, M, N] = lhs[B, M, K] . rhs[B or 1, K, N]; transposed operands are stored [K, M] / [N, K]
+    (kernels/matmul.cpp:96-110); accumulation wider than the storage type, one rounding to `dtype` (:480-493)."""
+    a = np.asarray(lhs, dtype=np.float64)
+    b = np.asarray(rhs, dtype=np.float64)
+    if lhs_transpose:
+        a = np.swapaxes(a, -1, -2)
+    if rhs_transpose:
+        b = np.swapaxes(b, -1, -2)
+    return round_through((a @ b).astype(np.float32), dtype)
+
+
 # ----------------------------------------------------------------------------- synthetic inputs
 def gen_q8_0_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
     """int8 quants uniform in [-127,127], f16 scales uniform in [1e-3,1e-2] -> bytes [N, K/32, 34]."""

@@ -145,3 +145,103 @@ def test_config3_q4k_prefill_full_size(dev):
     # linearity: doubling the activations doubles every output exactly (powers of two commute with rounding)
     got2 = _run(dev, w, 2 * x[:64], 64, N, K, True, DTYPE_BF16, DTYPE_BF16)
     assert np.array_equal(got2, 2 * got[:64])
+
+
+# ----------------------------------------------------------------------------- single-token kernel (K = 2048 / 4096)
+@pytest.mark.parametrize("x_dtype", [DTYPE_F32, DTYPE_BF16])
+@pytest.mark.parametrize("out_dtype", [DTYPE_F32, DTYPE_BF16, DTYPE_F16])
+@pytest.mark.parametrize("N,K", [(1, 4096), (17, 2048), (4747, 4096), (4736, 2048), (30000, 4096), (20000, 2048)])
+def test_q4k_single_token_kernel(dev, x_dtype, out_dtype, N, K):
+    """M = 1 at K = 2048 / 4096: ragged last tile, fewer tiles than CTAs, and more tiles per CTA than the ring has
+    stages (30000 rows at K = 4096: 1875 tiles on 296 CTAs of 3 stages, so stages are re-armed)."""
+    rng = np.random.default_rng(N + K)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, 1, K, x_dtype == DTYPE_BF16)
+    want = o.c_qmatmul(x, w, N, K, True)
+    got = _run(dev, w, x, 1, N, K, True, x_dtype, out_dtype)
+    if out_dtype == DTYPE_F32:
+        # 15-bit block fixed-point activations: ~1e-5 over thousands of rows; a handful of rows is a handful of
+        # samples of that noise, so only the task's tolerance is asserted there
+        assert o.rel_l2(got, want) < (1e-4 if N >= 1000 else TOL_DECODE)
+    else:
+        assert np.array_equal(got, o.round_through(_run(dev, w, x, 1, N, K, True, x_dtype, DTYPE_F32),
+                                                   o.UB_BF16 if out_dtype == DTYPE_BF16 else o.UB_F16))
+
+
+def test_q4k_single_token_many_tiles_per_cta(dev):
+    """More 16-row tiles per CTA than one batch of partial sums holds (70000 rows: 15 tiles per CTA)."""
+    rng = np.random.default_rng(70)
+    N, K = 70000, 2048
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, 1, K, True)
+    got = _run(dev, w, x, 1, N, K, True, DTYPE_BF16, DTYPE_F32)
+    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, True)) < 1e-4
+
+
+def test_q4k_single_token_zero_and_huge_activations(dev):
+    rng = np.random.default_rng(5)
+    N, K = 300, 4096
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, 1, K, True)
+    x[0, :256] = 0.0                # a whole super-block of zeros (scale 0)
+    x[0, 256:512] *= 8192.0         # and one with a large range (a power of two keeps the values bf16)
+    got = _run(dev, w, x, 1, N, K, True, DTYPE_BF16, DTYPE_F32)
+    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, True)) < 1e-4
+
+
+# ----------------------------------------------------------------------------- large K: every kernel the sharded stack uses
+@pytest.mark.parametrize("N,K", [(512, 28672), (512, 14336), (640, 8192), (384, 7168), (256, 3584)])
+@pytest.mark.parametrize("M", [1, 2])
+def test_q4k_decode_large_k(dev, M, N, K):
+    """Row lengths of the 70B-shaped stack and of its tensor-parallel shards (down projection 28672 / tp; others
+    8192): K = 28672 does not fit the integer-MMA kernel's fragment area and takes the streaming kernel."""
+    rng = np.random.default_rng(K + M)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    got = _run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_F32)
+    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, True)) < TOL_DECODE
+
+
+# ----------------------------------------------------------------------------- weights written just before the matmul
+def test_quantize_then_matmul_back_to_back(dev):
+    """ub_quantize_q8_0 and the Q8_0 matmul on one stream with nothing in between: the matmul must not request
+    weight tiles ahead of its dependency wait."""
+    rng = np.random.default_rng(8)
+    N, K = 4096, 4096
+    wf = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    x = o.gen_activation(rng, 1, K, False)
+    want = o.c_qmatmul(x, o.c_quantize_q8_0(wf.reshape(-1)), N, K, False)
+    d_wf, d_x = dev.htod_sync_copy(wf), dev.htod_sync_copy(x)
+    d_y = dev.alloc(N * 4)
+    for rep in range(3):  # a fresh destination every time, so that stale bytes cannot pass
+        d_wq = dev.alloc_zeros(N * K // 32 * 34)
+        dev.synchronize()
+        ops.quantize_q8_0(d_wq, d_wf, N * K, DTYPE_F32, stream=dev.stream)
+        ops.qmatmul(d_y, d_x, d_wq, 1, N, K, is_q4k=False, x_dtype=DTYPE_F32, out_dtype=DTYPE_F32, stream=dev.stream)
+        got = dev.dtoh_sync_copy(d_y, np.float32, (1, N))
+        assert o.rel_l2(got, want) < 1e-4
+
+
+@pytest.mark.parametrize("M,K", [(1, 4096), (2, 4096), (1, 8192)])
+def test_repack_then_q4k_matmul_back_to_back(dev, M, K):
+    from ubridge_b200._lib import UB_QMATMUL_WEIGHTS_FRESH
+
+    rng = np.random.default_rng(9)
+    N = 2048
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    want = o.c_qmatmul(x, w, N, K, True)
+    nblocks = N * K // 256
+    d_w = dev.htod_sync_copy(w)
+    d_split = dev.alloc(w.size)
+    ops.repack_to_split(d_split, d_w, nblocks, True, stream=dev.stream)
+    d_x = dev.htod_sync_copy(to_storage(x, DTYPE_BF16))
+    d_y = dev.alloc(M * N * 4)
+    for flag in (0, UB_QMATMUL_WEIGHTS_FRESH):
+        d_w2 = dev.alloc_zeros(w.size)
+        dev.synchronize()
+        ops.repack_to_interleaved(d_w2, d_split, nblocks, True, stream=dev.stream)
+        ops.qmatmul(d_y, d_x, d_w2, M, N, K, is_q4k=True, x_dtype=DTYPE_BF16, out_dtype=DTYPE_F32 | flag,
+                    stream=dev.stream)
+        got = dev.dtoh_sync_copy(d_y, np.float32, (M, N))
+        assert o.rel_l2(got, want) < 1e-4

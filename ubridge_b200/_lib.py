@@ -24,6 +24,8 @@ UB_ERR_TOO_LARGE = 8
 
 # element type codes (the reference's DATATYPE enum, src/lib.rs:87-106)
 DTYPE_I8, DTYPE_U8, DTYPE_F16, DTYPE_BF16, DTYPE_I32, DTYPE_F32 = 0, 1, 4, 5, 6, 8
+# OR into out_dtype of ub_qmatmul_*: the weight bytes were written by the kernel launched just before on the stream
+UB_QMATMUL_WEIGHTS_FRESH = 0x100
 
 
 class UbridgeError(RuntimeError):
@@ -109,6 +111,8 @@ _SIGS = {
     "moe_bf16": (None, [_P] * 5 + [c_int] * 4 + [_P]),
     "indexed_moe_f16": (None, [_P] * 4 + [c_int] * 6 + [_P]),
     "indexed_moe_bf16": (None, [_P] * 4 + [c_int] * 6 + [_P]),
+    "dequant_f16": (None, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "dequant_bf16": (None, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "topsaten_topk_softmax_f32": (c_int, [_P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, _P]),
     "topsaten_moe_align_block_size": (c_int, [_P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, _P]),
     "topsaten_fused_moe_gemm": (c_int, [_P] * 8 + [c_int32] * 8 + [_P]),

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/ubridge_b200.h"
 
 #define UB_QK8_0 32
@@ -22,6 +24,12 @@ void set_cuda_error(cudaError_t e);
 int fail(int st);                 // records and returns st
 int check_launch();               // cudaGetLastError -> UB_OK / UB_ERR_CUDA (recorded)
 
+// ---- weight bytes produced on a stream by this library's own kernels (quantise, repack) ----
+// mark: called by those entry points; take: true once for the next quantized matmul on that stream, which then
+// requests no weight tile ahead of its dependency wait.
+void mark_weights_written(cudaStream_t s);
+bool take_weights_written(cudaStream_t s);
+
 // ---- per-device error word written by kernels instead of trapping ----
 // Address of the device's error word (resolved once per device with cudaGetSymbolAddress).
 int* device_error_word();
@@ -33,16 +41,16 @@ __device__ __forceinline__ void report_device_error(int* err_word, int code) {
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 inline int num_sms() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64];  // zero-initialised; threads of different ranks fill it concurrently
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 // ---- storage types ----

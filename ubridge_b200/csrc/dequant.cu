@@ -204,7 +204,9 @@ int ub_dequant_q4k(void* out, const void* blocks, size_t numel, int out_dtype, v
   return dequant_q4k_launch<false>(out, blocks, numel, out_dtype, ub::as_stream(stream));
 }
 int ub_quantize_q8_0(void* blocks, const void* x, size_t numel, int in_dtype, void* stream) {
-  return quantize_q8_0_launch<false>(blocks, x, numel, in_dtype, ub::as_stream(stream));
+  const int st = quantize_q8_0_launch<false>(blocks, x, numel, in_dtype, ub::as_stream(stream));
+  if (st == UB_OK && numel) ub::mark_weights_written(ub::as_stream(stream));
+  return st;
 }
 
 int ub_repack_to_split(void* split, const void* interleaved, size_t nblocks, int is_q4k, void* stream) {
@@ -222,6 +224,7 @@ int ub_repack_to_interleaved(void* interleaved, const void* split, size_t nblock
   const int hb = is_q4k ? 16 : 2, qb = is_q4k ? 128 : 32;
   repack_kernel<false><<<grid_for(nblocks * (hb + qb) / 2, 256), 256, 0, ub::as_stream(stream)>>>(
       static_cast<const uint8_t*>(split), static_cast<uint8_t*>(interleaved), nblocks, hb, qb);
+  ub::mark_weights_written(ub::as_stream(stream));
   return ub::check_launch();
 }
 

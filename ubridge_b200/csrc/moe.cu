@@ -23,8 +23,8 @@ using namespace ub;
 // to the lowest expert index exactly as the scalar scan does.
 template <typename T>
 __global__ void __launch_bounds__(128) topk_softmax_kernel(const T* __restrict__ in, T* __restrict__ out_w,
-                                                            int* __restrict__ out_idx, int T_tokens, int E, int k,
-                                                            int norm) {
+                                                            int* __restrict__ out_idx, int* __restrict__ out_src,
+                                                            int T_tokens, int E, int k, int norm) {
   extern __shared__ float smem_prob[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* prob = smem_prob + static_cast<size_t>(warp) * E;
@@ -78,6 +78,8 @@ __global__ void __launch_bounds__(128) topk_softmax_kernel(const T* __restrict__
       if (lane == 0) {
         out_w[static_cast<size_t>(t) * k + j] = from_f32<T>(best);
         out_idx[static_cast<size_t>(t) * k + j] = bi;
+        // source-row id of slot (t, j) in the expanded [k, T] layout, as vLLM's router kernel numbers them
+        if (out_src) out_src[static_cast<size_t>(t) * k + j] = j * T_tokens + t;
         prob[bi] = -INFINITY;
       }
       wsum += best;
@@ -97,7 +99,7 @@ __global__ void __launch_bounds__(128) topk_softmax_kernel(const T* __restrict__
 
 template <typename T>
 int topk_softmax_launch(const void* in, void* out_w, int* out_idx, int T_tokens, int E, int k, int norm,
-                        cudaStream_t s) {
+                        cudaStream_t s, int* out_src = nullptr) {
   if (T_tokens == 0) return ub::fail(UB_OK);
   // same limits as the reference (kernels/topk_softmax_host.cpp:108-110): silently do nothing beyond them
   if (E > 4096 || k > 4096) return ub::fail(UB_ERR_INVALID_ARG);
@@ -116,7 +118,7 @@ int topk_softmax_launch(const void* in, void* out_w, int* out_idx, int T_tokens,
   const int cap = ub::num_sms() * 8;
   if (blocks > cap) blocks = cap;
   topk_softmax_kernel<T><<<blocks, threads, smem, s>>>(static_cast<const T*>(in), static_cast<T*>(out_w), out_idx,
-                                                       T_tokens, E, k, norm);
+                                                       out_src, T_tokens, E, k, norm);
   return ub::check_launch();
 }
 
@@ -648,14 +650,16 @@ void indexed_moe_bf16(void* in, void* w, void* out, uint32_t* indices, int N, in
 int topsaten_topk_softmax_f32(float* gating_output, float* topk_weights, int32_t* topk_indices,
                               int32_t* token_expert_indices, int32_t num_tokens, int32_t num_experts, int32_t topk,
                               int32_t norm_topk_prob, void* stream) {
-  (void)token_expert_indices;  // scratch of the vendor op; not an output the caller reads
+  // token_expert_indices [num_tokens, topk] is an output tensor of the vendor op
+  // (kernels/topsaten_moe_wrapper.cpp:95-100); it receives slot (t, j) -> j * num_tokens + t, the
+  // source-row numbering of vLLM's topk_softmax, which that op mirrors.  NULL is accepted.
   return topk_softmax_launch<float>(gating_output, topk_weights, topk_indices, num_tokens, num_experts, topk,
-                                    norm_topk_prob != 0, ub::as_stream(stream));
+                                    norm_topk_prob != 0, ub::as_stream(stream), token_expert_indices);
 }
 
 int topsaten_moe_align_block_size(int32_t* sorted_token_ids, int32_t* experts_ids, int32_t* num_tokens_post_pad,
-                                  int32_t* topk_ids, int32_t num_experts, int32_t block_size, int32_t num_tokens,
-                                  int32_t topk, void* stream) {
+                                  int32_t* topk_ids, int32_t num_tokens, int32_t topk, int32_t num_experts,
+                                  int32_t block_size, void* stream) {
   return moe_align_launch(sorted_token_ids, experts_ids, num_tokens_post_pad, topk_ids, nullptr, nullptr, num_experts,
                           block_size, num_tokens, topk, ub::as_stream(stream));
 }

@@ -924,14 +924,17 @@ inline size_t dtype_size(int dt) { return dt == UB_DTYPE_F32 ? 4 : 2; }
 namespace ub {
 
 template <typename XT>
-int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s);
+int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
 template <typename XT>
-int q8_0_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s);
+int q8_0_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+template <typename XT>
+int q4k_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
 
 // Q4_K: up to eight rows of x per pass on the integer tensor-core kernel when its shared-memory plan fits.
 // Otherwise rows of x are processed four (then two, then one) at a time; each pass streams W once.
 template <typename XT>
-int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, cudaStream_t s) {
+int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
+          cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
   int m0 = 0;
   while (m0 < M) {
@@ -942,8 +945,11 @@ int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K
     int st;
     if ((reinterpret_cast<uintptr_t>(wq) & 15) == 0) {
       const int mi = left >= 8 ? 8 : left;
-      st = is_q4k ? q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, s)
-                  : q8_0_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, s);
+      // a single token at K = 2048 / 4096: the two-CTAs-per-SM kernel; everything else: token pairs / quads
+      st = (is_q4k && mi == 1) ? q4k_gemv_m1<XT>(wq, xp, yp, N, K, y_dtype, fresh, s) : UB_ERR_UNSUPPORTED;
+      if (st == UB_ERR_UNSUPPORTED)
+        st = is_q4k ? q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, s)
+                    : q8_0_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, s);
       if (st == UB_OK) {
         m0 += mi;
         continue;
@@ -965,7 +971,7 @@ int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K
   return ub::fail(UB_OK);
 }
 
-template int qgemv<float>(bool, void*, const float*, const void*, int, int, int, int, cudaStream_t);
-template int qgemv<__nv_bfloat16>(bool, void*, const __nv_bfloat16*, const void*, int, int, int, int, cudaStream_t);
+template int qgemv<float>(bool, void*, const float*, const void*, int, int, int, int, bool, cudaStream_t);
+template int qgemv<__nv_bfloat16>(bool, void*, const __nv_bfloat16*, const void*, int, int, int, int, bool, cudaStream_t);
 
 }  // namespace ub

@@ -162,7 +162,7 @@ __host__ __device__ inline ImmaGeom imma_geom(int K, bool use_tm) {
 template <typename XT, int MP>
 __global__ void __launch_bounds__(kImmaThreads, 1)
 qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void* __restrict__ y, int M, int N,
-                      int K, int y_dtype, int S, int* err_word, int use_tm, const __grid_constant__ CUtensorMap w_map) {
+                      int K, int y_dtype, int S, int early, int* err_word, int use_tm, const __grid_constant__ CUtensorMap w_map) {
   constexpr int kMT = imma_mt(MP);
   extern __shared__ __align__(128) unsigned char ismem_raw[];
   // swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for rounding the base up
@@ -338,7 +338,7 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
       for (int mt = 0; mt < n_mt; mt++) {
         const int rows_here = min(16, N - tile_row0(mt));
         for (int c = 0; c < nchunks; c++, ring_next()) {
-          if (round == 0 && slot == kEarlySlots) {
+          if (round == 0 && slot == early) {
             // Two tiles are requested before the previous kernel has finished; the rest of the ring waits
             // until the compute warps have sent their activation loads, which would otherwise queue behind
             // ~27 MB of weight traffic (measured: 2 us instead of 0.8 us until the activations arrive).
@@ -490,7 +490,7 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
 }
 
 template <typename XT, int MP>
-int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
+int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -534,7 +534,8 @@ int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, in
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, wq, x, y, M, N, K, y_dtype, S, ub::device_error_word(), use_tm ? 1 : 0, wmap);
+  e = cudaLaunchKernelEx(&cfg, kernel, wq, x, y, M, N, K, y_dtype, S, fresh ? 0 : kEarlySlots, ub::device_error_word(),
+                         use_tm ? 1 : 0, wmap);
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
@@ -568,7 +569,7 @@ __device__ __forceinline__ uint32_t swz128(uint32_t L) { return L ^ (((L >> 7) &
 template <typename XT, int MQ>
 __global__ void __launch_bounds__(kImmaThreads, 1)
 qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, int N, int K, int y_dtype, int S,
-                       int* err_word, const __grid_constant__ CUtensorMap w_map) {
+                       int early, int* err_word, const __grid_constant__ CUtensorMap w_map) {
   constexpr int kMT = 7;
   extern __shared__ __align__(128) unsigned char ismem_raw[];
   unsigned char* const ismem =
@@ -657,7 +658,7 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
     if (warp == kCW) {
       for (int mt = 0; mt < n_mt; mt++) {
         for (int c = 0; c < nchunks; c++, ring_next()) {
-          if (round == 0 && slot == kEarlySlots) {
+          if (round == 0 && slot == early) {
             // Two tiles are requested before the previous kernel has finished; the rest of the ring waits
             // until the compute warps have sent their activation loads, which would otherwise queue behind
             // ~27 MB of weight traffic (measured: 2 us instead of 0.8 us until the activations arrive).
@@ -770,7 +771,7 @@ qgemv_q8_0_imma_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, in
 }
 
 template <typename XT, int MQ>
-int launch_q8_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
+int launch_q8_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -811,7 +812,7 @@ int launch_q8_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K,
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, x, y, M, N, K, y_dtype, S, ub::device_error_word(), wmap);
+  e = cudaLaunchKernelEx(&cfg, kernel, x, y, M, N, K, y_dtype, S, fresh ? 0 : kEarlySlots, ub::device_error_word(), wmap);
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
@@ -826,24 +827,24 @@ namespace ub {
 // y[M,N] = x[M,K] . dequant(Wq)^T for 1 <= M <= 8; returns UB_ERR_UNSUPPORTED (without setting the thread's
 // status) when the shape does not fit this kernel's shared-memory plan, so that the caller can use another.
 template <typename XT>
-int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
+int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
-  if (M <= 2) return launch_imma<XT, 1>(w, x, y, M, N, K, y_dtype, s);
-  if (M <= 4) return launch_imma<XT, 2>(w, x, y, M, N, K, y_dtype, s);
-  return launch_imma<XT, 4>(w, x, y, M, N, K, y_dtype, s);
+  if (M <= 2) return launch_imma<XT, 1>(w, x, y, M, N, K, y_dtype, fresh, s);
+  if (M <= 4) return launch_imma<XT, 2>(w, x, y, M, N, K, y_dtype, fresh, s);
+  return launch_imma<XT, 4>(w, x, y, M, N, K, y_dtype, fresh, s);
 }
 
 // Q8_0 flavour, same contract.
 template <typename XT>
-int q8_0_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, cudaStream_t s) {
+int q8_0_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
-  if (M <= 4) return launch_q8_imma<XT, 1>(w, x, y, M, N, K, y_dtype, s);
-  return launch_q8_imma<XT, 2>(w, x, y, M, N, K, y_dtype, s);
+  if (M <= 4) return launch_q8_imma<XT, 1>(w, x, y, M, N, K, y_dtype, fresh, s);
+  return launch_q8_imma<XT, 2>(w, x, y, M, N, K, y_dtype, fresh, s);
 }
 
-template int q8_0_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, cudaStream_t);
-template int q8_0_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, cudaStream_t);
-template int q4k_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, cudaStream_t);
-template int q4k_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, cudaStream_t);
+template int q8_0_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, bool, cudaStream_t);
+template int q8_0_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, bool, cudaStream_t);
+template int q4k_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, bool, cudaStream_t);
+template int q4k_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, bool, cudaStream_t);
 
 }  // namespace ub

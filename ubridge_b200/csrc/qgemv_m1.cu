@@ -1,0 +1,413 @@
+// Decode GEMV for ONE token (M = 1) on Q4_K weights with K = 2048 or 4096: the launch-to-launch pipeline.
+//
+//   y[N] = dequant(Wq)[N,K] . x[K]        (f32 accumulation of exact integer dots)
+//
+// Replaces the reference's LHS-resident decode matmul (kernels/matmul.cpp:1197-1208,
+// kernels/third_party/matmul_decoding.h:12-570) for GGUF Q4_K weights (block layout kernels/quant.cpp:145-150,
+// scale unpacking :356-363) at the shape the decode path spends its time on.
+//
+// A 14336 x 4096 Q4_K matrix is 33 MB: at HBM speed it streams in 5 us, so what one launch costs is decided
+// by everything that is NOT streaming: the hand-over between consecutive launches, the wait for the
+// activations, the arithmetic behind the last tile.  The design follows from that:
+//
+// * Two CTAs of 8 warps per SM (<= 113 KB of shared memory, 128 registers), grid = 2 x SMs.  A CTA takes the
+//   16-row tiles blockIdx.x, blockIdx.x + gridDim.x, ... (three of the 896 at 14336 rows) and its ring of
+//   three 36 KB stages holds all of them.  With programmatic dependent launch the CTAs of the NEXT launch
+//   move in as the CTAs of this one retire, request their first stage at once (the weights are not
+//   written by any kernel; see `fresh`) and only then wait for the previous launch: the first third of the
+//   next matrix crosses HBM while the tail of this launch computes, the rest is requested right behind
+//   the activation loads.  More than one stage ahead of the wait costs more than it gains: the activation
+//   loads then queue behind the weight traffic of their own SM.
+// * No producer warp: the warp that is (item mod 8) re-arms a stage once all eight have read it.
+// * One-token MMA arrangement.  mma.sync.m16n8k32 (u8 x s8 -> s32) takes the nibble bytes as they lie in
+//   memory.  The k range of one instruction is split in two: k 0..15 carries 16 bytes of group Ga = 2q,
+//   k 16..31 carries 16 bytes of group Gb = 2q+1 of the same 16 rows; columns 0-3 of B are non-zero only
+//   for k < 16, columns 4-7 only for k >= 16.  Per group the four columns are
+//       raw bytes  x [ xh(2G) | xl(2G) |    0     |    0     ]
+//       raw & 0xF0 x [-xh(2G) |-xl(2G) | xh(2G+1) | xl(2G+1) ]      (accumulated on top)
+//   which leaves sum(lo . x(2G)) and 16 sum(hi . x(2G+1)) for both limbs of the activation: all eight columns
+//   and all 32 lanes carry results of the one token (lane t owns sub-blocks t and 4+t of rows g, g+8).
+//   Activations are quantised once per launch to 15-bit block fixed point per 256 values
+//   (q = 254 hi + lo, both limbs signed bytes); each warp quantises only the two super-blocks it owns and
+//   keeps their B fragments in registers: no shared memory, no CTA-wide barrier in front of the main loop.
+// * Every mbarrier wait is bounded; on expiry the kernel records UB_ERR_TIMEOUT in the device error word and
+//   runs out its loops without waiting again.
+#include <cuda.h>  // CUtensorMap type and enums only; the encoder is resolved at run time
+
+#include <string.h>
+
+#include "common.cuh"
+
+namespace ub {
+void* tensor_map_encoder();
+}
+
+namespace {
+
+using namespace ub;
+
+constexpr int kW = 8;                 // warps per CTA, all of them compute
+constexpr int kThreadsM1 = kW * 32;
+constexpr int kMaxStagesM1 = 8;
+constexpr int kBatchTiles = 4;        // tiles whose row sums are added across warps at once
+constexpr uint32_t kSpinM1 = 400000;
+constexpr float kXQMaxM1 = 32258.f;   // 127 * 254
+constexpr size_t kRingBudget = 110 * 1024 + 512;  // two CTAs per SM: 2 x (ring + 1 KB slack + static + 1 KB reserved) <= 228 KB
+
+__device__ __forceinline__ void mb_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mb_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mb_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mb_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mb_wait(uint32_t bar, uint32_t parity) {
+  if (mb_try(bar, parity)) return true;
+  for (uint32_t i = 0; i < kSpinM1; i++) {
+    if (mb_try(bar, parity)) return true;
+    if (i >= 2) __nanosleep(40);
+  }
+  return false;
+}
+// d = A(16x32 u8, row) . B(32x8 s8, col)
+__device__ __forceinline__ void mma_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "r"(0));
+}
+// d += A . B
+__device__ __forceinline__ void mma_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint2 b) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
+}
+__device__ __forceinline__ uint32_t pack4_m1(int a, int b, int c, int d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+template <typename XT>
+__device__ __forceinline__ void ld8(const XT* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void ld8<float>(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void ld8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+__device__ __forceinline__ void st_out(void* y, size_t idx, int dtype, float v) {
+  if (dtype == UB_DTYPE_F32)
+    static_cast<float*>(y)[idx] = v;
+  else if (dtype == UB_DTYPE_BF16)
+    static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+  else
+    static_cast<__half*>(y)[idx] = __float2half_rn(v);
+}
+
+// SBW: super-blocks per warp = K / 2048.  A stage is one 16-row tile: 16 rows x 8*SBW super-blocks.
+// early: stages requested before the wait for the previous kernel (0 when the weights may be fresh).
+template <typename XT, int SBW>
+__global__ void __launch_bounds__(kThreadsM1, 2)
+qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y_dtype, int S, int early,
+                    int* err_word, const __grid_constant__ CUtensorMap w_map) {
+  constexpr int kRowStride = 8 * SBW * UB_Q4K_BYTES;  // 1152 or 2304: whole 128-byte lines
+  constexpr int kStageBytes = 16 * kRowStride;
+  extern __shared__ __align__(128) unsigned char m1_smem_raw[];
+  // swizzled stages need 1024-byte alignment; the launch reserves 1 KB of slack for rounding the base up
+  unsigned char* const sm =
+      m1_smem_raw + ((1024u - (static_cast<uint32_t>(__cvta_generic_to_shared(m1_smem_raw)) & 1023u)) & 1023u);
+  __shared__ __align__(8) unsigned long long bars[2 * kMaxStagesM1];  // full[S], empty[S]
+  __shared__ float red[kW][kBatchTiles][16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(sm));
+  const uint32_t bars_s = static_cast<uint32_t>(__cvta_generic_to_shared(bars));
+  const int total_tiles = (N + 15) >> 4;
+  const int my_tiles =
+      static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int nbatches = (my_tiles + kBatchTiles - 1) / kBatchTiles;
+
+  // The next kernel in the stream may start as soon as every CTA of this grid has passed this point: its
+  // CTAs take over SMs as ours retire.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      mb_init(bars_s + 8 * s, 1);
+      mb_init(bars_s + 8 * (kMaxStagesM1 + s), kW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // tile n of this CTA -> ring slot n % S: one tensor-map copy of 16 rows x (kRowStride / 128) lines, 128-byte
+  // swizzle; rows past N arrive as zeros
+  auto issue_tile = [&](int n) {
+    const uint32_t full = bars_s + 8 * (n % S);
+    mb_expect_tx(full, kStageBytes);
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::
+            "r"(ring_s + (n % S) * kStageBytes),
+        "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(full), "r"(0), "r"(0),
+        "r"(16 * (static_cast<int>(blockIdx.x) + n * static_cast<int>(gridDim.x)))
+        : "memory");
+  };
+  const int n_early = min(min(early, S), my_tiles);
+  if (threadIdx.x == 0)
+    for (int n = 0; n < n_early; n++) issue_tile(n);
+
+  // everything below reads what the previous kernel may have written (x) or writes what it may still read (y)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- activations of this warp's super-blocks -> B fragments in registers ----
+  uint2 bf[SBW][2][4];  // [super-block][q][MMA 1 first/second half, MMA 2 first/second half] = (k < 16, k >= 16)
+  int Sa[SBW], Sb[SBW];  // sums of q over sub-blocks t and 4 + t (for the min term)
+  float xs[SBW];
+  {
+    float v[SBW][8];
+#pragma unroll
+    for (int k = 0; k < SBW; k++) ld8<XT>(x + static_cast<size_t>(warp + 8 * k) * 256 + 8 * lane, v[k]);
+    // the rest of the ring goes out right behind the activation loads
+    if (threadIdx.x == 0)
+      for (int n = n_early; n < min(S, my_tiles); n++) issue_tile(n);
+#pragma unroll
+    for (int k = 0; k < SBW; k++) {
+      float amax = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[k][e]));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      const float inv = amax > 0.f ? kXQMaxM1 / amax : 0.f;
+      xs[k] = amax * (1.f / kXQMaxM1);
+      // Round through the mantissa of 1.5 * 2^23.  q = rint(v inv); hi = rint(v inv / 254) differs from
+      // rint(q / 254) only where q / 254 is within 0.002 of a half, and there both choices leave |lo| <= 127.
+      const float inv254 = inv * (1.f / 254.f);
+      int hi[8], lo[8], sum = 0;
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        const int q = __float_as_int(fmaf(v[k][e], inv, 12582912.f)) - 0x4B400000;
+        hi[e] = __float_as_int(fmaf(v[k][e], inv254, 12582912.f)) - 0x4B400000;
+        lo[e] = q - 254 * hi[e];
+        sum += q;
+      }
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);  // sum of q over this lane's 32-value sub-block (lane / 4)
+      const uint32_t hvx = pack4_m1(hi[0], hi[1], hi[2], hi[3]), hvy = pack4_m1(hi[4], hi[5], hi[6], hi[7]);
+      const uint32_t lvx = pack4_m1(lo[0], lo[1], lo[2], lo[3]), lvy = pack4_m1(lo[4], lo[5], lo[6], lo[7]);
+      // B fragment of lane (column g, k rows 4t..4t+3): column g of group pair q belongs to sub-block
+      // 4q + g/2, even columns carry the high limb, odd ones the low limb; elements 8t..8t+7 of that
+      // sub-block sit in lane 4 (4q + g/2) + t
+#pragma unroll
+      for (int q = 0; q < 2; q++) {
+        const int src = 4 * (4 * q + (g >> 1)) + t;
+        const uint32_t hx = __shfl_sync(0xFFFFFFFFu, hvx, src), hy = __shfl_sync(0xFFFFFFFFu, hvy, src);
+        const uint32_t lx = __shfl_sync(0xFFFFFFFFu, lvx, src), ly = __shfl_sync(0xFFFFFFFFu, lvy, src);
+        const uint32_t wx = (g & 1) ? lx : hx, wy = (g & 1) ? ly : hy;
+        // MMA 1 (raw bytes): columns 0, 1, 4, 5 only.  MMA 2 (raw & 0xF0): those negated, columns 2, 3, 6, 7 plain
+        // (no limb is -128, so the per-byte negation cannot overflow)
+        const uint32_t m1x = (g & 2) ? 0u : wx, m1y = (g & 2) ? 0u : wy;
+        const uint32_t m2x = (g & 2) ? wx : __vneg4(wx), m2y = (g & 2) ? wy : __vneg4(wy);
+        const bool lowk = g < 4;  // columns 0-3 live in k 0..15, columns 4-7 in k 16..31
+        bf[k][q][0] = lowk ? make_uint2(m1x, 0) : make_uint2(0, m1x);
+        bf[k][q][1] = lowk ? make_uint2(m1y, 0) : make_uint2(0, m1y);
+        bf[k][q][2] = lowk ? make_uint2(m2x, 0) : make_uint2(0, m2x);
+        bf[k][q][3] = lowk ? make_uint2(m2y, 0) : make_uint2(0, m2y);
+      }
+      Sa[k] = __shfl_sync(0xFFFFFFFFu, sum, 4 * t);
+      Sb[k] = __shfl_sync(0xFFFFFFFFu, sum, 16 + 4 * t);
+    }
+  }
+
+  // byte offsets of this lane's header and nibble pieces inside a stage (row g, super-blocks warp + 8 i); the
+  // 16-byte unit index is XORed with the 128-byte line index modulo 8 (the copy's swizzle).  Row g + 8 lies a
+  // multiple of 8 lines further and shares the offsets.
+  uint32_t off_h[SBW], off_q[SBW][4];
+#pragma unroll
+  for (int i = 0; i < SBW; i++) {
+    auto swz = [](uint32_t L) { return L ^ (((L >> 7) & 7u) << 4); };
+    const uint32_t L0 = static_cast<uint32_t>(g * kRowStride + (warp + 8 * i) * UB_Q4K_BYTES);
+    off_h[i] = swz(L0);
+#pragma unroll
+    for (int G = 0; G < 4; G++) off_q[i][G] = swz(L0 + 16 + 32 * G + 8 * t);
+  }
+  const uint32_t selb = 0x4440u | static_cast<uint32_t>(t);  // byte t of a word
+  const float odd16 = (t & 1) ? 0.0625f : 1.f;               // odd lanes carry 16 x the high nibbles
+
+  bool ok = true;
+  int slot = 0, round = 0, tile = 0;
+  for (int b = 0; b < nbatches; b++) {
+    const int n_mt = min(kBatchTiles, my_tiles - b * kBatchTiles);
+#pragma unroll 1
+    for (int mt = 0; mt < n_mt; mt++, tile++) {
+      if (ok) ok = mb_wait(bars_s + 8 * slot, round & 1);
+      const unsigned char* rowA = sm + static_cast<size_t>(slot) * kStageBytes;
+      const unsigned char* rowB = rowA + 8 * kRowStride;
+      uint4 hA[SBW], hB[SBW];
+      uint2 wA[SBW][4], wB[SBW][4];
+#pragma unroll
+      for (int i = 0; i < SBW; i++) {
+        hA[i] = *reinterpret_cast<const uint4*>(rowA + off_h[i]);
+        hB[i] = *reinterpret_cast<const uint4*>(rowB + off_h[i]);
+#pragma unroll
+        for (int G = 0; G < 4; G++) {
+          wA[i][G] = *reinterpret_cast<const uint2*>(rowA + off_q[i][G]);
+          wB[i][G] = *reinterpret_cast<const uint2*>(rowB + off_q[i][G]);
+        }
+      }
+      // everything this warp needs from the stage is in registers: hand the slot back (the arrive is a
+      // release, so the loads above are performed before the re-arming warp sees it)
+      __syncwarp();
+      if (lane == 0) mb_arrive(bars_s + 8 * (kMaxStagesM1 + slot));
+      if ((tile & (kW - 1)) == warp && tile + S < my_tiles) {
+        if (ok) ok = mb_wait(bars_s + 8 * (kMaxStagesM1 + slot), round & 1);
+        if (ok && lane == 0) issue_tile(tile + S);
+      }
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < SBW; i++) {
+        int d[2][4];
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+          const int Ga = 2 * q, Gb = 2 * q + 1;
+          mma_first(d[q], wA[i][Ga].x, wB[i][Ga].x, wA[i][Gb].x, wB[i][Gb].x, bf[i][q][0]);
+          mma_acc(d[q], wA[i][Ga].y, wB[i][Ga].y, wA[i][Gb].y, wB[i][Gb].y, bf[i][q][1]);
+          mma_acc(d[q], wA[i][Ga].x & 0xF0F0F0F0u, wB[i][Ga].x & 0xF0F0F0F0u, wA[i][Gb].x & 0xF0F0F0F0u,
+                  wB[i][Gb].x & 0xF0F0F0F0u, bf[i][q][2]);
+          mma_acc(d[q], wA[i][Ga].y & 0xF0F0F0F0u, wB[i][Ga].y & 0xF0F0F0F0u, wA[i][Gb].y & 0xF0F0F0F0u,
+                  wB[i][Gb].y & 0xF0F0F0F0u, bf[i][q][3]);
+        }
+        // 6-bit scales and mins of sub-blocks t and 4 + t (kernels/quant.cpp:356-363), rows g (A) and g + 8 (B)
+        const uint32_t a0 = __byte_perm(hA[i].y, 0, selb), a1 = __byte_perm(hA[i].z, 0, selb),
+                       a2 = __byte_perm(hA[i].w, 0, selb);
+        const uint32_t b0 = __byte_perm(hB[i].y, 0, selb), b1 = __byte_perm(hB[i].z, 0, selb),
+                       b2 = __byte_perm(hB[i].w, 0, selb);
+        const int scA0 = a0 & 63, mnA0 = a1 & 63, scA1 = (a2 & 15) | ((a0 >> 2) & 0x30),
+                  mnA1 = (a2 >> 4) | ((a1 >> 2) & 0x30);
+        const int scB0 = b0 & 63, mnB0 = b1 & 63, scB1 = (b2 & 15) | ((b0 >> 2) & 0x30),
+                  mnB1 = (b2 >> 4) | ((b1 >> 2) & 0x30);
+        // columns 2t, 2t+1 of d: high- and low-limb dots of sub-block 4q + t
+        const int hiA = d[0][0] * scA0 + d[1][0] * scA1, loA = d[0][1] * scA0 + d[1][1] * scA1;
+        const int hiB = d[0][2] * scB0 + d[1][2] * scB1, loB = d[0][3] * scB0 + d[1][3] * scB1;
+        const int tA = mnA0 * Sa[i] + mnA1 * Sb[i], tB = mnB0 * Sa[i] + mnB1 * Sb[i];
+        const float dA = half_bits_to_f32(hA[i].x), dminA = half_bits_to_f32(hA[i].x >> 16);
+        const float dB = half_bits_to_f32(hB[i].x), dminB = half_bits_to_f32(hB[i].x >> 16);
+        const float fA = fmaf(static_cast<float>(hiA), 254.f, static_cast<float>(loA));
+        const float fB = fmaf(static_cast<float>(hiB), 254.f, static_cast<float>(loB));
+        const float xsm = xs[i] * odd16;
+        acc0 = fmaf(fA, dA * xsm, acc0);
+        acc0 = fmaf(-static_cast<float>(tA), dminA * xs[i], acc0);
+        acc1 = fmaf(fB, dB * xsm, acc1);
+        acc1 = fmaf(-static_cast<float>(tB), dminB * xs[i], acc1);
+      }
+      // rows g and g + 8 of this tile: add the four lanes of a row (fixed order), park the warp's partial sums
+      acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1);
+      acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 1);
+      acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
+      acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 2);
+      if (t == 0) red[warp][mt][g] = acc0, red[warp][mt][8 + g] = acc1;
+      if (++slot == S) slot = 0, round++;
+    }
+    __syncthreads();  // partial sums of the batch are complete
+    if (static_cast<int>(threadIdx.x) < n_mt * 16) {
+      const int mt = threadIdx.x >> 4, r = threadIdx.x & 15;
+      const int row = 16 * (static_cast<int>(blockIdx.x) + (b * kBatchTiles + mt) * static_cast<int>(gridDim.x)) + r;
+      if (row < N) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kW; w++) tot += red[w][mt][r];  // fixed order: deterministic
+        st_out(y, row, y_dtype, tot);
+      }
+    }
+    if (b + 1 < nbatches) __syncthreads();  // before the next batch overwrites the partial sums
+  }
+  if (!ok && lane == 0) report_device_error(err_word, UB_ERR_TIMEOUT);
+}
+
+template <typename XT, int SBW>
+int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
+  typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ub::tensor_map_encoder());
+  if (!enc) return UB_ERR_UNSUPPORTED;
+  constexpr int kRowStride = 8 * SBW * UB_Q4K_BYTES;
+  constexpr int kStageBytes = 16 * kRowStride;
+  // rows as lines of 128 bytes: {128 bytes, lines per row, N rows}; box = one 16-row tile
+  CUtensorMap wmap;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(K / UB_QK_K) * UB_Q4K_BYTES;
+  const cuuint64_t dims[3] = {128, row_bytes / 128, static_cast<cuuint64_t>(N)};
+  const cuuint64_t strides[2] = {128, row_bytes};
+  const cuuint32_t box[3] = {128, static_cast<cuuint32_t>(kRowStride / 128), 16};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(wq), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return UB_ERR_UNSUPPORTED;
+  int S = static_cast<int>(kRingBudget / kStageBytes);
+  if (S > kMaxStagesM1) S = kMaxStagesM1;
+  const size_t smem = static_cast<size_t>(S) * kStageBytes + 1024;
+  auto kernel = qgemv_q4k_m1_kernel<XT, SBW>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  const int tiles = (N + 15) / 16;
+  const int slots = 2 * ub::num_sms();
+  const int grid = tiles < slots ? tiles : slots;
+  // one 36 KB stage (two 18 KB ones) ahead of the dependency wait; none when the weights may still be
+  // in flight from the previous kernel
+  const int early = fresh ? 0 : (SBW == 2 ? 1 : 2);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kThreadsM1), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, y_dtype, S, early, ub::device_error_word(), wmap);
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  return ub::check_launch();
+}
+
+}  // namespace
+
+namespace ub {
+
+// y[N] = dequant(Wq) . x for one token; UB_ERR_UNSUPPORTED (without touching the thread's status) for shapes
+// this kernel does not take (K other than 2048 / 4096, unaligned weights, no tensor-map encoder).
+// fresh: the weight bytes may have been written by the kernel launched just before on the same stream.
+template <typename XT>
+int q4k_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
+  const uint8_t* w = static_cast<const uint8_t*>(wq);
+  if (reinterpret_cast<uintptr_t>(w) & 15) return UB_ERR_UNSUPPORTED;
+  if (K == 4096) return launch_m1<XT, 2>(w, x, y, N, K, y_dtype, fresh, s);
+  if (K == 2048) return launch_m1<XT, 1>(w, x, y, N, K, y_dtype, fresh, s);
+  return UB_ERR_UNSUPPORTED;
+}
+
+template int q4k_gemv_m1<float>(const void*, const float*, void*, int, int, int, bool, cudaStream_t);
+template int q4k_gemv_m1<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, bool, cudaStream_t);
+
+}  // namespace ub

@@ -15,7 +15,8 @@
 
 namespace ub {
 template <typename XT>
-int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, cudaStream_t s);
+int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
+          cudaStream_t s);
 int q4k_gemm_mma(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
 }  // namespace ub
@@ -49,6 +50,9 @@ inline int conv_grid(size_t n) {
 // x_dtype: UB_DTYPE_F32 or UB_DTYPE_BF16
 int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype,
             void* workspace, size_t ws_bytes, void* stream) {
+  // UB_QMATMUL_WEIGHTS_FRESH rides in the upper bits of out_dtype
+  bool fresh = (out_dtype & UB_QMATMUL_WEIGHTS_FRESH) != 0;
+  out_dtype &= ~UB_QMATMUL_WEIGHTS_FRESH;
   if (M == 0 || N == 0) return ub::fail(UB_OK);
   if (!y || !x || !wq || M < 0 || N < 0 || K <= 0) return ub::fail(UB_ERR_INVALID_ARG);
   if (K % (is_q4k ? UB_QK_K : UB_QK8_0)) return ub::fail(UB_ERR_INVALID_ARG);
@@ -60,6 +64,7 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
       (x_dtype == UB_DTYPE_F32 && (K % 4)))
     return ub::fail(UB_ERR_INVALID_ARG);
   cudaStream_t s = ub::as_stream(stream);
+  if (ub::take_weights_written(s)) fresh = true;
 
   if (is_q4k && M > kDecodeOnePassM && M <= kDecodeMaxM && x_dtype == UB_DTYPE_BF16 && out_dtype == UB_DTYPE_BF16) {
     const int st = ub::q4k_gemm_tc(y, x, wq, M, N, K, s);
@@ -67,8 +72,8 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
   }
   if (M <= kDecodeMaxM || !is_q4k) {
     if (x_dtype == UB_DTYPE_F32)
-      return ub::qgemv<float>(is_q4k, y, static_cast<const float*>(x), wq, M, N, K, out_dtype, s);
-    return ub::qgemv<__nv_bfloat16>(is_q4k, y, static_cast<const __nv_bfloat16*>(x), wq, M, N, K, out_dtype, s);
+      return ub::qgemv<float>(is_q4k, y, static_cast<const float*>(x), wq, M, N, K, out_dtype, fresh, s);
+    return ub::qgemv<__nv_bfloat16>(is_q4k, y, static_cast<const __nv_bfloat16*>(x), wq, M, N, K, out_dtype, fresh, s);
   }
 
   // tensor-core path: bf16 in, bf16 out; convert around it when the caller's types differ

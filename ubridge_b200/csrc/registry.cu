@@ -15,6 +15,8 @@ namespace ub {
 int dequant_q8_0_split(void* out, const void* in, size_t numel, int dt, cudaStream_t s);
 int dequant_q4k_split(void* out, const void* in, size_t numel, int dt, cudaStream_t s);
 int quantize_q8_0_split(void* out, const void* x, size_t numel, int dt, cudaStream_t s);
+int dense_matmul(int dtype, int quant, const void* a, const void* b, void* out, const void* scales, const void* zeros,
+                 int B, int M, int K, int N, int lhs_t, int rhs_t, int bcast_w, int group, cudaStream_t s);
 }  // namespace ub
 
 struct ub_function {
@@ -48,6 +50,25 @@ int launch_quantize_q8_0(const ub_function* f, void** p, cudaStream_t s) {
   return ub::quantize_q8_0_split(arg<void*>(p, 1), arg<void*>(p, 0), numel, f->dtype, s);
 }
 
+// module "matmul", 20 parameters (kernels/matmul.cpp:1143-1150,1171-1177):
+// (T* a, T* b, T* out, int dtype, int B, int M, int K, int N, int lhs_multicore, int rhs_multicore,
+//  int batch_multicore, int lhs_transpose, int rhs_transpose, float alpha, float beta, float addmm_beta,
+//  int sip_m, int sip_k, int sip_n, int broadcasted_weight)
+int launch_matmul(const ub_function* f, void** p, cudaStream_t s) {
+  return ub::dense_matmul(f->dtype, 0, arg<void*>(p, 0), arg<void*>(p, 1), arg<void*>(p, 2), nullptr, nullptr,
+                          arg<int>(p, 4), arg<int>(p, 5), arg<int>(p, 6), arg<int>(p, 7), arg<int>(p, 11),
+                          arg<int>(p, 12), arg<int>(p, 19), -1, s);
+}
+// 23 parameters (kernels/matmul.cpp:1186-1194): (T* a, W* b, T* out, T* scales, T* zeros, int dtype, int B, int M,
+//  int K, int N, 3 x multicore, lhs_transpose, rhs_transpose, alpha, beta, addmm_beta, sip_m, sip_k, sip_n,
+//  int broadcasted_weight, int group_size)
+template <int QUANT>
+int launch_matmul_quant(const ub_function* f, void** p, cudaStream_t s) {
+  return ub::dense_matmul(f->dtype, QUANT, arg<void*>(p, 0), arg<void*>(p, 1), arg<void*>(p, 2), arg<void*>(p, 3),
+                          arg<void*>(p, 4), arg<int>(p, 6), arg<int>(p, 7), arg<int>(p, 8), arg<int>(p, 9),
+                          arg<int>(p, 13), arg<int>(p, 14), arg<int>(p, 21), arg<int>(p, 22), s);
+}
+
 const ub_function kTable[] = {
     {"quant", "dequantize_block_q8_0_f16", UB_OP_DEQUANT_Q8_0, UB_DTYPE_F16, launch_dequant_q8_0},
     {"quant", "dequantize_block_q8_0_bf16", UB_OP_DEQUANT_Q8_0, UB_DTYPE_BF16, launch_dequant_q8_0},
@@ -58,6 +79,14 @@ const ub_function kTable[] = {
     {"quant", "quantize_block_q8_0_f16", UB_OP_QUANTIZE_Q8_0, UB_DTYPE_F16, launch_quantize_q8_0},
     {"quant", "quantize_block_q8_0_bf16", UB_OP_QUANTIZE_Q8_0, UB_DTYPE_BF16, launch_quantize_q8_0},
     {"quant", "quantize_block_q8_0_f32", UB_OP_QUANTIZE_Q8_0, UB_DTYPE_F32, launch_quantize_q8_0},
+    // src/device_executor.rs:361-376
+    {"matmul", "matmul_f32", UB_OP_MATMUL, UB_DTYPE_F32, launch_matmul},
+    {"matmul", "matmul_f16", UB_OP_MATMUL, UB_DTYPE_F16, launch_matmul},
+    {"matmul", "matmul_bf16", UB_OP_MATMUL, UB_DTYPE_BF16, launch_matmul},
+    {"matmul", "matmul_f16_4bit", UB_OP_MATMUL_W4, UB_DTYPE_F16, launch_matmul_quant<1>},
+    {"matmul", "matmul_bf16_4bit", UB_OP_MATMUL_W4, UB_DTYPE_BF16, launch_matmul_quant<1>},
+    {"matmul", "matmul_f16_8bit", UB_OP_MATMUL_W8, UB_DTYPE_F16, launch_matmul_quant<2>},
+    {"matmul", "matmul_bf16_8bit", UB_OP_MATMUL_W8, UB_DTYPE_BF16, launch_matmul_quant<2>},
 };
 constexpr int kTableSize = sizeof(kTable) / sizeof(kTable[0]);
 

@@ -1,8 +1,10 @@
 // Host runtime of the shim: status bookkeeping, the device/stream/memory surface that
 // mirrors GcuDevice (src/gcu_device.rs:61-635) and GcuSlice (src/gcu_slice.rs:49-101), and
 // the per-device error word kernels write instead of trapping.
+#include <atomic>
 #include <mutex>
 #include <new>
+#include <vector>
 
 #include "common.cuh"
 
@@ -18,6 +20,14 @@ struct ErrWordCache {
   int* ptr[64] = {nullptr};
 };
 ErrWordCache g_err_cache;
+
+// Streams on which this library has just launched a kernel that writes GGUF weight bytes (quantise, repack).
+// The decode kernels request weight tiles before their dependency wait, which is only safe while no kernel
+// in front of them on the stream produces those bytes; the next quantized matmul on a marked stream is
+// launched without that early request and clears the mark.
+std::mutex g_fresh_mu;
+std::vector<cudaStream_t> g_fresh_streams;
+std::atomic<int> g_fresh_count{0};
 }  // namespace
 
 namespace ub {
@@ -35,6 +45,25 @@ int check_launch() {
   }
   t_status = UB_OK;
   return UB_OK;
+}
+
+void mark_weights_written(cudaStream_t s) {
+  std::lock_guard<std::mutex> lk(g_fresh_mu);
+  for (cudaStream_t t : g_fresh_streams)
+    if (t == s) return;
+  g_fresh_streams.push_back(s);
+  g_fresh_count.store(static_cast<int>(g_fresh_streams.size()), std::memory_order_release);
+}
+bool take_weights_written(cudaStream_t s) {
+  if (g_fresh_count.load(std::memory_order_acquire) == 0) return false;
+  std::lock_guard<std::mutex> lk(g_fresh_mu);
+  for (size_t i = 0; i < g_fresh_streams.size(); i++)
+    if (g_fresh_streams[i] == s) {
+      g_fresh_streams.erase(g_fresh_streams.begin() + i);
+      g_fresh_count.store(static_cast<int>(g_fresh_streams.size()), std::memory_order_release);
+      return true;
+    }
+  return false;
 }
 
 int* device_error_word() {
