@@ -4,14 +4,23 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 Default workload `c2_m1`: the Q4_K 14336x4096 decode GEMV with one bf16 activation row (the shape
-the headline metric "weight-GB/s at M=1" is quoted on).  One STEP is four passes over a stack of 32
+the headline metric "weight-GB/s at M=1" is quoted on).  One CUDA graph holds four passes over a stack of 32
 distinct weight matrices of that shape (1.06 GB, far larger than the 126 MB L2, so every launch
-streams its weights from HBM); the 128 launches of a step are replayed from one CUDA graph.
+streams its weights from HBM); one STEP replays that graph k times, k chosen so that the timed region
+(--steps steps) lasts at least two seconds: long enough for the clocks to settle and for the clock sampler
+to see them.  k is stated in config.workload.
+
+With the default workload the line also carries
+  secondary  (one GPU) the other single-GPU configurations: c1, c2_m4, c2_m16, c3
+  sharded    (any number of GPUs) the strong-scaling configurations at this GPU count: c5_m1, c5_m512
+             (tensor parallel) and c4 (expert parallel), run in the same process group
+(--no-extras leaves both out).
 
 Printed JSON (one line, rank 0):
   value      whole-job weight-GB/s with everything resident in HBM (CUDA events, max over ranks)
   e2e        the same metric through the public GcuDevice API: activations copied from host memory
              and the result copied back and synchronised inside every step
+  e2e_per_call   one matmul per round trip: host activations in, one launch, host result out, synchronise
   roofline   algorithmic weight+activation+output bytes of one launch / average launch duration
              inside the timed region, against the measured HBM copy bandwidth
   cpu_baseline   the CPU restatement of the same dequant-dot on this box's host cores (bounded sample)
@@ -41,9 +50,25 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# dram__bytes_read + dram__bytes_write of ONE launch of the workload's dominant kernel, from the ncu
-# captures summarised under profiles/ (null where no capture has been taken yet)
-NCU_TRAFFIC_BYTES = {"c1": 17896448, "c2_m1": 33104128, "c3": 66714368}
+# ncu summary of the workload's dominant kernel: its line `dram_bytes_per_launch = <n>` (dram__bytes_read +
+# dram__bytes_write of ONE launch) is what roofline.traffic reports; null where no capture has been summarised
+PROFILE_OF = {"c1": "qgemv_q8_0_imma_kernel__c1.md", "c2_m1": "qgemv_q4k_m1_kernel__c2_m1.md",
+              "c3": "qgemm_q4k_tc_kernel__c3.md", "c4": "qgemm_q4k_tc_kernel__c4.md",
+              "q6k_m1": "qgemv_q6k_kernel__q6k_m1.md"}
+
+
+def profile_traffic(workload: str):
+    import re
+
+    name = PROFILE_OF.get(workload)
+    if not name:
+        return None
+    try:
+        with open(os.path.join(ROOT, "profiles", name)) as f:
+            m = re.search(r"dram_bytes_per_launch\s*=\s*(\d+)", f.read())
+    except OSError:
+        return None
+    return int(m.group(1)) if m else None
 
 Q4K_ROW_BYTES = lambda K: K // 256 * 144  # noqa: E731
 Q8_ROW_BYTES = lambda K: K // 32 * 34  # noqa: E731
@@ -178,7 +203,9 @@ class CpuArm:
         self.x = o.gen_activation(rng, self.Ms, K, workload["x_bf16"])
         self.y = np.empty((self.Ms, N), dtype=np.float32)
         self.fn = o.clib().ub_oracle_qmatmul_f32
-        self.cores = os.cpu_count()
+        # launchers such as torch.distributed.run export OMP_NUM_THREADS=1: ask for every host core and report
+        # the thread count OpenMP actually grants
+        self.cores = o.set_threads(os.cpu_count() or 1)
         self.call()  # warm-up: page-in and thread pool
 
     def call(self):
@@ -239,7 +266,14 @@ WORKLOADS = {
 }
 
 
-def run_linear(args, wl, rank, world, torch, dist):
+def replays_for(min_seconds: float, steps: int, seconds_per_replay: float) -> int:
+    """Graph replays per step so that `steps` steps last at least min_seconds."""
+    if seconds_per_replay <= 0:
+        return 1
+    return max(1, int(np.ceil(min_seconds / (steps * seconds_per_replay))))
+
+
+def run_linear(wl_name, wl, steps, warmup, min_seconds, rank, world, torch, with_e2e=True):
     """Replicated (data-parallel, weak scaling) linear workloads: every rank streams its own copies."""
     import ubridge_b200 as ub
     from ubridge_b200 import synth as o  # seeded synthetic inputs
@@ -280,41 +314,50 @@ def run_linear(args, wl, rank, world, torch, dist):
 
     stream = torch.cuda.Stream()
     sp = ctypes.c_void_p(stream.cuda_stream)
-
     passes = wl.get("passes", 1)
 
-    def one_step():
+    def one_replay_body():
         for _p in range(passes):
             for c in range(copies):
                 matmul(y_dev.data_ptr(), x_dev.data_ptr(), w_dev[c].data_ptr(), ws.data_ptr(), sp)
 
     with torch.cuda.stream(stream):
-        one_step()  # first call resolves symbols and attributes outside any capture
+        one_replay_body()  # first call resolves symbols and attributes outside any capture
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            one_step()
-        for _ in range(args.warmup):
+            one_replay_body()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
             graph.replay()
+        ev0.record(stream)
+        for _ in range(5):
+            graph.replay()
+        ev1.record(stream)
+        stream.synchronize()
+        k = replays_for(min_seconds, steps, CTL.max(ev0.elapsed_time(ev1) * 1e-3 / 5))
+        for _ in range(warmup):
+            for _r in range(k):
+                graph.replay()
         stream.synchronize()
         CTL.barrier()
         torch.cuda.synchronize()
         sampler = ClockSampler(dev_index)
         if rank == 0:
             sampler.start()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
+        for _ in range(steps):
+            for _r in range(k):
+                graph.replay()
         ev1.record(stream)
         stream.synchronize()
         torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else None
     ms_total = ev0.elapsed_time(ev1)
     ms_total = CTL.max(ms_total)
-    ms_step = ms_total / args.steps
+    ms_step = ms_total / steps
 
-    # Q8_0 decode kernel: M rows are processed 4/2/1 at a time, one launch each
+    # Q8_0 / Q6_K decode kernels: M rows are processed 4/2/1 at a time, one launch each
     def decode_launches(m):
         n = 0
         while m > 0:
@@ -322,22 +365,24 @@ def run_linear(args, wl, rank, world, torch, dist):
             m -= t_
             n += 1
         return n
-    if is_q4k:
+    if fmt == "Q4_K":
         # decode kernel: up to eight rows per pass; bf16 in and out from nine rows on: one tensor-core launch
         launches_per_call = 1 if M > 16 or (M > 8 and wl["x_bf16"]) else (M + 7) // 8
-    else:  # Q8_0 and Q6_K
-        launches_per_call = decode_launches(M)
-    launches = args.steps * copies * passes * launches_per_call
-
-    calls = copies * passes * world
-    if wl["unit"] == "GB/s":
-        value = calls * w_bytes / (ms_step * 1e-3) / 1e9
+    elif fmt == "Q8_0":
+        launches_per_call = (M + 7) // 8 if K % 2048 == 0 else decode_launches(M)
     else:
-        value = calls * 2.0 * M * N * K / (ms_step * 1e-3) / 1e12
+        launches_per_call = decode_launches(M)
+    calls_per_step = k * copies * passes
+    launches = steps * calls_per_step * launches_per_call
 
-    # ---- end to end through the public device API: host activations in, host result out, every step
-    e2e = None
-    if rank == 0 or world > 1:
+    if wl["unit"] == "GB/s":
+        value = world * calls_per_step * w_bytes / (ms_step * 1e-3) / 1e9
+    else:
+        value = world * calls_per_step * 2.0 * M * N * K / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public device API: host activations in, host result out
+    e2e, e2e_call = None, None
+    if with_e2e:
         dev = ub.GcuDevice(dev_index)
         w_e2e = [dev.alloc(w_bytes) for _ in range(copies)]
         for c in range(copies):
@@ -351,31 +396,54 @@ def run_linear(args, wl, rank, world, torch, dist):
         d_x, d_y = dev.alloc(host_x.numel()), dev.alloc(host_y.numel())
         d_ws = dev.alloc(max(ws_bytes, 256))
         lib = ub.lib()
+        hx, hy = ctypes.c_void_p(host_x.data_ptr()), ctypes.c_void_p(host_y.data_ptr())
 
-        def e2e_step():
-            lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), ctypes.c_void_p(host_x.data_ptr()), host_x.numel())
+        def e2e_step():  # one copy in, one pass over the weight stack, one copy out, one synchronisation
+            lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), hx, host_x.numel())
             for _p in range(passes):
                 for c in range(copies):
                     matmul(d_y, d_x, w_e2e[c], d_ws, dev.stream)
-            lib.ub_memcpy_dtoh(dev._handle, ctypes.c_void_p(host_y.data_ptr()), ctypes.c_void_p(d_y.ptr), host_y.numel())
+            lib.ub_memcpy_dtoh(dev._handle, hy, ctypes.c_void_p(d_y.ptr), host_y.numel())
             dev.synchronize()
 
-        for _ in range(max(3, args.warmup)):
+        def e2e_call_once(c):  # what one plugin call with host buffers costs: copy, launch, copy, synchronise
+            lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), hx, host_x.numel())
+            matmul(d_y, d_x, w_e2e[c % copies], d_ws, dev.stream)
+            lib.ub_memcpy_dtoh(dev._handle, hy, ctypes.c_void_p(d_y.ptr), host_y.numel())
+            dev.synchronize()
+
+        for _ in range(3):
             e2e_step()
+        t0 = time.perf_counter()
+        e2e_step()
+        e2e_reps = max(1, int(np.ceil(min(min_seconds, 1.0) / (steps * max(time.perf_counter() - t0, 1e-6)))))
         CTL.barrier()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
-        el = time.perf_counter() - t0
-        el = CTL.max(el)
-        s_step = el / args.steps
-        ev = calls * w_bytes / s_step / 1e9 if wl["unit"] == "GB/s" else calls * 2.0 * M * N * K / s_step / 1e12
-        e2e = {"value": ev, "unit": wl["unit"], "h2d_bytes_per_step": int(host_x.numel()),
-               "d2h_bytes_per_step": int(host_y.numel())}
+        for _ in range(steps):
+            for _r in range(e2e_reps):
+                e2e_step()
+        el = CTL.max(time.perf_counter() - t0)
+        per_pass = el / (steps * e2e_reps)
+        calls = copies * passes * world
+        ev = calls * w_bytes / per_pass / 1e9 if wl["unit"] == "GB/s" else calls * 2.0 * M * N * K / per_pass / 1e12
+        e2e = {"value": ev, "unit": wl["unit"], "h2d_bytes_per_step": int(host_x.numel()) * e2e_reps,
+               "d2h_bytes_per_step": int(host_y.numel()) * e2e_reps,
+               "what": "per step %d x (one H2D of x, %d matmuls, one D2H of y, one synchronise)" % (
+                   e2e_reps, copies * passes)}
+        n_calls = 200 if M <= 16 else 20
+        for c in range(10):
+            e2e_call_once(c)
+        t0 = time.perf_counter()
+        for c in range(n_calls):
+            e2e_call_once(c)
+        per_call = CTL.max(time.perf_counter() - t0) / n_calls
+        cv = world * w_bytes / per_call / 1e9 if wl["unit"] == "GB/s" else world * 2.0 * M * N * K / per_call / 1e12
+        e2e_call = {"value": cv, "unit": wl["unit"], "us_per_call": per_call * 1e6,
+                    "h2d_bytes_per_call": int(host_x.numel()), "d2h_bytes_per_call": int(host_y.numel())}
 
     peaks = measured_peaks()
     algo_bytes = w_bytes + M * K * esz + M * N * esz
-    avg_launch_s = ms_total * 1e-3 / (args.steps * copies * passes)  # per matmul call (all of its launches)
+    avg_launch_s = ms_total * 1e-3 / (steps * calls_per_step)  # per matmul call (all of its launches)
     if wl["unit"] == "GB/s":
         achieved = algo_bytes / avg_launch_s / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -390,59 +458,95 @@ def run_linear(args, wl, rank, world, torch, dist):
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": None, "peak_source": peaks["source"],
                 "peak_kind": "burst" if burst else "sustained",
-                "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
+                "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
                 "algorithmic_flops_per_launch": 2.0 * M * N * K, "avg_launch_us": avg_launch_s * 1e6}
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
-    return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
+    roof["traffic"] = profile_traffic(wl_name)
+    return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, e2e_per_call=e2e_call, roofline=roof,
+                clocks=clocks, replays_per_step=k, timed_seconds=ms_total * 1e-3,
                 dtype={"Q4_K": "u4+f16 scales -> f32 accumulate", "Q8_0": "i8+f16 scales -> f32 accumulate",
                        "Q6_K": "u6+i8 scales+f16 -> f32 accumulate"}[fmt])
 
 
-def run_sharded(args, wl, rank, world, torch, dist):
+class ShardedContext:
+    """What the sharded workloads of one run share: the device, the NCCL communicator behind the eccl entry
+    points, the one-shot peer-memory all-reduce and a device-resident pool of random Q4_K super-blocks from
+    which every weight shard is filled (any run of whole super-blocks is a valid Q4_K matrix of any shape)."""
+
+    POOL_BLOCKS = 1 << 18  # 37.7 MB of super-blocks
+
+    def __init__(self, rank, world, torch):
+        import ubridge_b200 as ub
+        from ubridge_b200 import eccl
+        from ubridge_b200 import synth as o
+
+        self.rank, self.world, self.torch, self.ub, self.eccl = rank, world, torch, ub, eccl
+        self.dev_index = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.dev_index)
+        self.dev = ub.GcuDevice(self.dev_index)
+        self.dev.bind_to_thread()
+        self.ext = torch.cuda.ExternalStream(self.dev.stream.value)
+        self.comm, self.oneshot, self.oneshot_limit = None, None, 0
+        if world > 1:
+            # the 128-byte unique id travels out of band (the CPU group), as it does in the reference
+            uid = CTL.broadcast(eccl.Id().internal() if rank == 0 else None)
+            self.comm = eccl.Comm.from_rank(rank, world, eccl.Id(uid))
+            # messages of a few KB (the decode path) go through the one-shot peer-memory kernel, larger ones
+            # through NCCL; UB_BENCH_ALLREDUCE=nccl forces NCCL for comparison
+            self.oneshot_limit = 0 if os.environ.get("UB_BENCH_ALLREDUCE") == "nccl" else 65536
+            if self.oneshot_limit:
+                self.oneshot = eccl.OneShotAllReduce(self.dev, rank, world, self.oneshot_limit, CTL.all_gather)
+            CTL.barrier()
+        rng = np.random.default_rng(4242 + 17 * rank)
+        pool = o.gen_q4k_weight(rng, self.POOL_BLOCKS // 16, 4096).reshape(-1)
+        self.pool = self.dev.htod_sync_copy(pool)
+        self.pool_bytes = pool.nbytes
+        self.cursor = 0
+
+    def nccl_all_reduce(self, buf, count):
+        e = self.eccl
+        self.comm.all_reduce(buf, buf, count, e.Bfloat16, e.ReduceOp.Sum, stream=self.dev.stream)
+
+    def all_reduce(self, buf, count):
+        if self.oneshot is not None and count * 2 <= self.oneshot_limit and count % 8 == 0:
+            self.oneshot.all_reduce(buf, count)
+        else:
+            self.nccl_all_reduce(buf, count)
+
+    def q4k_matrix(self, rows: int, K: int):
+        """A device buffer of rows x K/256 super-blocks filled from the pool (wrapping, at a moving offset)."""
+        nbytes = rows * Q4K_ROW_BYTES(K)
+        buf = self.dev.alloc(nbytes)
+        lib, done = self.ub.lib(), 0
+        while done < nbytes:
+            n = min(nbytes - done, self.pool_bytes - self.cursor)
+            lib.ub_memcpy_dtod(self.dev._handle, ctypes.c_void_p(buf.ptr + done), ctypes.c_void_p(self.pool.ptr + self.cursor), n)
+            done += n
+            self.cursor = (self.cursor + n) % self.pool_bytes
+        return buf
+
+    def close(self):
+        self.dev.synchronize()
+        if self.comm is not None:
+            CTL.barrier()
+            if self.oneshot is not None:
+                self.oneshot.close()
+            self.comm.destroy()
+            self.comm = None
+
+
+def run_sharded(ctx, wl_name, wl, steps, warmup, min_seconds, with_e2e=True):
     """Tensor-parallel (c5) and expert-parallel (c4) workloads: the matrices are split over the ranks, every
-    rank streams its shard and the partial outputs meet in NCCL all-reduces (strong scaling)."""
-    import ubridge_b200 as ub
-    from ubridge_b200 import synth as o  # seeded synthetic inputs
-    from ubridge_b200 import eccl, parallel
+    rank streams its shard and the partial outputs meet in all-reduces (strong scaling)."""
+    from ubridge_b200 import parallel
+    from ubridge_b200 import synth as o
 
-    dev_index = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(dev_index)
-    dev = ub.GcuDevice(dev_index)
-    dev.bind_to_thread()
-    ext = torch.cuda.ExternalStream(dev.stream.value)
-    comm, all_reduce = None, None
-
-    def note(msg):
-        if os.environ.get("UB_BENCH_VERBOSE"):
-            print("[rank %d] %s" % (rank, msg), file=sys.stderr, flush=True)
-
-    if world > 1:
-        # the 128-byte unique id travels out of band (the CPU group), as it does in the reference
-        uid = CTL.broadcast(eccl.Id().internal() if rank == 0 else None)
-        note("unique id exchanged")
-        comm = eccl.Comm.from_rank(rank, world, eccl.Id(uid))
-        note("communicator ready")
-
-        # messages of a few KB (the decode path) go through the one-shot peer-memory kernel, larger ones
-        # through NCCL; UB_BENCH_ALLREDUCE=nccl forces NCCL for comparison
-        oneshot_limit = 0 if os.environ.get("UB_BENCH_ALLREDUCE") == "nccl" else 65536
-        oneshot = eccl.OneShotAllReduce(dev, rank, world, oneshot_limit, CTL.all_gather) if oneshot_limit else None
-        CTL.barrier()
-        note("peer staging buffers open")
-
-        def all_reduce(buf, count):
-            if oneshot is not None and count * 2 <= oneshot_limit and count % 8 == 0:
-                oneshot.all_reduce(buf, count)
-            else:
-                comm.all_reduce(buf, buf, count, eccl.Bfloat16, eccl.ReduceOp.Sum, stream=dev.stream)
-
-    rng = np.random.default_rng(wl["seed"] + 17 * rank)
-    q4 = lambda n, k: o.gen_q4k_weight(rng, n, k).reshape(-1)  # noqa: E731
+    torch, dev, ext, rank, world, ub = ctx.torch, ctx.dev, ctx.ext, ctx.rank, ctx.world, ctx.ub
+    all_reduce = ctx.all_reduce if world > 1 else None
     kind = wl["kind"]
     if kind == "tp":
         H, I, M = wl["hidden"], wl["inter"], wl["M"]
         ql, kvl, il = wl["q_heads"] * wl["head_dim"] // world, wl["kv_heads"] * wl["head_dim"] // world, I // world
-        shapes = [(ql + 2 * kvl, H), (H, ql), (2 * il, H), (H, il)]  # this rank's shards, generated at shard shape
+        shapes = [(ql + 2 * kvl, H), (H, ql), (2 * il, H), (H, il)]  # this rank's shards, filled at shard shape
         shard_bytes = sum(n * Q4K_ROW_BYTES(k) for n, k in shapes)
         total_bytes = shard_bytes * world
         flop = 2.0 * M * sum(n * k for n, k in shapes) * world
@@ -460,14 +564,12 @@ def run_sharded(args, wl, rank, world, torch, dist):
     layers = []
     for _c in range(ncopies):
         if kind == "tp":
-            ws_ = [q4(n, k) for n, k in shapes]
+            ws_ = [ctx.q4k_matrix(n, k) for n, k in shapes]
             layers.append(parallel.TPLinearStack(dev, H, I, wl["q_heads"], wl["kv_heads"], wl["head_dim"], world,
                                                  ws_[0], ws_[1], ws_[2], ws_[3], M, all_reduce))
         else:
-            w13 = np.concatenate([q4(2 * I, H) for _e in range(el)])
-            w2 = np.concatenate([q4(H, I) for _e in range(el)])
-            layers.append(parallel.EPMoELayer(dev, T, H, I, E, wl["top_k"], wl["block"], rank, world, w13, w2,
-                                              all_reduce))
+            layers.append(parallel.EPMoELayer(dev, T, H, I, E, wl["top_k"], wl["block"], rank, world,
+                                              ctx.q4k_matrix(el * 2 * I, H), ctx.q4k_matrix(el * H, I), all_reduce))
     xr = np.random.default_rng(wl["seed"])  # activations are replicated: same seed on every rank
     x_host = o.f32_to_bf16_bits(o.gen_activation(xr, in_elems // H, H, True)).reshape(-1)
     d_x = dev.htod_sync_copy(x_host)
@@ -480,51 +582,59 @@ def run_sharded(args, wl, rank, world, torch, dist):
         return layer.forward(d_x, wl["M"]) if kind == "tp" else layer.forward(d_x, d_logits)
 
     # one eager pass per copy (resolves symbols, sets attributes), then one CUDA graph per copy; with several
-    # GPUs the graphs contain the NCCL all-reduces
-    note("weights resident, %d copies" % ncopies)
+    # GPUs the graphs contain the all-reduces
     for layer in layers:
         forward(layer)
     dev.synchronize()
-    note("eager pass done")
-    use_graph = True
+    # the exchange checks itself: the layer's output with the one-shot kernel against the same layer with NCCL
+    check = None
+    if world > 1 and ctx.oneshot is not None and out_elems * 2 <= ctx.oneshot_limit:
+        a = dev.dtoh_sync_copy(layers[0].out, np.uint16, (out_elems,)).copy()
+        layers[0].all_reduce = ctx.nccl_all_reduce
+        forward(layers[0])
+        b_ = dev.dtoh_sync_copy(layers[0].out, np.uint16, (out_elems,)).copy()
+        layers[0].all_reduce = all_reduce
+        fa, fb = o.bf16_bits_to_f32(a).astype(np.float64), o.bf16_bits_to_f32(b_).astype(np.float64)
+        check = {"one_shot_vs_nccl_rel_l2": float(np.sqrt(((fa - fb) ** 2).sum() / max((fb ** 2).sum(), 1e-30)))}
     graphs = []
     with torch.cuda.stream(ext):
-        if use_graph:
-            for layer in layers:
-                g_ = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g_, stream=ext, capture_error_mode="thread_local"):
-                    forward(layer)
-                graphs.append(g_)
-            note("graphs captured")
-
-        def step(i):
-            if use_graph:
-                graphs[i % ncopies].replay()
-            else:
-                forward(layers[i % ncopies])
-
-        for i in range(args.warmup):
-            step(i)
+        for layer in layers:
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=ext, capture_error_mode="thread_local"):
+                forward(layer)
+            graphs.append(g_)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(3):
+            graphs[i % ncopies].replay()
+        ev0.record(ext)
+        for i in range(ncopies):
+            graphs[i].replay()
+        ev1.record(ext)
         ext.synchronize()
-        note("warm-up done")
+        k = replays_for(min_seconds, steps, CTL.max(ev0.elapsed_time(ev1) * 1e-3 / ncopies))
+        n = 0
+        for _ in range(warmup * k):
+            graphs[n % ncopies].replay()
+            n += 1
+        ext.synchronize()
         CTL.barrier()
         torch.cuda.synchronize()
-        sampler = ClockSampler(dev_index)
+        sampler = ClockSampler(ctx.dev_index)
         if rank == 0:
             sampler.start()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(ext)
-        for i in range(args.steps):
-            step(i)
+        for _ in range(steps * k):
+            graphs[n % ncopies].replay()
+            n += 1
         ev1.record(ext)
         ext.synchronize()
         torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else None
-    ms_total = ev0.elapsed_time(ev1)
-    note("timed region done: %.3f ms" % ms_total)
-    ms_total = CTL.max(ms_total)
-    ms_step = ms_total / args.steps
-    s_step = ms_step * 1e-3
+    ms_total = CTL.max(ev0.elapsed_time(ev1))
+    ms_step = ms_total / steps
+    s_layer = ms_total * 1e-3 / (steps * k)
+    # a bounded wait that ran out (one-shot all-reduce, mbarrier rings) leaves its code in the device error word
+    status = max(CTL.all_gather(int(dev.device_status())))
 
     def metric_value(sec):
         if wl["unit"] == "GB/s":
@@ -533,103 +643,129 @@ def run_sharded(args, wl, rank, world, torch, dist):
             return flop / sec / 1e12
         return wl["T"] / sec
 
-    value = metric_value(s_step)
-    # ---- end to end: host activations in, host result out, every step (eager launches through the API)
-    host_x = torch.from_numpy(x_host.view(np.uint8).reshape(-1).copy()).pin_memory()
-    host_y = torch.empty((out_elems * 2,), dtype=torch.uint8).pin_memory()
-    lib = ub.lib()
+    value = metric_value(s_layer)
+    e2e = None
+    if with_e2e:
+        # end to end: host activations in, host result out, every pass over the layer.  A single GPU launches
+        # the layer eagerly through the API; with several GPUs the pass replays the captured graph between
+        # the two copies, so that host launch cost does not hide the collectives.
+        host_x = torch.from_numpy(x_host.view(np.uint8).reshape(-1).copy()).pin_memory()
+        host_y = torch.empty((out_elems * 2,), dtype=torch.uint8).pin_memory()
+        lib = ub.lib()
+        e2e_graph = world > 1
 
-    # A single GPU launches the layer eagerly through the API.  With several GPUs the step replays the
-    # captured graph between the two copies, so that host launch cost does not hide the collectives.
-    e2e_graph = world > 1
+        def e2e_pass(i):
+            lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), ctypes.c_void_p(host_x.data_ptr()), host_x.numel())
+            if e2e_graph:
+                with torch.cuda.stream(ext):
+                    graphs[i % ncopies].replay()
+                out = layers[i % ncopies].out
+            else:
+                out = forward(layers[i % ncopies])
+            lib.ub_memcpy_dtoh(dev._handle, ctypes.c_void_p(host_y.data_ptr()), ctypes.c_void_p(out.ptr), host_y.numel())
+            dev.synchronize()
 
-    def e2e_step(i):
-        lib.ub_memcpy_htod(dev._handle, ctypes.c_void_p(d_x.ptr), ctypes.c_void_p(host_x.data_ptr()), host_x.numel())
-        if e2e_graph:
-            with torch.cuda.stream(ext):
-                graphs[i % ncopies].replay()
-            out = layers[i % ncopies].out
-        else:
-            out = forward(layers[i % ncopies])
-        lib.ub_memcpy_dtoh(dev._handle, ctypes.c_void_p(host_y.data_ptr()), ctypes.c_void_p(out.ptr), host_y.numel())
-        dev.synchronize()
-
-    note("end-to-end loop starts")
-    for i in range(max(3, args.warmup)):
-        e2e_step(i)
-    note("end-to-end warm-up done")
-    CTL.barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(i)
-    el_s = time.perf_counter() - t0
-    el_s = CTL.max(el_s)
-    note("end-to-end loop done")
-    e2e = {"value": metric_value(el_s / args.steps), "unit": wl["unit"], "h2d_bytes_per_step": int(host_x.numel()),
-           "d2h_bytes_per_step": int(host_y.numel()), "launch_mode": "cuda graph" if e2e_graph else "eager"}
+        for i in range(3):
+            e2e_pass(i)
+        reps = max(1, min(k, int(np.ceil(0.5 / (steps * max(s_layer, 1e-6))))))
+        CTL.barrier()
+        t0 = time.perf_counter()
+        for i in range(steps * reps):
+            e2e_pass(i)
+        el_s = CTL.max(time.perf_counter() - t0)
+        e2e = {"value": metric_value(el_s / (steps * reps)), "unit": wl["unit"],
+               "h2d_bytes_per_step": int(host_x.numel()) * reps, "d2h_bytes_per_step": int(host_y.numel()) * reps,
+               "launch_mode": "cuda graph" if e2e_graph else "eager"}
 
     peaks = measured_peaks()
-    # per-GPU roofline: this rank's shard bytes (or flop) per step against one GPU's measured peak
-    hbm = shard_bytes / s_step / 1e9
-    tf = flop / world / s_step / 1e12
-    tensor_peak = peaks["bf16_tflops"] if ms_total < 1000.0 else peaks["bf16_tflops_sustained"]
+    # per-GPU roofline: this rank's shard bytes (or flop) per pass against one GPU's measured peak
+    hbm = shard_bytes / s_layer / 1e9
+    tf = flop / world / s_layer / 1e12
+    burst = ms_total < 1000.0
+    tensor_peak = peaks["bf16_tflops"] if burst else peaks["bf16_tflops_sustained"]
     if wl["unit"] == "TFLOP/s":
-        roof = {"bound": "tensor", "achieved": tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": tf / tensor_peak}
+        roof = {"bound": "tensor", "achieved": tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": tf / tensor_peak,
+                "peak_kind": "burst" if burst else "sustained"}
     else:
         roof = {"bound": "hbm", "achieved": hbm, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": hbm / peaks["hbm_gbs"],
                 "tensor_frac": tf / tensor_peak}
-    roof.update({"traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": peaks["source"], "per_gpu": True,
-                 "algorithmic_bytes_per_step_per_gpu": shard_bytes, "algorithmic_flops_per_step": flop,
-                 "step_us": s_step * 1e6})
-    # kernels of ours per step: tp = 4 matmuls (+ conversions none: bf16) + copy + SiLU.up; ep = the fused layer
-    launches = args.steps * layers[0].launches_per_forward
-    if comm is not None:
-        # NCCL keeps a communicator alive while a CUDA graph that captured its collectives exists, and
-        # ncclCommDestroy waits for those references: release the graphs first
-        dev.synchronize()
-        graphs.clear()
-        g_ = None
-        import gc
-        gc.collect()
-        CTL.barrier()
-        note("graphs released")
-        if oneshot is not None:
-            oneshot.close()
-        comm.destroy()
-        note("communicator destroyed")
+    roof.update({"traffic": profile_traffic(wl_name), "peak_source": peaks["source"], "per_gpu": True,
+                 "algorithmic_bytes_per_pass_per_gpu": shard_bytes, "algorithmic_flops_per_pass": flop,
+                 "pass_us": s_layer * 1e6})
+    launches = steps * k * layers[0].launches_per_forward
+    # NCCL keeps a communicator alive while a CUDA graph that captured its collectives exists, and
+    # ncclCommDestroy waits for those references: release the graphs before anything else is torn down
+    dev.synchronize()
+    graphs.clear()
+    g_ = None
+    del layers
+    import gc
+    gc.collect()
+    CTL.barrier()
     return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
-                dtype="u4+f16 scales -> f32 accumulate", ncopies=ncopies,
-                launch_mode="cuda graph" if use_graph else "eager",
-                allreduce=("one-shot peer-memory kernel up to 64 KB, NCCL above" if world > 1 and oneshot_limit
+                dtype="u4+f16 scales -> f32 accumulate", ncopies=ncopies, replays_per_step=k,
+                timed_seconds=ms_total * 1e-3, launch_mode="cuda graph", device_status=status, allreduce_check=check,
+                allreduce=("one-shot peer-memory kernel up to 64 KB, NCCL above" if world > 1 and ctx.oneshot_limit
                            else ("NCCL" if world > 1 else "none")))
+
+
+def describe(wl_name, wl, n_gpus, res=None):
+    k = res["replays_per_step"] if res else 1
+    if "kind" in wl:
+        cfg = {"workload": "%s: %s; one step = %d passes over the layer; consecutive passes use distinct weight "
+                           "copies (>= 300 MB per GPU in total, larger than L2)" % (wl_name, wl["desc"], k),
+               "M": wl.get("M"), "format": "Q4_K", "l2_policy": "inputs larger than L2",
+               "parallelism": "%s%d" % (wl["kind"], n_gpus)}
+        if res:
+            cfg.update({"launch_mode": res["launch_mode"], "weight_copies": res["ncopies"], "allreduce": res["allreduce"]})
+    else:
+        per_replay = wl["copies"] * wl.get("passes", 1)
+        cfg = {"workload": "%s: %s; one step = %d graph replays of %d matmuls over %d distinct weight copies (%.0f MB, "
+                           "larger than L2)" % (wl_name, wl["desc"], k, per_replay, wl["copies"],
+                                                wl["copies"] * wl["N"] * wl_row_bytes(wl) / 1e6),
+               "N": wl["N"], "K": wl["K"], "M": wl["M"], "format": wl_format(wl),
+               "l2_policy": "inputs larger than L2", "parallelism": "replicas x%d" % n_gpus}
+    if res:
+        cfg["replays_per_step"] = k
+        cfg["timed_region_s"] = round(res["timed_seconds"], 3)
+    return cfg
+
+
+def short_record(wl_name, wl, n_gpus, res):
+    """A secondary / sharded result as carried inside the headline line."""
+    rec = {"workload": wl_name, "metric": METRIC_OF[wl["unit"]], "value": res["value"], "unit": wl["unit"],
+           "ms_per_step": res["ms_per_step"], "config": describe(wl_name, wl, n_gpus, res),
+           "roofline": res["roofline"], "gpu_launches": res["launches"], "clocks": res["clocks"]}
+    if "kind" in wl:
+        rec["scaling"] = "strong"
+        rec["device_status"] = res["device_status"]
+        if res["allreduce_check"]:
+            rec["allreduce_check"] = res["allreduce_check"]
+    return rec
+
+
+METRIC_OF = {"GB/s": "weight_GBps", "TFLOP/s": "TFLOPS", "tok/s": "moe_tokens_per_s"}
+SECONDARY = ["c1", "c2_m4", "c2_m16", "c3"]   # single-GPU configurations carried by the default line
+SHARDED = ["c5_m1", "c5_m512", "c4"]          # strong-scaling configurations carried at every GPU count
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=500)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_m1", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
+    ap.add_argument("--min-seconds", type=float, default=2.0, help="least duration of the timed region")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    metric = {"GB/s": "weight_GBps", "TFLOP/s": "TFLOPS", "tok/s": "moe_tokens_per_s"}[wl["unit"]]
+    metric = METRIC_OF[wl["unit"]]
     sharded = "kind" in wl
-    if sharded:
-        config = {"workload": "%s: %s; one step = one pass over the layer; consecutive steps use distinct weight "
-                              "copies (>= 300 MB per GPU in total, larger than L2)" % (args.workload, wl["desc"]),
-                  "M": wl["M"], "format": "Q4_K", "l2_policy": "inputs larger than L2",
-                  "parallelism": "%s%d" % (wl["kind"], args.gpus)}
-    else:
-        config = {"workload": "%s: %s; one step = %d matmuls over %d distinct weight copies (%.0f MB, larger than "
-                              "L2)" % (args.workload, wl["desc"], wl["copies"] * wl.get("passes", 1), wl["copies"],
-                                       wl["copies"] * wl["N"] * wl_row_bytes(wl) / 1e6),
-                  "N": wl["N"], "K": wl["K"], "M": wl["M"], "format": wl_format(wl),
-                  "l2_policy": "inputs larger than L2", "parallelism": "replicas x%d" % args.gpus}
 
     if args.impl == "reference":
         if rank != 0:
@@ -647,7 +783,7 @@ def main():
         line = {"impl": "reference", "metric": metric, "value": value, "unit": wl["unit"], "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
                 "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": config,
+                "config": describe(args.workload, wl, args.gpus),
                 "cpu_baseline": {"value": value, "unit": wl["unit"], "cores": cores, "kind": "port",
                                  "sample": "each step: " + sample},
                 "e2e": {"value": value, "unit": wl["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -655,37 +791,88 @@ def main():
         print(json.dumps(line))
         return
 
+    if world > 1:
+        # leave NCCL's communicator-initialisation lines on: they are the record of how many ranks the
+        # data path's communicator really spans
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
     import torch
     import torch.distributed as dist
 
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-        # torch's own NCCL communicator is created lazily and never used: every collective of the control
-        # plane goes through the CPU group of Control
-        dist.init_process_group("nccl")
+        # the control plane (barriers, max over ranks, unique-id hand-over) is a CPU group: torch creates no
+        # NCCL communicator of its own
+        dist.init_process_group("gloo")
     global CTL
     CTL = Control(torch, dist, world)
+    ctx = None
     try:
-        res = (run_sharded if sharded else run_linear)(args, wl, rank, world, torch, dist)
+        extras = args.workload == "c2_m1" and not args.no_extras
+        if sharded:
+            ctx = ShardedContext(rank, world, torch)
+            res = run_sharded(ctx, args.workload, wl, args.steps, args.warmup, args.min_seconds)
+        else:
+            res = run_linear(args.workload, wl, args.steps, args.warmup, args.min_seconds, rank, world, torch)
+        secondary, sharded_recs = [], []
+        if extras:
+            torch.cuda.empty_cache()
+            if world == 1:
+                for name in SECONDARY:
+                    try:
+                        r = run_linear(name, WORKLOADS[name], args.steps, args.warmup, min(args.min_seconds, 1.0), rank,
+                                       world, torch, with_e2e=False)
+                        secondary.append(short_record(name, WORKLOADS[name], world, r))
+                    except Exception as exc:  # a secondary record must not take the headline down
+                        secondary.append({"workload": name, "error": repr(exc)})
+                    torch.cuda.empty_cache()
+            ctx = ShardedContext(rank, world, torch)
+            for name in SHARDED:
+                try:
+                    r = run_sharded(ctx, name, WORKLOADS[name], args.steps, args.warmup, min(args.min_seconds, 1.0),
+                                    with_e2e=False)
+                    sharded_recs.append(short_record(name, WORKLOADS[name], world, r))
+                except Exception as exc:
+                    sharded_recs.append({"workload": name, "error": repr(exc)})
+                torch.cuda.empty_cache()
+        if ctx is not None:
+            ctx.close()
+            ctx = None
         if rank == 0:
             cpu = None
             if world == 1:
                 arm = CpuArm(wl)
                 v, sample = arm.run(args.cpu_seconds)
                 cpu = {"value": v, "unit": wl["unit"], "cores": arm.cores, "kind": "port", "sample": sample}
-            if "launch_mode" in res:
-                config["launch_mode"] = res["launch_mode"]
-                config["weight_copies"] = res["ncopies"]
-                config["allreduce"] = res["allreduce"]
             line = {"metric": metric, "value": res["value"], "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
                     "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
                     "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": res["dtype"],
-                    "data": "synthetic",
-                    "config": config, "roofline": res["roofline"], "cpu_baseline": cpu, "e2e": res["e2e"],
+                    "data": "synthetic", "config": describe(args.workload, wl, world, res),
+                    "roofline": res["roofline"], "cpu_baseline": cpu, "e2e": res["e2e"],
                     "gpu_launches": res["launches"], "clocks": res["clocks"]}
-            print(json.dumps(line))
+            if res.get("e2e_per_call"):
+                line["e2e_per_call"] = res["e2e_per_call"]
+            if sharded:
+                line["device_status"] = res["device_status"]
+                if res["allreduce_check"]:
+                    line["allreduce_check"] = res["allreduce_check"]
+            if secondary:
+                line["secondary"] = secondary
+            if sharded_recs:
+                line["sharded"] = sharded_recs
+            bad = [r for r in ([line] if sharded else []) + sharded_recs if r.get("device_status")]
+            if bad:
+                line["error"] = "device error word set (a bounded device-side wait ran out): " + ", ".join(
+                    "%s=%d" % (r.get("workload", args.workload), r["device_status"]) for r in bad)
+            sys.stdout.flush()
+            print(json.dumps(line), flush=True)
     finally:
+        if ctx is not None:
+            try:
+                ctx.close()
+            except Exception:
+                pass
         if world > 1:
             dist.destroy_process_group()
 

@@ -259,7 +259,8 @@ int ub_moe_layer_q4k(void* out, const void* hidden, const void* router_logits, c
  * process call ub_enable_peer_access and use the pointer itself.  `staging` is a host array of `world` device
  * pointers in rank order (own buffer at [rank]).  data (bf16, count % 8 == 0, 16-byte aligned, count*2 <=
  * max_bytes) is summed in place over the ranks, in rank order, on every rank.  All ranks must issue the same
- * sequence of calls.  The wait for the peers is bounded (UB_ERR_TIMEOUT in the device error word). */
+ * sequence of calls.  The wait for the peers is bounded (UB_ERR_TIMEOUT in the device error word, see
+ * ub_allreduce_oneshot_set_spin_limit). */
 int ub_p2p_alloc(size_t bytes, void** out_ptr);   /* zero-filled, mappable by peers (cudaMalloc, synchronous) */
 int ub_p2p_free(void* ptr);
 int ub_ipc_get_handle(void* dev_ptr, void* handle64);
@@ -268,6 +269,12 @@ int ub_ipc_close_handle(void* ptr);
 int ub_enable_peer_access(int peer_device);
 size_t ub_allreduce_oneshot_staging_bytes(int world, size_t max_bytes);
 int ub_allreduce_oneshot_bf16(void* data, size_t count, void* const* staging, int rank, int world, size_t max_bytes, void* stream);
+/* Polls of a peer's flag (about half a microsecond each; default 2 000 000, i.e. one to two seconds) before a
+ * call gives up, records UB_ERR_TIMEOUT in the device error word and returns with an undefined result: read
+ * ub_device_status before trusting the output of a run in which a rank may have gone away.  0 restores the
+ * default; applies to later launches, process-wide; returns the previous limit.  No reference counterpart
+ * (the reference has no bounded waits). */
+unsigned ub_allreduce_oneshot_set_spin_limit(unsigned polls);
 
 /* ------------------------------------------------------------------ collectives
  * ECCL-shaped surface (src/eccllib.rs:7-169, src/eccl.rs:14-426) forwarding to NCCL over

@@ -199,6 +199,49 @@ def qmatmul_exact(x_f32: np.ndarray, w_deq_f32: np.ndarray) -> np.ndarray:
     return (x_f32.astype(np.float64) @ w_deq_f32.astype(np.float64).T).astype(np.float32)
 
 
+def qmatmul_q8act(x_f32: np.ndarray, wq: np.ndarray, N: int, K: int, is_q4k: bool) -> np.ndarray:
+    """numpy restatement of the "q8act" arm (see ub_oracle_qmatmul_q8act_f32): activation rows quantised to 8-bit
+    blocks, integer block dots, f32 accumulation over blocks in block order."""
+    x = np.asarray(x_f32, dtype=np.float32)
+    M = x.shape[0]
+    if not is_q4k:
+        nb = K // QK8_0
+        blk = np.asarray(wq, dtype=np.uint8).reshape(N, nb, Q8_0_BYTES)
+        dw = blk[..., :2].copy().view(np.float16)[..., 0].astype(np.float32)
+        qw = blk[..., 2:].view(np.int8).astype(np.int32)
+        xb = x.reshape(M, nb, QK8_0)
+        amax = np.abs(xb).max(axis=2)
+        d = (amax / np.float32(127.0)).astype(np.float32)
+        inv = np.where(d != 0, np.float32(1.0) / np.where(d != 0, d, 1), 0).astype(np.float32)
+        v = xb * inv[..., None]
+        qx = (np.sign(v) * np.floor(np.abs(v) + np.float32(0.5))).astype(np.int32)  # half away from zero
+        dx = d.astype(np.float16).astype(np.float32)
+        dots = np.einsum("nbi,mbi->mnb", qw, qx).astype(np.float32)
+        terms = dots * dw[None] * dx[:, None, :]
+    else:
+        nb = K // QK_K
+        blk = np.asarray(wq, dtype=np.uint8).reshape(N, nb, Q4K_BYTES)
+        dw = blk[..., 0:2].copy().view(np.float16)[..., 0].astype(np.float32)
+        mw = blk[..., 2:4].copy().view(np.float16)[..., 0].astype(np.float32)
+        sc, mn = unpack_scales_k4(blk[..., 4:16])
+        qs = blk[..., 16:].reshape(N, nb, 4, 32)
+        q4 = np.stack([qs & 0xF, qs >> 4], axis=3).reshape(N, nb, 8, 32).astype(np.int32)
+        xb = x.reshape(M, nb, QK_K)
+        idx = np.abs(xb).argmax(axis=2)
+        mx = np.take_along_axis(xb, idx[..., None], axis=2)[..., 0]
+        iscale = np.where(mx != 0, np.float32(-128.0) / np.where(mx != 0, mx, 1), 0).astype(np.float32)
+        q8 = np.minimum(np.rint(xb * iscale[..., None]), 127).astype(np.int32).reshape(M, nb, 8, 32)
+        dx = np.where(iscale != 0, np.float32(1.0) / np.where(iscale != 0, iscale, 1), 0).astype(np.float32)
+        sub = np.einsum("nbji,mbji->mnbj", q4, q8)
+        sumi = (sub * sc[None].astype(np.int64)).sum(axis=3).astype(np.float32)
+        summ = (q8.sum(axis=3)[:, None] * mn[None].astype(np.int64)).sum(axis=3).astype(np.float32)
+        terms = dw[None] * dx[:, None, :] * sumi - mw[None] * dx[:, None, :] * summ
+    y = np.zeros((M, N), dtype=np.float32)
+    for b in range(terms.shape[2]):
+        y += terms[:, :, b]
+    return y
+
+
 def rel_l2(a: np.ndarray, ref: np.ndarray) -> float:
     a = np.asarray(a, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
@@ -454,11 +497,13 @@ def clib() -> ctypes.CDLL:
             "ub_oracle_silu_and_mul": [vp, vp, i, i, i], "ub_oracle_topk_sum": [vp, vp, i, i, i, i],
             "ub_oracle_moe_combine": [vp] * 5 + [i] * 5,
             "ub_oracle_indexed_moe": [vp] * 4 + [i] * 7,
+            "ub_oracle_qmatmul_q8act_f32": [vp, vp, vp, i, i, i, i],
+            "ub_oracle_set_threads": [i],
         }
         for name, args in sigs.items():
             fn = getattr(h, name)
             fn.argtypes = args
-            fn.restype = ctypes.c_int if name == "ub_oracle_moe_align" else None
+            fn.restype = ctypes.c_int if name in ("ub_oracle_moe_align", "ub_oracle_set_threads") else None
         _clib = h
     return _clib
 
@@ -498,6 +543,22 @@ def c_qmatmul(x_f32: np.ndarray, wq: np.ndarray, N: int, K: int, is_q4k, exact: 
     fn = clib().ub_oracle_qmatmul_exact if exact else clib().ub_oracle_qmatmul_f32
     fn(_p(x), _p(w), _p(y), M, N, K, int(is_q4k))
     return y
+
+
+def c_qmatmul_q8act(x_f32: np.ndarray, wq: np.ndarray, N: int, K: int, is_q4k) -> np.ndarray:
+    """The informational "q8act" arm: activation rows quantised to 8-bit blocks before integer block dots, as
+    GGML-family CPU back ends do (Q8_0 blocks against Q8_0 weights, 256-wide int8 blocks against Q4_K weights)."""
+    x = np.ascontiguousarray(x_f32, dtype=np.float32)
+    w = np.ascontiguousarray(wq, dtype=np.uint8)
+    M = x.shape[0]
+    y = np.empty((M, N), dtype=np.float32)
+    clib().ub_oracle_qmatmul_q8act_f32(_p(x), _p(w), _p(y), M, N, K, int(is_q4k))
+    return y
+
+
+def set_threads(n: int) -> int:
+    """Sets the OpenMP thread count of the C restatement; returns the count in effect."""
+    return int(clib().ub_oracle_set_threads(int(n)))
 
 
 def c_quantize_q8_0(x_f32: np.ndarray) -> np.ndarray:

@@ -367,6 +367,135 @@ void ub_oracle_qmatmul_f32(const float* x, const uint8_t* wq, float* y, int M, i
   }
 }
 
+/* ---------------------------------------------------------------- "q8act" arm (informational)
+ * GGML-family CPU back ends (candle's quantized matmul among them, the parity target the task names) do not
+ * multiply f32 activations with dequantised weights: they first quantise every activation row to 8-bit blocks
+ * and take integer dot products per block.  This arm restates that published algorithm so that the distance
+ * between it and the exact arm above can be reported:
+ *   Q8_0 weights: activations -> Q8_0 blocks of 32 (d = amax/127 kept in f16, q = round(x/d); the quantiser of
+ *                 kernels/quant.cpp:280-289), block result d_w * d_x * sum(q_w * q_x);
+ *   Q4_K weights: activations -> 256-wide int8 blocks with an f32 scale (GGML's Q8_K: iscale = -128/max where
+ *                 max is the SIGNED value of largest magnitude, q = min(127, round(iscale * x)), d = 1/iscale),
+ *                 block result d_w*d_x*sum_j sc_j*sum(q4*q8) - dmin_w*d_x*sum_j m_j*sum_j(q8).
+ * No version of candle is pinned by the reference, so this arm is not a gate. */
+static float round_half_away(float v) { return roundf(v); }
+
+void ub_oracle_qmatmul_q8act_f32(const float* x, const uint8_t* wq, float* y, int M, int N, int K, int fmt) {
+  if (fmt == 0) {
+    const int nb = K / QK8_0;
+    int8_t* xq = (int8_t*)malloc((size_t)M * K);
+    float* xd = (float*)malloc((size_t)M * nb * sizeof(float));
+    for (int m = 0; m < M; m++)
+      for (int b = 0; b < nb; b++) {
+        const float* xr = x + (size_t)m * K + (size_t)b * QK8_0;
+        float amax = 0.f;
+        for (int i = 0; i < QK8_0; i++) amax = fmaxf(amax, fabsf(xr[i]));
+        const float d = amax / 127.f, id = d != 0.f ? 1.f / d : 0.f;
+        for (int i = 0; i < QK8_0; i++) xq[(size_t)m * K + (size_t)b * QK8_0 + i] = (int8_t)round_half_away(xr[i] * id);
+        xd[(size_t)m * nb + b] = f16_to_f32(f32_to_f16(d));
+      }
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; n++)
+      for (int m = 0; m < M; m++) {
+        float acc = 0.f;
+        for (int b = 0; b < nb; b++) {
+          const uint8_t* blk = wq + ((size_t)n * nb + b) * Q8_0_BYTES;
+          uint16_t dh;
+          memcpy(&dh, blk, 2);
+          const int8_t* qw = (const int8_t*)(blk + 2);
+          const int8_t* qx = xq + (size_t)m * K + (size_t)b * QK8_0;
+          int s = 0;
+          for (int i = 0; i < QK8_0; i++) s += (int)qw[i] * (int)qx[i];
+          acc += f16_to_f32(dh) * xd[(size_t)m * nb + b] * (float)s;
+        }
+        y[(size_t)m * N + n] = acc;
+      }
+    free(xq);
+    free(xd);
+    return;
+  }
+  /* Q4_K weights x 256-wide int8 activation blocks */
+  const int nb = K / QK_K;
+  int8_t* xq = (int8_t*)malloc((size_t)M * K);
+  float* xd = (float*)malloc((size_t)M * nb * sizeof(float));
+  int* bs = (int*)malloc((size_t)M * nb * 8 * sizeof(int)); /* sums of q over the 8 sub-blocks of 32 */
+  for (int m = 0; m < M; m++)
+    for (int b = 0; b < nb; b++) {
+      const float* xr = x + (size_t)m * K + (size_t)b * QK_K;
+      float max = 0.f, amax = 0.f;
+      for (int i = 0; i < QK_K; i++) {
+        const float ax = fabsf(xr[i]);
+        if (ax > amax) amax = ax, max = xr[i];
+      }
+      int8_t* q = xq + (size_t)m * K + (size_t)b * QK_K;
+      if (amax == 0.f) {
+        memset(q, 0, QK_K);
+        xd[(size_t)m * nb + b] = 0.f;
+      } else {
+        const float iscale = -128.f / max;
+        for (int i = 0; i < QK_K; i++) {
+          int v = (int)lrintf(iscale * xr[i]); /* nearest, ties to even, as GGML's nearest_int */
+          q[i] = (int8_t)(v > 127 ? 127 : v);
+        }
+        xd[(size_t)m * nb + b] = 1.f / iscale;
+      }
+      for (int j = 0; j < 8; j++) {
+        int sacc = 0;
+        for (int i = 0; i < 32; i++) sacc += q[32 * j + i];
+        bs[((size_t)m * nb + b) * 8 + j] = sacc;
+      }
+    }
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; n++)
+    for (int m = 0; m < M; m++) {
+      float acc = 0.f;
+      for (int b = 0; b < nb; b++) {
+        const uint8_t* blk = wq + ((size_t)n * nb + b) * Q4K_BYTES;
+        uint16_t dh, mh;
+        memcpy(&dh, blk, 2);
+        memcpy(&mh, blk + 2, 2);
+        const uint8_t* scales = blk + 4;
+        const uint8_t* qs = blk + 16;
+        const int8_t* q8 = xq + (size_t)m * K + (size_t)b * QK_K;
+        const int* bsum = bs + ((size_t)m * nb + b) * 8;
+        int sumi = 0, summ = 0;
+        for (int g = 0; g < 4; g++) {
+          uint8_t sc0, m0, sc1, m1;
+          scale_min_k4(2 * g, scales, &sc0, &m0);
+          scale_min_k4(2 * g + 1, scales, &sc1, &m1);
+          int lo = 0, hi = 0;
+          for (int i = 0; i < 32; i++) {
+            lo += (int)(qs[32 * g + i] & 0xF) * (int)q8[64 * g + i];
+            hi += (int)(qs[32 * g + i] >> 4) * (int)q8[64 * g + 32 + i];
+          }
+          sumi += (int)sc0 * lo + (int)sc1 * hi;
+          summ += (int)m0 * bsum[2 * g] + (int)m1 * bsum[2 * g + 1];
+        }
+        const float dx = xd[(size_t)m * nb + b];
+        acc += f16_to_f32(dh) * dx * (float)sumi - f16_to_f32(mh) * dx * (float)summ;
+      }
+      y[(size_t)m * N + n] = acc;
+    }
+  free(xq);
+  free(xd);
+  free(bs);
+}
+
+/* OpenMP thread count of the CPU arm: launchers such as torch.distributed.run export OMP_NUM_THREADS=1, so the
+ * arm sets its thread count explicitly and reports what it got. */
+#ifdef _OPENMP
+#include <omp.h>
+int ub_oracle_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+}
+#else
+int ub_oracle_set_threads(int n) {
+  (void)n;
+  return 1;
+}
+#endif
+
 /* ---------------------------------------------------------------- MoE router */
 
 /* kernels/topk_softmax_host.cpp:121-172.  f32 softmax, k rounds of strict-greater arg-max

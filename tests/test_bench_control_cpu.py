@@ -71,3 +71,13 @@ def test_workload_table_is_consistent():
             assert (wl["q_heads"] % 8, wl["kv_heads"] % 8) == (0, 0)
         if wl.get("kind") == "ep":
             assert wl["E"] % 8 == 0 and wl["flop_per_token"] == 2 * 3 * 2.0 * wl["H"] * wl["I"]
+
+
+def test_timed_region_sizing_and_profile_lookup():
+    # steps x k replays must reach the minimum duration; never fewer than one replay per step
+    assert bench.replays_for(2.0, 20, 0.85e-3) == 118
+    assert bench.replays_for(2.0, 20, 1.0) == 1
+    assert bench.replays_for(2.0, 20, 0.0) == 1
+    # roofline.traffic comes from the profile summaries, not from a constant in the script
+    assert bench.profile_traffic("c1") == 17896448
+    assert bench.profile_traffic("c5_m1") is None

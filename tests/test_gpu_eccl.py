@@ -58,3 +58,42 @@ def test_all_reduce_across_devices_threads_as_ranks():
         t.join(timeout=120)
     for r in range(n):
         assert results[r] is not None and (results[r] == n * (n + 1) / 2).all()
+
+
+def test_one_shot_all_reduce_gives_up_when_a_rank_never_arrives(dev):
+    """Failure detection without a fault: world = 2 with both staging buffers on this GPU, only rank 0 ever
+    launches, so rank 1's flag is never raised.  With a small poll limit the wait runs out in well under a
+    second, the kernel returns, the context stays usable and the device error word reads UB_ERR_TIMEOUT."""
+    import ctypes
+    import time
+
+    from ubridge_b200._lib import UB_ERR_TIMEOUT, check, lib
+
+    dev.bind_to_thread()
+    dev.synchronize()
+    assert dev.device_status() == 0
+    world, max_bytes, count = 2, 4096, 1024
+    nbytes = lib().ub_allreduce_oneshot_staging_bytes(world, max_bytes)
+    bufs = []
+    for _ in range(world):
+        p = ctypes.c_void_p()
+        check(lib().ub_p2p_alloc(nbytes, ctypes.byref(p)), "ub_p2p_alloc")
+        bufs.append(p.value)
+    table = (ctypes.c_void_p * world)(*bufs)
+    x = np.ones(count, dtype=np.uint16) * 0x3F80  # bf16 1.0
+    d_x = dev.htod_sync_copy(x)
+    prev = lib().ub_allreduce_oneshot_set_spin_limit(2000)
+    try:
+        t0 = time.perf_counter()
+        check(lib().ub_allreduce_oneshot_bf16(ctypes.c_void_p(d_x.ptr), count, table, 0, world, max_bytes, dev.stream),
+              "ub_allreduce_oneshot_bf16")
+        dev.synchronize()
+        assert time.perf_counter() - t0 < 1.0
+        assert dev.device_status() == UB_ERR_TIMEOUT  # read and clear
+        assert dev.device_status() == 0
+        # the context is intact: an ordinary copy still works
+        assert np.array_equal(dev.dtoh_sync_copy(dev.htod_sync_copy(x), np.uint16), x)
+    finally:
+        lib().ub_allreduce_oneshot_set_spin_limit(prev)
+        for p in bufs:
+            lib().ub_p2p_free(ctypes.c_void_p(p))

@@ -80,6 +80,7 @@ _SIGS = {
     "ub_enable_peer_access": (c_int, [c_int]),
     "ub_allreduce_oneshot_staging_bytes": (c_size_t, [c_int, c_size_t]),
     "ub_allreduce_oneshot_bf16": (c_int, [_P, c_size_t, ctypes.POINTER(_P), c_int, c_int, c_size_t, _P]),
+    "ub_allreduce_oneshot_set_spin_limit": (ctypes.c_uint, [ctypes.c_uint]),
     "ub_synchronize": (c_int, [_P]),
     "ub_get_function": (_P, [c_char_p, c_char_p]),
     "ub_has_function": (c_int, [c_char_p, c_char_p]),

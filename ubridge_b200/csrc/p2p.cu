@@ -12,9 +12,13 @@
 //   [1024 ..]      slots[2][world][max_bytes]
 // Two sets alternate by epoch parity: a rank can start epoch k+2 only after it has seen every peer's flag of
 // epoch k+1, which a peer raises only after it has finished reading epoch k.
-// The wait on the flags is bounded; on expiry the kernel records UB_ERR_TIMEOUT in the device error word and
-// still leaves (the result is then undefined).  No multimem, no cluster features: peer loads and stores only.
+// The wait on the flags is bounded (a launch parameter, ub_allreduce_oneshot_set_spin_limit; the default is one
+// to two seconds of polling); on expiry the kernel records UB_ERR_TIMEOUT in the device error word and still
+// leaves: it adds whatever the slots hold, so the result of that call is undefined and the caller must read
+// ub_device_status before trusting it.  No multimem, no cluster features: peer loads and stores only.
 #include <string.h>
+
+#include <atomic>
 
 #include "common.cuh"
 
@@ -22,7 +26,8 @@ namespace {
 
 using namespace ub;
 
-constexpr uint32_t kFlagSpinLimit = 4000000;  // about a second of polling
+constexpr uint32_t kDefaultFlagSpinLimit = 2000000;  // polls of ~0.5 us each: one to two seconds
+std::atomic<uint32_t> g_flag_spin_limit{kDefaultFlagSpinLimit};
 constexpr size_t kFlagsOff = 128, kSlotsOff = 1024;
 constexpr int kMaxWorld = 16;
 
@@ -46,7 +51,7 @@ __device__ __forceinline__ uint4 ld_cg16(const void* p) {
 
 __global__ void __launch_bounds__(1024, 1)
 allreduce_oneshot_bf16_kernel(__nv_bfloat16* __restrict__ data, size_t count, PeerTable peers, int rank, int world,
-                              size_t max_bytes, int* err_word) {
+                              size_t max_bytes, uint32_t spin_limit, int* err_word) {
   __shared__ uint32_t s_epoch;
   unsigned char* const mine = peers.base[rank];
   if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(mine) + 1;
@@ -69,7 +74,7 @@ allreduce_oneshot_bf16_kernel(__nv_bfloat16* __restrict__ data, size_t count, Pe
   if (threadIdx.x < world) {
     const uint32_t* f = reinterpret_cast<const uint32_t*>(mine + kFlagsOff) + set * world + threadIdx.x;
     bool seen = false;
-    for (uint32_t it = 0; it < kFlagSpinLimit; it++) {
+    for (uint32_t it = 0; it < spin_limit; it++) {
       if (ld_acquire_sys(f) == epoch) {
         seen = true;
         break;
@@ -185,6 +190,13 @@ size_t ub_allreduce_oneshot_staging_bytes(int world, size_t max_bytes) {
   return kSlotsOff + 2 * static_cast<size_t>(world) * max_bytes;
 }
 
+// Polls of a peer's flag (about half a microsecond each) before a call gives up with UB_ERR_TIMEOUT in the
+// device error word; 0 restores the default.  Applies to launches made after the call, process-wide.
+// Returns the previous limit.
+unsigned ub_allreduce_oneshot_set_spin_limit(unsigned polls) {
+  return g_flag_spin_limit.exchange(polls ? polls : kDefaultFlagSpinLimit, std::memory_order_relaxed);
+}
+
 int ub_allreduce_oneshot_bf16(void* data, size_t count, void* const* staging, int rank, int world, size_t max_bytes,
                               void* stream) {
   if (!data || !staging || world <= 0 || world > kMaxWorld || rank < 0 || rank >= world)
@@ -199,7 +211,8 @@ int ub_allreduce_oneshot_bf16(void* data, size_t count, void* const* staging, in
   const size_t nvec = count / 8;
   const int threads = nvec >= 1024 ? 1024 : static_cast<int>((nvec + 31) / 32 * 32);  // >= 32 >= world
   allreduce_oneshot_bf16_kernel<<<1, threads, 0, ub::as_stream(stream)>>>(
-      static_cast<__nv_bfloat16*>(data), count, t, rank, world, max_bytes, ub::device_error_word());
+      static_cast<__nv_bfloat16*>(data), count, t, rank, world, max_bytes,
+      g_flag_spin_limit.load(std::memory_order_relaxed), ub::device_error_word());
   return ub::check_launch();
 }
 

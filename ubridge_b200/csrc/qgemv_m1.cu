@@ -96,23 +96,33 @@ __device__ __forceinline__ uint32_t pack4_m1(int a, int b, int c, int d) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
+// Eight activations of a lane: the load and the conversion are separate steps, so that nothing between them
+// (the requests for the rest of the ring) waits for the data to arrive.
 template <typename XT>
-__device__ __forceinline__ void ld8(const XT* p, float (&v)[8]);
+struct Raw8;
 template <>
-__device__ __forceinline__ void ld8<float>(const float* p, float (&v)[8]) {
-  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-}
-template <>
-__device__ __forceinline__ void ld8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
-  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
-  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
   }
-}
+  __device__ __forceinline__ void unpack(float (&v)[8]) const {
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+  }
+};
+template <>
+struct Raw8<__nv_bfloat16> {
+  uint4 r;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { r = __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void unpack(float (&v)[8]) const {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+};
 
 __device__ __forceinline__ void st_out(void* y, size_t idx, int dtype, float v) {
   if (dtype == UB_DTYPE_F32)
@@ -182,12 +192,15 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
   int Sa[SBW], Sb[SBW];  // sums of q over sub-blocks t and 4 + t (for the min term)
   float xs[SBW];
   {
-    float v[SBW][8];
+    Raw8<XT> raw[SBW];
 #pragma unroll
-    for (int k = 0; k < SBW; k++) ld8<XT>(x + static_cast<size_t>(warp + 8 * k) * 256 + 8 * lane, v[k]);
+    for (int k = 0; k < SBW; k++) raw[k].load(x + static_cast<size_t>(warp + 8 * k) * 256 + 8 * lane);
     // the rest of the ring goes out right behind the activation loads
     if (threadIdx.x == 0)
       for (int n = n_early; n < min(S, my_tiles); n++) issue_tile(n);
+    float v[SBW][8];
+#pragma unroll
+    for (int k = 0; k < SBW; k++) raw[k].unpack(v[k]);
 #pragma unroll
     for (int k = 0; k < SBW; k++) {
       float amax = 0.f;

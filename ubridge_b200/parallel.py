@@ -98,12 +98,17 @@ def expert_map(E: int, rank: int, world: int) -> np.ndarray:
 AllReduce = Callable[[object, int], None]  # (device buffer, element count) -> in-place bf16 sum
 
 
+def _resident(dev, w):
+    """Packed weights as a device buffer: host arrays are uploaded, device buffers are taken as they are."""
+    return w if hasattr(w, "ptr") else dev.htod_sync_copy(w)
+
+
 class TPLinearStack:
     """Llama-style linear stack under tensor parallelism: qkv (column) -> o (row) -> all-reduce ->
     gate/up (column, SiLU.up) -> down (row) -> all-reduce.  Attention itself is not part of this path:
     the first `hidden` columns of this rank's q output feed o, which keeps the data flow and sizes.
 
-    `dev` is a GcuDevice; weights are numpy block arrays already sharded for this rank; `all_reduce`
+    `dev` is a GcuDevice; weights are numpy block arrays (or device buffers) already sharded for this rank; `all_reduce`
     is called with (buffer, count) after each row-split GEMM (None for a single rank)."""
 
     def __init__(self, dev, hidden: int, inter: int, n_q_heads: int, n_kv_heads: int, head_dim: int, world: int,
@@ -115,10 +120,8 @@ class TPLinearStack:
         self.qkv_n = self.q_local + 2 * self.kv_local
         self.i_local = inter // world
         self.all_reduce = all_reduce
-        self.w_qkv = dev.htod_sync_copy(w_qkv)
-        self.w_o = dev.htod_sync_copy(w_o)
-        self.w_gu = dev.htod_sync_copy(w_gate_up)
-        self.w_down = dev.htod_sync_copy(w_down)
+        self.w_qkv, self.w_o = _resident(dev, w_qkv), _resident(dev, w_o)
+        self.w_gu, self.w_down = _resident(dev, w_gate_up), _resident(dev, w_down)
         self.max_m = max_m
         self.qkv = dev.alloc(max_m * self.qkv_n * 2)
         self.attn = dev.alloc(max_m * self.q_local * 2)
@@ -172,8 +175,7 @@ class EPMoELayer:
                  w13_local: np.ndarray, w2_local: np.ndarray, all_reduce: Optional[AllReduce] = None):
         self.dev, self.T, self.H, self.I, self.E, self.top_k, self.block = dev, T, H, I, E, top_k, block
         self.all_reduce = all_reduce
-        self.w13 = dev.htod_sync_copy(w13_local)
-        self.w2 = dev.htod_sync_copy(w2_local)
+        self.w13, self.w2 = _resident(dev, w13_local), _resident(dev, w2_local)
         self.map = dev.htod_sync_copy(expert_map(E, rank, world)) if world > 1 else None
         self.ws_bytes = ops.moe_layer_q4k_workspace_bytes(T, H, I, E, top_k, block)
         self.ws = dev.alloc(self.ws_bytes)
