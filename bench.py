@@ -794,8 +794,9 @@ def main():
     if world > 1:
         # leave NCCL's communicator-initialisation lines on: they are the record of how many ranks the
         # data path's communicator really spans
-        os.environ.setdefault("NCCL_DEBUG", "INFO")
-        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+        if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
+            os.environ["NCCL_DEBUG"] = "INFO"
+            os.environ["NCCL_DEBUG_SUBSYS"] = "INIT"
     import torch
     import torch.distributed as dist
 
