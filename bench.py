@@ -566,7 +566,8 @@ def run_sharded(ctx, wl_name, wl, steps, warmup, min_seconds, with_e2e=True):
         if kind == "tp":
             ws_ = [ctx.q4k_matrix(n, k) for n, k in shapes]
             layers.append(parallel.TPLinearStack(dev, H, I, wl["q_heads"], wl["kv_heads"], wl["head_dim"], world,
-                                                 ws_[0], ws_[1], ws_[2], ws_[3], M, all_reduce))
+                                                 ws_[0], ws_[1], ws_[2], ws_[3], M, all_reduce,
+                                                 fused=ctx.oneshot if world > 1 else None))
         else:
             layers.append(parallel.EPMoELayer(dev, T, H, I, E, wl["top_k"], wl["block"], rank, world,
                                               ctx.q4k_matrix(el * 2 * I, H), ctx.q4k_matrix(el * H, I), all_reduce))
@@ -590,10 +591,15 @@ def run_sharded(ctx, wl_name, wl, steps, warmup, min_seconds, with_e2e=True):
     check = None
     if world > 1 and ctx.oneshot is not None and out_elems * 2 <= ctx.oneshot_limit:
         a = dev.dtoh_sync_copy(layers[0].out, np.uint16, (out_elems,)).copy()
+        fused_ = getattr(layers[0], "fused", None)
         layers[0].all_reduce = ctx.nccl_all_reduce
+        if fused_ is not None:
+            layers[0].fused = None
         forward(layers[0])
         b_ = dev.dtoh_sync_copy(layers[0].out, np.uint16, (out_elems,)).copy()
         layers[0].all_reduce = all_reduce
+        if fused_ is not None:
+            layers[0].fused = fused_
         fa, fb = o.bf16_bits_to_f32(a).astype(np.float64), o.bf16_bits_to_f32(b_).astype(np.float64)
         check = {"one_shot_vs_nccl_rel_l2": float(np.sqrt(((fa - fb) ** 2).sum() / max((fb ** 2).sum(), 1e-30)))}
     graphs = []
@@ -693,6 +699,7 @@ def run_sharded(ctx, wl_name, wl, steps, warmup, min_seconds, with_e2e=True):
                  "algorithmic_bytes_per_pass_per_gpu": shard_bytes, "algorithmic_flops_per_pass": flop,
                  "pass_us": s_layer * 1e6})
     launches = steps * k * layers[0].launches_per_forward
+    fused_note = kind == "tp" and world > 1 and getattr(layers[0], "fused", None) is not None and wl["M"] == 1
     # NCCL keeps a communicator alive while a CUDA graph that captured its collectives exists, and
     # ncclCommDestroy waits for those references: release the graphs before anything else is torn down
     dev.synchronize()
@@ -705,8 +712,9 @@ def run_sharded(ctx, wl_name, wl, steps, warmup, min_seconds, with_e2e=True):
     return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, roofline=roof, clocks=clocks,
                 dtype="u4+f16 scales -> f32 accumulate", ncopies=ncopies, replays_per_step=k,
                 timed_seconds=ms_total * 1e-3, launch_mode="cuda graph", device_status=status, allreduce_check=check,
-                allreduce=("one-shot peer-memory kernel up to 64 KB, NCCL above" if world > 1 and ctx.oneshot_limit
-                           else ("NCCL" if world > 1 else "none")))
+                allreduce=("in the epilogue of the row-split matmuls (peer stores, last CTA reduces)" if fused_note else
+                           ("one-shot peer-memory kernel up to 64 KB, NCCL above" if world > 1 and ctx.oneshot_limit
+                            else ("NCCL" if world > 1 else "none"))))
 
 
 def describe(wl_name, wl, n_gpus, res=None):
@@ -794,9 +802,11 @@ def main():
     if world > 1:
         # leave NCCL's communicator-initialisation lines on: they are the record of how many ranks the
         # data path's communicator really spans
+        # (on stderr when this script is the one that switches them on, so that stdout stays the one JSON line)
         if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
             os.environ["NCCL_DEBUG"] = "INFO"
             os.environ["NCCL_DEBUG_SUBSYS"] = "INIT"
+            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     import torch
     import torch.distributed as dist
 

@@ -173,6 +173,14 @@ int ub_qmatmul_q6k_bf16(void* y, const void* x, const void* wq, int M, int N, in
 #define UB_QMATMUL_WEIGHTS_FRESH 0x100
 size_t ub_qmatmul_workspace_bytes(int M, int N, int K, int is_q4k);
 int ub_qmatmul_q8_0_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
+/* Gate/up projection with SiLU.up in the matmul's epilogue: y[M,I] = silu(x . Wgate^T) * (x . Wup^T), wq = [gate
+ * rows; up rows] (2 I rows of K/256 Q4_K super-blocks), x bf16, out_dtype bf16 / f16 (f32 for one token only).
+ * The reference's caller runs the matmul and then silu_and_mul (kernels/topsaten_ops_wrapper.cpp:375-391); the
+ * result here has the bits of that sequence (gate and up rounded to the output type first).  One token with K a
+ * multiple of 2048 up to 12288 is one launch and needs no workspace; other shapes need
+ * ub_qmatmul_q4k_gate_up_workspace_bytes. */
+size_t ub_qmatmul_q4k_gate_up_workspace_bytes(int M, int I, int K);
+int ub_qmatmul_q4k_gate_up_bf16(void* y, const void* x, const void* wq, int M, int I, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 int ub_qmatmul_q8_0_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 int ub_qmatmul_q4k_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 int ub_qmatmul_q4k_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
@@ -275,6 +283,15 @@ int ub_allreduce_oneshot_bf16(void* data, size_t count, void* const* staging, in
  * default; applies to later launches, process-wide; returns the previous limit.  No reference counterpart
  * (the reference has no bounded waits). */
 unsigned ub_allreduce_oneshot_set_spin_limit(unsigned polls);
+
+/* Row-split Q4_K matmul with the all-reduce over the ranks in its epilogue: y[M,N] bf16 = sum over ranks of
+ * x_r[M,K] . W_r^T, identical bits on every rank (rank-ordered f32 sum of the bf16 partials, as
+ * ub_allreduce_oneshot_bf16 gives).  It stands where the reference's caller runs a matmul and then ecclAllReduce
+ * (src/eccl.rs:209-245).  staging / rank / world / max_bytes as above (the same buffers serve both entry points,
+ * M*N*2 <= max_bytes, M*N % 8 == 0).  With one token the matmul's own CTAs push their rows to the peers and the
+ * last CTA of the grid completes the exchange: ONE launch; other shapes run the matmul and then the one-shot
+ * exchange.  world <= 1 is the plain matmul.  No reference counterpart as an entry point. */
+int ub_qmatmul_q4k_allreduce_bf16(void* y, const void* x, const void* wq, int M, int N, int K, void* const* staging, int rank, int world, size_t max_bytes, void* stream);
 
 /* ------------------------------------------------------------------ collectives
  * ECCL-shaped surface (src/eccllib.rs:7-169, src/eccl.rs:14-426) forwarding to NCCL over

@@ -178,6 +178,118 @@ def test_oneshot_all_reduce_matches_rank_ordered_sum():
             i += 1
 
 
+@pytest.mark.parametrize("N,K", [(1024, 4096), (8192, 2048), (512, 8192), (256, 1024), (2048, 3584)])
+def test_matmul_with_fused_all_reduce(N, K):
+    """Row-split one-token matmul whose CTAs push their rows to the peers and whose last CTA completes the
+    exchange: same bits as matmul followed by the one-shot all-reduce, over several rounds and on every kernel
+    that carries the epilogue (K = 4096 / 2048: register fragments; 8192: shared-memory fragments; 1024 and 3584:
+    the token-pair kernel with and without tensor-map copies)."""
+    world = _world()
+    barrier = threading.Barrier(world)
+    shared = [None] * world
+    rng = np.random.default_rng(N + K)
+    rounds = 4
+    ws = [o.gen_q4k_weight(rng, N, K) for _ in range(world)]
+    xs = [[o.gen_activation(rng, 1, K, True) for _ in range(world)] for _ in range(rounds)]
+
+    def rank_main(r):
+        d = ub.GcuDevice(r)
+        d.bind_to_thread()
+
+        def exchange(obj):
+            shared[r] = obj
+            barrier.wait()
+            out = list(shared)
+            barrier.wait()
+            return out
+
+        ar = eccl.OneShotAllReduce(d, r, world, 16384, exchange, same_process=True)
+        barrier.wait()
+        d_w = d.htod_sync_copy(ws[r])
+        outs = []
+        for k in range(rounds):
+            d_x = d.htod_sync_copy(o.f32_to_bf16_bits(xs[k][r]).reshape(-1))
+            d_y = d.alloc(N * 2)
+            ar.matmul_all_reduce(d_y, d_x, d_w, 1, N, K)
+            if k == 1:  # a stand-alone exchange in between shares the staging buffers and the epoch sequence
+                ar.all_reduce(d_y, N)
+            d.synchronize()
+            outs.append(d.dtoh_sync_copy(d_y, np.uint16).copy())
+        assert d.device_status() == 0
+        barrier.wait()
+        ar.close()
+        return outs
+
+    got = _run_ranks(world, rank_main)
+    for k in range(rounds):
+        acc = np.zeros(N, dtype=np.float32)
+        exact = np.zeros(N, dtype=np.float64)
+        for r in range(world):
+            part = o.c_qmatmul(xs[k][r], ws[r], N, K, True).reshape(-1)
+            acc = acc + _bf16(part)
+            exact += part
+        if k == 1:
+            acc = _bf16(acc) * world  # the extra stand-alone exchange sums `world` copies of the reduced vector
+            exact *= world
+        for r in range(world):
+            assert np.array_equal(got[r][k], got[0][k])  # every rank holds the same bits
+        y = o.bf16_bits_to_f32(got[0][k])
+        # partial sums are rounded to bf16 before the exchange (matmul accumulation differs in the last bits
+        # from the oracle's, so a bf16 tie may fall the other way: compare values, not bits)
+        assert o.rel_l2(y, exact.astype(np.float32)) < 5e-3
+        assert o.rel_l2(y, acc) < 2e-3
+
+
+def test_tp_stack_with_fused_exchanges_matches_the_plain_one():
+    """The tensor-parallel stack at one token with SiLU.up and both exchanges inside the matmul launches gives
+    the bits of the same stack with separate matmul / SiLU.up / one-shot all-reduce launches."""
+    world = _world()
+    hidden, inter, nq, nkv, hd = 2048, 4096, 16, 2, 128
+    rng = np.random.default_rng(700)
+    x = o.gen_activation(rng, 1, hidden, True)
+    w_qkv = o.gen_q4k_weight(rng, (nq + 2 * nkv) * hd, hidden)
+    w_o = o.gen_q4k_weight(rng, hidden, nq * hd)
+    w_gate, w_up = o.gen_q4k_weight(rng, inter, hidden), o.gen_q4k_weight(rng, inter, hidden)
+    w_down = o.gen_q4k_weight(rng, hidden, inter)
+    barrier = threading.Barrier(world)
+    shared = [None] * world
+
+    def rank_main(r):
+        d = ub.GcuDevice(r)
+        d.bind_to_thread()
+
+        def exchange(obj):
+            shared[r] = obj
+            barrier.wait()
+            out = list(shared)
+            barrier.wait()
+            return out
+
+        ar = eccl.OneShotAllReduce(d, r, world, 16384, exchange, same_process=True)
+        barrier.wait()
+        shards = (par.qkv_column_split(w_qkv, nq, nkv, hd, hidden, True, r, world),
+                  par.row_split(w_o, hidden, nq * hd, True, r, world)[0],
+                  par.gate_up_column_split(w_gate, w_up, inter, hidden, True, r, world),
+                  par.row_split(w_down, hidden, inter, True, r, world)[0])
+        d_x = d.htod_sync_copy(o.f32_to_bf16_bits(x).reshape(-1))
+        outs = []
+        for fused in (ar, None):
+            stack = par.TPLinearStack(d, hidden, inter, nq, nkv, hd, world, *shards, 1, ar.all_reduce, fused=fused)
+            for _ in range(2):
+                out = stack.forward(d_x, 1)
+                d.synchronize()
+                outs.append(d.dtoh_sync_copy(out, np.uint16)[:hidden].copy())
+        assert d.device_status() == 0
+        barrier.wait()
+        ar.close()
+        return outs
+
+    got = _run_ranks(world, rank_main)
+    for r in range(world):
+        for k in range(1, 4):
+            assert np.array_equal(got[r][k], got[0][0])
+
+
 @pytest.mark.parametrize("M", [1, 5])
 def test_linear_stack_on_one_gpu_chains_dependent_launches(dev, M):
     """World size 1: four matmuls back to back on one stream, each consuming the previous one's output (the

@@ -245,3 +245,45 @@ def test_repack_then_q4k_matmul_back_to_back(dev, M, K):
                     stream=dev.stream)
         got = dev.dtoh_sync_copy(d_y, np.float32, (M, N))
         assert o.rel_l2(got, want) < 1e-4
+
+
+@pytest.mark.parametrize("x_dtype", [DTYPE_F32, DTYPE_BF16])
+@pytest.mark.parametrize("N,K", [(33, 8192), (5000, 8192), (20000, 6144), (4100, 12288), (9000, 10240)])
+def test_q4k_single_token_long_rows(dev, x_dtype, N, K):
+    """M = 1 with K a multiple of 2048 beyond 4096: the activation fragments live in shared memory, a tile takes
+    K / 2048 stages, stages are re-armed many times (20000 rows at K = 6144: 13 stages per CTA through a ring of 4)."""
+    rng = np.random.default_rng(N + K)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, 1, K, x_dtype == DTYPE_BF16)
+    got = _run(dev, w, x, 1, N, K, True, x_dtype, DTYPE_F32)
+    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, True)) < (1e-4 if N >= 1000 else TOL_DECODE)
+
+
+# ----------------------------------------------------------------------------- gate/up with SiLU.up in the epilogue
+@pytest.mark.parametrize("M,I,K", [(1, 1000, 2048), (1, 4744, 8192), (1, 37, 4096), (1, 640, 1024), (3, 520, 2048),
+                                   (40, 264, 1024)])
+def test_gate_up_silu_matches_the_two_call_sequence(dev, M, I, K):
+    """One token with K % 2048 == 0 is one launch; the result must have the bits of matmul -> ub_silu_and_mul
+    (which every other shape runs)."""
+    rng = np.random.default_rng(M + I + K)
+    w = o.gen_q4k_weight(rng, 2 * I, K)
+    x = o.gen_activation(rng, M, K, True)
+    d_w, d_x = dev.htod_sync_copy(w), dev.htod_sync_copy(to_storage(x, DTYPE_BF16))
+    ws_bytes = ops.qmatmul_q4k_gate_up_workspace_bytes(M, I, K)
+    ws = dev.alloc(max(ws_bytes, 256))
+    d_y = dev.alloc(M * I * 2)
+    ops.qmatmul_q4k_gate_up(d_y, d_x, d_w, M, I, K, out_dtype=DTYPE_BF16, workspace=ws, ws_bytes=ws_bytes,
+                            stream=dev.stream)
+    got = fetch(dev, d_y, DTYPE_BF16, (M, I))
+    # the two-call sequence on the device
+    d_gu, d_y2 = dev.alloc(M * 2 * I * 2), dev.alloc(M * I * 2)
+    ws2_bytes = ops.qmatmul_workspace_bytes(M, 2 * I, K, True)
+    ws2 = dev.alloc(max(ws2_bytes, 256))
+    ops.qmatmul(d_gu, d_x, d_w, M, 2 * I, K, is_q4k=True, x_dtype=DTYPE_BF16, out_dtype=DTYPE_BF16, workspace=ws2,
+                ws_bytes=ws2_bytes, stream=dev.stream)
+    ops.silu_and_mul(d_y2, d_gu, M, I, DTYPE_BF16, stream=dev.stream)
+    assert np.array_equal(got, fetch(dev, d_y2, DTYPE_BF16, (M, I)))
+    # and the oracle: exact matmul, rounded to bf16, SiLU.up
+    gu = o.round_through(o.c_qmatmul(x, w, 2 * I, K, True), o.UB_BF16)
+    want = o.silu_and_mul(gu, o.UB_BF16)
+    assert o.rel_l2(got, want) < (1e-2 if M > 8 else 5e-3)

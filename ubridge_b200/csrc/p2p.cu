@@ -113,6 +113,10 @@ allreduce_oneshot_bf16_kernel(__nv_bfloat16* __restrict__ data, size_t count, Pe
 
 }  // namespace
 
+namespace ub {
+uint32_t oneshot_spin_limit() { return g_flag_spin_limit.load(std::memory_order_relaxed); }
+}  // namespace ub
+
 extern "C" {
 
 // Zero-filled device memory that peers can map: plain cudaMalloc (allocations of the stream-ordered pool behind

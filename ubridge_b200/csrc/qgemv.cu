@@ -923,18 +923,34 @@ inline size_t dtype_size(int dt) { return dt == UB_DTYPE_F32 ? 4 : 2; }
 
 namespace ub {
 
+struct ArParams;
 template <typename XT>
-int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, const ArParams* ar,
+                  cudaStream_t s);
 template <typename XT>
 int q8_0_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
 template <typename XT>
-int q4k_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+int q4k_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const ArParams* ar,
+                cudaStream_t s);
+
+template <typename XT>
+int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
+             const ArParams* ar, cudaStream_t s);
 
 // Q4_K: up to eight rows of x per pass on the integer tensor-core kernel when its shared-memory plan fits.
 // Otherwise rows of x are processed four (then two, then one) at a time; each pass streams W once.
 template <typename XT>
 int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
           cudaStream_t s) {
+  return qgemv_ar<XT>(is_q4k, y, x, wq, M, N, K, y_dtype, fresh, nullptr, s);
+}
+
+// ar != nullptr: one token of Q4_K whose launch ends with the all-reduce over the ranks (see ar_epilogue.cuh);
+// UB_ERR_UNSUPPORTED when no kernel with that epilogue takes the shape (the caller then runs matmul and exchange
+// as two launches).
+template <typename XT>
+int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
+             const ArParams* ar, cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
   int m0 = 0;
   while (m0 < M) {
@@ -946,9 +962,9 @@ int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K
     if ((reinterpret_cast<uintptr_t>(wq) & 15) == 0) {
       const int mi = left >= 8 ? 8 : left;
       // a single token at K = 2048 / 4096: the two-CTAs-per-SM kernel; everything else: token pairs / quads
-      st = (is_q4k && mi == 1) ? q4k_gemv_m1<XT>(wq, xp, yp, N, K, y_dtype, fresh, s) : UB_ERR_UNSUPPORTED;
+      st = (is_q4k && mi == 1) ? q4k_gemv_m1<XT>(wq, xp, yp, N, K, y_dtype, fresh, ar, s) : UB_ERR_UNSUPPORTED;
       if (st == UB_ERR_UNSUPPORTED)
-        st = is_q4k ? q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, s)
+        st = is_q4k ? q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, ar, s)
                     : q8_0_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, s);
       if (st == UB_OK) {
         m0 += mi;
@@ -956,6 +972,7 @@ int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K
       }
       if (st != UB_ERR_UNSUPPORTED) return st;
     }
+    if (ar) return UB_ERR_UNSUPPORTED;  // the streaming fallbacks below have no exchange epilogue
     if (is_q4k) {
       st = mt == 4 ? launch_q4k<XT, 4>(w, xp, yp, N, K, y_dtype, s)
                    : (mt == 2 ? launch_q4k<XT, 2>(w, xp, yp, N, K, y_dtype, s)
@@ -971,6 +988,10 @@ int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K
   return ub::fail(UB_OK);
 }
 
+template int qgemv_ar<float>(bool, void*, const float*, const void*, int, int, int, int, bool, const ArParams*,
+                             cudaStream_t);
+template int qgemv_ar<__nv_bfloat16>(bool, void*, const __nv_bfloat16*, const void*, int, int, int, int, bool,
+                                     const ArParams*, cudaStream_t);
 template int qgemv<float>(bool, void*, const float*, const void*, int, int, int, int, bool, cudaStream_t);
 template int qgemv<__nv_bfloat16>(bool, void*, const __nv_bfloat16*, const void*, int, int, int, int, bool, cudaStream_t);
 

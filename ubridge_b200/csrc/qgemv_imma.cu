@@ -32,6 +32,7 @@
 
 #include <string.h>
 
+#include "ar_epilogue.cuh"
 #include "common.cuh"
 
 namespace ub {
@@ -162,7 +163,8 @@ __host__ __device__ inline ImmaGeom imma_geom(int K, bool use_tm) {
 template <typename XT, int MP>
 __global__ void __launch_bounds__(kImmaThreads, 1)
 qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void* __restrict__ y, int M, int N,
-                      int K, int y_dtype, int S, int early, int* err_word, int use_tm, const __grid_constant__ CUtensorMap w_map) {
+                      int K, int y_dtype, int S, int early, int* err_word, int use_tm, const ArParams ar,
+                      const __grid_constant__ CUtensorMap w_map) {
   constexpr int kMT = imma_mt(MP);
   extern __shared__ __align__(128) unsigned char ismem_raw[];
   // swizzled tiles need 1024-byte alignment; the launch reserves 1 KB of slack for rounding the base up
@@ -481,16 +483,21 @@ qgemv_q4k_imma_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, 
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < kCW; w++) tot += red[((((w * kMT + mt) * MP + p) * 2 + rs) * 8 + gg) * 2 + tk];
-        st_y(y, static_cast<size_t>(tok) * N + row, y_dtype, tot);
+        if (ar.world > 1)  // fused all-reduce (one token): the row goes to every rank's staging slot
+          ar_push(ar, ar_epoch(ar), row, tot);
+        else
+          st_y(y, static_cast<size_t>(tok) * N + row, y_dtype, tot);
       }
     }
     __syncthreads();  // (C) the ring is free again
   }
+  if (ar.world > 1) ar_finish(ar, ar_epoch(ar), y, N, err_word);
   if (!ok && lane == 0) report_device_error(err_word, UB_ERR_TIMEOUT);
 }
 
 template <typename XT, int MP>
-int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
+int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, const ArParams& ar,
+                cudaStream_t s) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -535,7 +542,7 @@ int launch_imma(const uint8_t* wq, const XT* x, void* y, int M, int N, int K, in
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
   e = cudaLaunchKernelEx(&cfg, kernel, wq, x, y, M, N, K, y_dtype, S, fresh ? 0 : kEarlySlots, ub::device_error_word(),
-                         use_tm ? 1 : 0, wmap);
+                         use_tm ? 1 : 0, ar, wmap);
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
@@ -827,11 +834,16 @@ namespace ub {
 // y[M,N] = x[M,K] . dequant(Wq)^T for 1 <= M <= 8; returns UB_ERR_UNSUPPORTED (without setting the thread's
 // status) when the shape does not fit this kernel's shared-memory plan, so that the caller can use another.
 template <typename XT>
-int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
+int q4k_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, const ArParams* ar,
+                  cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
-  if (M <= 2) return launch_imma<XT, 1>(w, x, y, M, N, K, y_dtype, fresh, s);
-  if (M <= 4) return launch_imma<XT, 2>(w, x, y, M, N, K, y_dtype, fresh, s);
-  return launch_imma<XT, 4>(w, x, y, M, N, K, y_dtype, fresh, s);
+  ArParams none;
+  memset(&none, 0, sizeof(none));
+  if (ar && ar->world > 1 && M != 1) return UB_ERR_UNSUPPORTED;  // the fused exchange is a one-token path
+  const ArParams& a = ar ? *ar : none;
+  if (M <= 2) return launch_imma<XT, 1>(w, x, y, M, N, K, y_dtype, fresh, a, s);
+  if (M <= 4) return launch_imma<XT, 2>(w, x, y, M, N, K, y_dtype, fresh, a, s);
+  return launch_imma<XT, 4>(w, x, y, M, N, K, y_dtype, fresh, a, s);
 }
 
 // Q8_0 flavour, same contract.
@@ -844,7 +856,9 @@ int q8_0_gemv_imma(const void* wq, const XT* x, void* y, int M, int N, int K, in
 
 template int q8_0_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, bool, cudaStream_t);
 template int q8_0_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, bool, cudaStream_t);
-template int q4k_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, bool, cudaStream_t);
-template int q4k_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, bool, cudaStream_t);
+template int q4k_gemv_imma<float>(const void*, const float*, void*, int, int, int, int, bool, const ArParams*,
+                                  cudaStream_t);
+template int q4k_gemv_imma<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, int, bool,
+                                          const ArParams*, cudaStream_t);
 
 }  // namespace ub

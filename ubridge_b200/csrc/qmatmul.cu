@@ -9,15 +9,24 @@
 //   M  > 16, Q4_K     tcgen05 tensor-core GEMM with in-kernel dequantisation (bf16 activations and output;
 //                     other types are converted through the caller's workspace);
 //   M  > 16, Q8_0     the decode kernel in passes of four rows.
+#include <string.h>
+
 #include <mutex>
 
+#include "ar_epilogue.cuh"
 #include "common.cuh"
 
 namespace ub {
 template <typename XT>
 int qgemv(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
           cudaStream_t s);
+template <typename XT>
+int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
+             const ArParams* ar, cudaStream_t s);
+template <typename XT>
+int q4k_gemv_m1_gate_up(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
 int q4k_gemm_mma(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
+uint32_t oneshot_spin_limit();
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
 }  // namespace ub
 
@@ -163,6 +172,81 @@ int ub_qmatmul_q4k_f32(void* y, const void* x, const void* wq, int M, int N, int
 int ub_qmatmul_q4k_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace,
                         size_t ws_bytes, void* stream) {
   return qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, out_dtype, workspace, ws_bytes, stream);
+}
+
+// ---- gate/up projection with the SiLU.up step in the matmul's epilogue ----
+// y[M, I] = silu(x . Wgate^T) * (x . Wup^T) with wq = [gate rows; up rows] (2 I rows of K), bf16 activations.
+// One token with K a multiple of 2048 up to 12288 is ONE launch; everything else is the matmul into the
+// workspace followed by ub_silu_and_mul (the reference's own sequence, kernels/topsaten_ops_wrapper.cpp:375-391).
+size_t ub_qmatmul_q4k_gate_up_workspace_bytes(int M, int I, int K) {
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  return align_up(static_cast<size_t>(M) * 2 * I * 2, 256) + align_up(ub_qmatmul_workspace_bytes(M, 2 * I, K, 1), 256);
+}
+
+int ub_qmatmul_q4k_gate_up_bf16(void* y, const void* x, const void* wq, int M, int I, int K, int out_dtype,
+                                void* workspace, size_t ws_bytes, void* stream) {
+  bool fresh = (out_dtype & UB_QMATMUL_WEIGHTS_FRESH) != 0;
+  out_dtype &= ~UB_QMATMUL_WEIGHTS_FRESH;
+  if (M == 0 || I == 0) return ub::fail(UB_OK);
+  if (!y || !x || !wq || M < 0 || I < 0 || K <= 0 || K % UB_QK_K) return ub::fail(UB_ERR_INVALID_ARG);
+  if (out_dtype != UB_DTYPE_BF16 && out_dtype != UB_DTYPE_F16 && out_dtype != UB_DTYPE_F32)
+    return ub::fail(UB_ERR_INVALID_ARG);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15)) return ub::fail(UB_ERR_INVALID_ARG);
+  cudaStream_t s = ub::as_stream(stream);
+  if (ub::take_weights_written(s)) fresh = true;
+  if (M == 1) {
+    const int st = ub::q4k_gemv_m1_gate_up<__nv_bfloat16>(wq, static_cast<const __nv_bfloat16*>(x), y, I, K, out_dtype,
+                                                         fresh, s);
+    if (st != UB_ERR_UNSUPPORTED) return st;
+  }
+  const size_t need = ub_qmatmul_q4k_gate_up_workspace_bytes(M, I, K);
+  if (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return ub::fail(UB_ERR_WORKSPACE);
+  char* ws = static_cast<char*>(workspace);
+  const size_t gu_bytes = align_up(static_cast<size_t>(M) * 2 * I * 2, 256);
+  // the intermediate is bf16 (f16 when that is the output type), as in the two-call sequence
+  const int mid = out_dtype == UB_DTYPE_F16 ? UB_DTYPE_F16 : UB_DTYPE_BF16;
+  int st = qmatmul(true, UB_DTYPE_BF16, ws, x, wq, M, 2 * I, K, mid | (fresh ? UB_QMATMUL_WEIGHTS_FRESH : 0),
+                   ws + gu_bytes, ws_bytes - gu_bytes, stream);
+  if (st != UB_OK) return st;
+  if (out_dtype == UB_DTYPE_F32) return ub::fail(UB_ERR_UNSUPPORTED);  // f32 output exists on the one-token path only
+  return ub_silu_and_mul(y, ws, M, I, out_dtype, stream);
+}
+
+// ---- row-split matmul with the all-reduce over the ranks in its epilogue ----
+// y[M, N] (bf16, summed over the ranks, identical bits on every rank) = sum_r x_r[M, K] . W_r^T.  `staging`,
+// rank, world, max_bytes as for ub_allreduce_oneshot_bf16 (the same buffers serve both; M*N*2 <= max_bytes).
+// One token is ONE launch on every kernel that takes the shape (the matmul's CTAs push their rows to the
+// peers, the last CTA completes the exchange); other shapes run the matmul and then the one-shot exchange.
+int ub_qmatmul_q4k_allreduce_bf16(void* y, const void* x, const void* wq, int M, int N, int K, void* const* staging,
+                                  int rank, int world, size_t max_bytes, void* stream) {
+  if (M == 0 || N == 0) return ub::fail(UB_OK);
+  if (!y || !x || !wq || M < 0 || N < 0 || K <= 0 || K % UB_QK_K) return ub::fail(UB_ERR_INVALID_ARG);
+  if (world <= 1) return qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, UB_DTYPE_BF16, nullptr, 0, stream);
+  if (!staging || world > ub::kArMaxWorld || rank < 0 || rank >= world || (max_bytes & 15))
+    return ub::fail(UB_ERR_INVALID_ARG);
+  const size_t count = static_cast<size_t>(M) * N;
+  if (count % 8 || (reinterpret_cast<uintptr_t>(y) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) ||
+      (reinterpret_cast<uintptr_t>(wq) & 15))
+    return ub::fail(UB_ERR_INVALID_ARG);
+  if (count * 2 > max_bytes) return ub::fail(UB_ERR_TOO_LARGE);
+  cudaStream_t s = ub::as_stream(stream);
+  if (M == 1) {
+    ub::ArParams ar;
+    memset(&ar, 0, sizeof(ar));
+    for (int p = 0; p < world; p++) {
+      ar.base[p] = static_cast<unsigned char*>(staging[p]);
+      if (!ar.base[p] || (reinterpret_cast<uintptr_t>(ar.base[p]) & 15)) return ub::fail(UB_ERR_INVALID_ARG);
+    }
+    ar.rank = rank, ar.world = world, ar.max_bytes = max_bytes;
+    ar.spin_limit = ub::oneshot_spin_limit();
+    const bool fresh = ub::take_weights_written(s);
+    const int st = ub::qgemv_ar<__nv_bfloat16>(true, y, static_cast<const __nv_bfloat16*>(x), wq, 1, N, K, UB_DTYPE_BF16,
+                                               fresh, &ar, s);
+    if (st != UB_ERR_UNSUPPORTED) return st;
+  }
+  const int st = qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, UB_DTYPE_BF16, nullptr, 0, stream);
+  if (st != UB_OK) return st;
+  return ub_allreduce_oneshot_bf16(y, count, staging, rank, world, max_bytes, stream);
 }
 
 // ub_qmatmul_q4k_f32 for callers that have no way to hand over a workspace: the type-conversion

@@ -81,6 +81,18 @@ def qmatmul(y, x, wq, M: int, N: int, K: int, *, is_q4k: bool, x_dtype: int, out
     check(getattr(lib(), name)(_p(y), _p(x), _p(wq), M, N, K, out_dtype, _p(workspace), ws_bytes, _s(stream)), name)
 
 
+def qmatmul_q4k_gate_up_workspace_bytes(M: int, I: int, K: int) -> int:
+    return lib().ub_qmatmul_q4k_gate_up_workspace_bytes(M, I, K)
+
+
+def qmatmul_q4k_gate_up(y, x, wq, M: int, I: int, K: int, *, out_dtype: int, workspace=None, ws_bytes: int = 0,
+                        stream=None) -> None:
+    """y[M, I] = silu(x . Wgate^T) * (x . Wup^T), wq = [gate rows; up rows] of Q4_K, x bf16.  One token is one
+    launch (SiLU.up in the matmul's epilogue); other shapes run the matmul into the workspace, then SiLU.up."""
+    check(lib().ub_qmatmul_q4k_gate_up_bf16(_p(y), _p(x), _p(wq), M, I, K, out_dtype, _p(workspace), ws_bytes,
+                                            _s(stream)), "ub_qmatmul_q4k_gate_up_bf16")
+
+
 def qmatmul_q4k_f32_static(y, x, wq, M: int, N: int, K: int, out_dtype: int, stream=None) -> None:
     """Q4_K matmul with f32 activations that takes no workspace and allocates nothing: its scratch is a
     fixed 8 MiB array inside the library (so roughly M*(K+N) <= 4M elements, else UB_ERR_TOO_LARGE).

@@ -113,13 +113,16 @@ class TPLinearStack:
 
     def __init__(self, dev, hidden: int, inter: int, n_q_heads: int, n_kv_heads: int, head_dim: int, world: int,
                  w_qkv: np.ndarray, w_o: np.ndarray, w_gate_up: np.ndarray, w_down: np.ndarray, max_m: int,
-                 all_reduce: Optional[AllReduce] = None):
+                 all_reduce: Optional[AllReduce] = None, fused=None):
         self.dev, self.H, self.I, self.world = dev, hidden, inter, world
         self.q_local = n_q_heads * head_dim // world
         self.kv_local = n_kv_heads * head_dim // world
         self.qkv_n = self.q_local + 2 * self.kv_local
         self.i_local = inter // world
         self.all_reduce = all_reduce
+        # an eccl.OneShotAllReduce: row-split matmuls whose output fits its staging slots run with the exchange
+        # in their own epilogue (one launch instead of matmul + all-reduce)
+        self.fused = fused
         self.w_qkv, self.w_o = _resident(dev, w_qkv), _resident(dev, w_o)
         self.w_gu, self.w_down = _resident(dev, w_gate_up), _resident(dev, w_down)
         self.max_m = max_m
@@ -130,11 +133,18 @@ class TPLinearStack:
         self.act = dev.alloc(max_m * self.i_local * 2)
         self.out = dev.alloc(max_m * hidden * 2)
         shapes = [(self.qkv_n, hidden), (hidden, self.q_local), (2 * self.i_local, hidden), (hidden, self.i_local)]
-        self.ws_bytes = max(ops.qmatmul_workspace_bytes(max_m, n, k, True) for n, k in shapes)
+        self.ws_bytes = max(max(ops.qmatmul_workspace_bytes(max_m, n, k, True) for n, k in shapes),
+                            ops.qmatmul_q4k_gate_up_workspace_bytes(max_m, self.i_local, hidden))
         self.ws = dev.alloc(max(self.ws_bytes, 256))
 
-    # kernels of this library per forward(): four matmuls (one launch each for M <= 8 or M > 16) + SiLU.up
-    launches_per_forward = 5
+    @property
+    def launches_per_forward(self) -> int:
+        """Kernels of this library per forward() at max_m: one token runs four launches (SiLU.up and the
+        exchanges ride in the matmuls' epilogues); otherwise four matmuls, SiLU.up and, beyond one rank, two
+        all-reduces (the stand-in copy for attention is a device copy, not a kernel of this library)."""
+        if self.max_m == 1:
+            return 4 if (self.world == 1 or self.fused is not None) else 6
+        return 5 + (2 if self.world > 1 else 0)
 
     def _mm(self, y, x, w, M, N, K):
         ops.qmatmul(y, x, w, M, N, K, is_q4k=True, x_dtype=DTYPE_BF16, out_dtype=DTYPE_BF16, workspace=self.ws,
@@ -144,17 +154,26 @@ class TPLinearStack:
         """x: device bf16 [M, hidden] (replicated).  Returns the device buffer holding bf16 [M, hidden]."""
         dev = self.dev
         self._mm(self.qkv, x, self.w_qkv, M, self.qkv_n, self.H)
-        # stand-in for attention: this rank's q columns, made contiguous
-        ops_copy_cols(dev, self.attn, self.qkv, M, self.qkv_n, self.q_local)
-        self._mm(self.h1, self.attn, self.w_o, M, self.H, self.q_local)
-        if self.all_reduce:
-            self.all_reduce(self.h1, M * self.H)
-        self._mm(self.gu, self.h1, self.w_gu, M, 2 * self.i_local, self.H)
-        ops.silu_and_mul(self.act, self.gu, M, self.i_local, DTYPE_BF16, stream=dev.stream)
-        self._mm(self.out, self.act, self.w_down, M, self.H, self.i_local)
-        if self.all_reduce:
-            self.all_reduce(self.out, M * self.H)
+        # stand-in for attention: this rank's q columns.  One token: they already lie contiguously at the start
+        # of the row; more tokens: made contiguous by one strided device copy
+        attn = self.qkv
+        if M > 1:
+            ops_copy_cols(dev, self.attn, self.qkv, M, self.qkv_n, self.q_local)
+            attn = self.attn
+        self._row_split(self.h1, attn, self.w_o, M, self.H, self.q_local)
+        ops.qmatmul_q4k_gate_up(self.act, self.h1, self.w_gu, M, self.i_local, self.H, out_dtype=DTYPE_BF16,
+                                workspace=self.ws, ws_bytes=self.ws_bytes, stream=dev.stream)
+        self._row_split(self.out, self.act, self.w_down, M, self.H, self.i_local)
         return self.out
+
+    def _row_split(self, y, x, w, M, N, K):
+        """Row-split matmul + sum over the ranks."""
+        if self.world > 1 and self.fused is not None and M * N * 2 <= self.fused.max_bytes and (M * N) % 8 == 0:
+            self.fused.matmul_all_reduce(y, x, w, M, N, K, stream=self.dev.stream)
+            return
+        self._mm(y, x, w, M, N, K)
+        if self.all_reduce:
+            self.all_reduce(y, M * N)
 
 
 def ops_copy_cols(dev, dst, src, M: int, src_cols: int, cols: int) -> None:
