@@ -195,6 +195,19 @@ int ub_qmatmul_q4k_bf16(void* y, const void* x, const void* wq, int M, int N, in
  * array: do not let two of them overlap on one GPU. */
 int ub_qmatmul_q4k_f32_static(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* stream);
 
+/* ------------------------------------------------------------------ GGUF tensor blobs
+ * A GGUF file stores a tensor as (GGML type tag, dims, interleaved block bytes); these entries take the blob's
+ * bytes as they lie in the file and dispatch on the tag.  The reference declares the block structs of the family
+ * (kernels/quant.cpp:64-185) and ships kernels for Q8_0 and Q4_K; taken here: Q4_0 (2), Q8_0 (8), Q4_K (12),
+ * Q5_K (13), Q6_K (14); other tags return UB_ERR_UNSUPPORTED.  x_dtype f32 / bf16; Q4_K with more than 16 tokens
+ * and non-bf16 types needs ub_qmatmul_gguf_workspace_bytes of workspace, the other formats none. */
+int ub_gguf_block_values(int ggml_type);
+int ub_gguf_block_bytes(int ggml_type);
+size_t ub_gguf_tensor_bytes(int ggml_type, size_t numel);
+int ub_dequant_gguf(void* out, const void* blob, int ggml_type, size_t numel, int out_dtype, void* stream);
+size_t ub_qmatmul_gguf_workspace_bytes(int ggml_type, int M, int N, int K);
+int ub_qmatmul_gguf(void* y, const void* x, const void* blob, int ggml_type, int M, int N, int K, int x_dtype, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
+
 /* ------------------------------------------------------------------ MoE: reference-named host launchers */
 /* src/ffi.rs:205-236, kernels/topk_softmax_host.cpp:178-208 */
 void topk_softmax_f32(float* input, float* output, int32_t* index, int32_t num_tokens, int32_t num_experts, int32_t topk, int32_t norm_topk_prob, void* stream);
@@ -249,6 +262,13 @@ int ub_topk_sum(void* out, const void* in, int T, int topk, int H, int dtype, vo
  * writes C[slot, :D] = silu(gate)*up (the SiLU.up step the reference's caller runs between
  * its two GEMMs, kernels/topsaten_ops_wrapper.cpp:375-391), C row stride D. */
 int ub_fused_moe_q4k_gemm(void* C, const void* A, const void* Bq, const float* topk_weights, const int32_t* sorted_ids, const int32_t* experts_ids, const int32_t* num_tokens_post_pad, int M, int K, int N, int E, int topk_ids_size, int top_k, int block_size, int mul_routed_weight, int act_silu_mul, void* workspace, size_t ws_bytes, void* stream);
+
+/* indexed_moe on Q4_K experts (decode-time sibling of the grouped GEMM; the reference's dense contract is
+ * indexed_moe_{f16,bf16}, src/ffi.rs:121-147, kernels/moe_host.cpp:100-109,278-293):
+ * out[b,t,:] = in[b,(M==1?0:t),:] . dequant(wq[indices[b,t]])^T with in [batch,M,K] (M = 1 or topk),
+ * wq [num_experts][N rows of K/256 super-blocks], indices [batch,topk], out [batch,topk,N]; dtype bf16 / f16.
+ * An index outside [0,num_experts) gives a zero row and UB_ERR_BAD_INDEX in the device error word. */
+int ub_indexed_moe_q4k(void* out, const void* in, const void* wq, const uint32_t* indices, int N, int K, int M, int batch, int topk, int num_experts, int dtype, void* stream);
 
 /* Whole expert layer: router logits -> out[T,H].  topk_softmax -> moe_align_block_size ->
  * grouped Q4_K GEMM (w13, SiLU.up) -> grouped Q4_K GEMM (w2, routed weight) -> sum over

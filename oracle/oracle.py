@@ -171,6 +171,65 @@ def dequant_q6k(blocks: np.ndarray) -> np.ndarray:
     return (dsc * q.reshape(lead + (16, 16))).reshape(lead + (QK_K,)).astype(np.float32)
 
 
+Q4_0_BYTES = 18
+Q5K_BYTES = 176
+GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q5_K, GGML_Q6_K = 2, 8, 12, 13, 14  # GGUF type tags
+
+
+def dequant_q4_0(blocks: np.ndarray) -> np.ndarray:
+    """block_q4_0 (kernels/quant.cpp:64-69): f16 d + 16 bytes; value i < 16 is the low nibble of byte i, value
+    16 + i its high nibble; y = d * (nibble - 8)."""
+    b = np.asarray(blocks, dtype=np.uint8).reshape(-1, Q4_0_BYTES)
+    d = b[:, :2].copy().view(np.float16)[:, 0].astype(np.float32)
+    q = b[:, 2:]
+    lo, hi = (q & 15).astype(np.int32) - 8, (q >> 4).astype(np.int32) - 8
+    return (d[:, None] * np.concatenate([lo, hi], axis=1).astype(np.float32)).reshape(-1)
+
+
+def dequant_q5k(blocks: np.ndarray) -> np.ndarray:
+    """block_q5_K (kernels/quant.cpp:154-161): f16 d, f16 dmin, 12 scale bytes (packed as in Q4_K, :356-363),
+    qh[32], qs[128].  64-value group g: values 0..31 = low nibbles of qs[32g..] + 16 * bit 2g of qh[l], pair 2g;
+    values 32..63 = high nibbles + 16 * bit 2g+1, pair 2g+1; y = (d * sc) * q - dmin * m."""
+    b = np.asarray(blocks, dtype=np.uint8).reshape(-1, Q5K_BYTES)
+    d = b[:, 0:2].copy().view(np.float16)[:, 0].astype(np.float32)
+    dmin = b[:, 2:4].copy().view(np.float16)[:, 0].astype(np.float32)
+    sc, mn = unpack_scales_k4(b[:, 4:16])
+    qh = b[:, 16:48].astype(np.int32)
+    qs = b[:, 48:].reshape(-1, 4, 32).astype(np.int32)
+    out = np.empty((b.shape[0], 8, 32), dtype=np.float32)
+    for g in range(4):
+        q0 = (qs[:, g] & 15) + (((qh >> (2 * g)) & 1) << 4)
+        q1 = (qs[:, g] >> 4) + (((qh >> (2 * g + 1)) & 1) << 4)
+        out[:, 2 * g] = (d * sc[:, 2 * g].astype(np.float32))[:, None] * q0.astype(np.float32) - (
+            dmin * mn[:, 2 * g].astype(np.float32))[:, None]
+        out[:, 2 * g + 1] = (d * sc[:, 2 * g + 1].astype(np.float32))[:, None] * q1.astype(np.float32) - (
+            dmin * mn[:, 2 * g + 1].astype(np.float32))[:, None]
+    return out.reshape(-1)
+
+
+def dequant_gguf(blob: np.ndarray, ggml_type: int) -> np.ndarray:
+    """A GGUF tensor blob (flat bytes of interleaved blocks) of the given GGML type -> flat f32 values."""
+    fn, nbytes = {GGML_Q4_0: (dequant_q4_0, Q4_0_BYTES), GGML_Q8_0: (dequant_q8_0, Q8_0_BYTES),
+                  GGML_Q4_K: (dequant_q4k, Q4K_BYTES), GGML_Q5_K: (dequant_q5k, Q5K_BYTES),
+                  GGML_Q6_K: (dequant_q6k, Q6K_BYTES)}[ggml_type]
+    return np.ascontiguousarray(fn(np.asarray(blob, dtype=np.uint8).reshape(-1, nbytes)), dtype=np.float32).reshape(-1)
+
+
+def gen_q4_0_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    nb = N * K // 32
+    b = rng.integers(0, 256, size=(nb, Q4_0_BYTES), dtype=np.uint8)
+    b[:, :2] = rng.uniform(1e-3, 1e-2, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    return b.reshape(-1)
+
+
+def gen_q5k_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    nb = N * K // QK_K
+    b = rng.integers(0, 256, size=(nb, Q5K_BYTES), dtype=np.uint8)
+    b[:, 0:2] = rng.uniform(1e-4, 1e-2, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    b[:, 2:4] = rng.uniform(1e-4, 1e-2, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    return b.reshape(-1)
+
+
 def split_layout(inter: np.ndarray, is_q4k: bool) -> np.ndarray:
     """Interleaved GGUF bytes -> the reference's de-interleaved device layout
     (kernels/quant.cpp:219-220, 441-442): all headers first, then all quants."""

@@ -194,6 +194,46 @@ def test_indexed_moe(dev, dtype, M_is_topk):
     assert o.rel_l2(got, from_storage(want, dtype)) < 2e-3
 
 
+@pytest.mark.parametrize("dtype", [DTYPE_F16, DTYPE_BF16])
+@pytest.mark.parametrize("batch,topk,N,K,E,M_is_topk", [(5, 3, 200, 1024, 6, False), (12, 2, 333, 4096, 8, False),
+                                                       (3, 4, 64, 512, 5, True), (1, 2, 1, 256, 2, True)])
+def test_indexed_moe_q4k(dev, dtype, batch, topk, N, K, E, M_is_topk):
+    """indexed_moe on Q4_K experts: per (token, slot) the exact matrix-vector product against that slot's expert
+    (the oracle's dequantised weights, f32 accumulation), rounded once to the storage type."""
+    rng = np.random.default_rng(batch + N + K)
+    M = topk if M_is_topk else 1
+    x = from_storage(to_storage(rng.standard_normal((batch, M, K)).astype(np.float32), dtype), dtype)
+    w = o.gen_q4k_weight(rng, E * N, K)
+    wb = w.reshape(E, -1)
+    idx = rng.integers(0, E, size=(batch, topk)).astype(np.uint32)
+    want = np.zeros((batch, topk, N), dtype=np.float32)
+    for b in range(batch):
+        for t in range(topk):
+            xr = x[b, 0 if M == 1 else t][None, :]
+            want[b, t] = o.c_qmatmul(xr, wb[idx[b, t]], N, K, True)[0]
+    d = [dev.htod_sync_copy(v) for v in (to_storage(x, dtype), w, idx)]
+    d_out = dev.alloc(batch * topk * N * 2)
+    ops.indexed_moe_q4k(d_out, d[0], d[1], d[2], N, K, M, batch, topk, E, dtype, stream=dev.stream)
+    got = fetch(dev, d_out, dtype, (batch, topk, N))
+    assert o.rel_l2(got, want) < 3e-3  # exact f32 products, one rounding to the 16-bit output
+    assert np.array_equal(got, o.round_through(want, ODT[dtype])) or o.rel_l2(got, o.round_through(want, ODT[dtype])) < 1e-3
+
+
+def test_indexed_moe_q4k_bad_index_gives_zero_row_and_error_word(dev):
+    rng = np.random.default_rng(4)
+    batch, topk, N, K, E = 2, 2, 70, 256, 3
+    x = to_storage(rng.standard_normal((batch, 1, K)).astype(np.float32), DTYPE_BF16)
+    w = o.gen_q4k_weight(rng, E * N, K)
+    idx = np.array([[0, 7], [2, 1]], dtype=np.uint32)
+    d = [dev.htod_sync_copy(v) for v in (x, w, idx)]
+    d_out = dev.htod_sync_copy(np.full(batch * topk * N, 0x7FC0, dtype=np.uint16))
+    assert dev.device_status() == 0
+    ops.indexed_moe_q4k(d_out, d[0], d[1], d[2], N, K, 1, batch, topk, E, DTYPE_BF16, stream=dev.stream)
+    got = fetch(dev, d_out, DTYPE_BF16, (batch, topk, N))
+    assert dev.device_status() == UB_ERR_BAD_INDEX
+    assert (got[0, 1] == 0).all() and np.isfinite(got).all() and np.abs(got[1]).max() > 0
+
+
 def test_silu_and_mul_and_topk_sum(dev):
     rng = np.random.default_rng(12)
     x = o.gen_activation(rng, 33, 2 * 72, True) * 4

@@ -26,6 +26,8 @@ UB_ERR_TOO_LARGE = 8
 DTYPE_I8, DTYPE_U8, DTYPE_F16, DTYPE_BF16, DTYPE_I32, DTYPE_F32 = 0, 1, 4, 5, 6, 8
 # OR into out_dtype of ub_qmatmul_*: the weight bytes were written by the kernel launched just before on the stream
 UB_QMATMUL_WEIGHTS_FRESH = 0x100
+# GGML type tags of the GGUF formats the library takes
+GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q5_K, GGML_Q6_K = 2, 8, 12, 13, 14
 
 
 class UbridgeError(RuntimeError):
@@ -93,6 +95,12 @@ _SIGS = {
     "ub_quantize_q8_0": (c_int, [_P, _P, c_size_t, c_int, _P]),
     "ub_repack_to_split": (c_int, [_P, _P, c_size_t, c_int, _P]),
     "ub_repack_to_interleaved": (c_int, [_P, _P, c_size_t, c_int, _P]),
+    "ub_gguf_block_values": (c_int, [c_int]),
+    "ub_gguf_block_bytes": (c_int, [c_int]),
+    "ub_gguf_tensor_bytes": (c_size_t, [c_int, c_size_t]),
+    "ub_dequant_gguf": (c_int, [_P, _P, c_int, c_size_t, c_int, _P]),
+    "ub_qmatmul_gguf_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "ub_qmatmul_gguf": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "ub_dequant_q6k": (c_int, [_P, _P, c_size_t, c_int, _P]),
     "ub_qmatmul_q6k_f32": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "ub_qmatmul_q6k_bf16": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
@@ -125,6 +133,7 @@ _SIGS = {
     "ub_silu_and_mul": (c_int, [_P, _P, c_int, c_int, c_int, _P]),
     "ub_topk_sum": (c_int, [_P, _P, c_int, c_int, c_int, c_int, _P]),
     "ub_fused_moe_q4k_gemm": (c_int, [_P] * 7 + [c_int] * 9 + [_P, c_size_t, _P]),
+    "ub_indexed_moe_q4k": (c_int, [_P, _P, _P, _P] + [c_int] * 7 + [_P]),
     "ub_moe_layer_q4k_workspace_bytes": (c_size_t, [c_int] * 6),
     "ub_moe_layer_q4k": (c_int, [_P] * 6 + [c_int] * 7 + [_P, c_size_t, _P]),
     "ecclGetVersion": (c_int, [POINTER(c_int)]),

@@ -141,11 +141,12 @@ __device__ __forceinline__ uint32_t deq_pair(uint32_t w4, __nv_bfloat162 dsc, __
 }
 
 constexpr int kTcMaxStages = 8;
-constexpr int kTcWStages = 3;                        // most slots a ring of packed weight tiles has
+constexpr int kTcWStages = 8;                        // most slots a ring of packed weight tiles has
 // Shared-memory plan per token-tile size: the 256-token tile spends its memory on token stages (the
 // copies' latency, not their bandwidth, bounds a K step) and keeps the other two areas small.
 // With two CTAs per SM (the producer-bound MoE tiles of up to 128 tokens) every area is halved again.
-constexpr int tc_wstages(int tok, int ctas) { return (tok > 128 || ctas > 1) ? 2 : 3; }  // packed weight ring
+// packed weight ring: WST slots when the launch names a depth, else 2 or 3
+constexpr int tc_wstages(int tok, int ctas, int wst = 0) { return wst ? wst : ((tok > 128 || ctas > 1) ? 2 : 3); }
 constexpr int tc_stage_tok(int tok, int ctas) {  // staging rows
   return (tok > 128 || ctas > 1) ? 64 : (tok < 128 ? tok : 128);
 }
@@ -182,7 +183,10 @@ struct TcShared {
 // expert, output act[position, N] = silu(gate) * up.  MODE 2 (grouped): output row sorted_ids[position],
 // multiplied by the routed weight.  In the grouped modes M is the number of positions of A.
 // CTAS: CTAs per SM the launch is planned for (2: each takes half of the SM's tensor memory and shared memory).
-template <int TOK, int STAGES, int MODE, int CTAS>
+// WST: slots of the packed-weight ring (0: the default of tc_wstages).  Measured on B200: deeper rings do not
+// help (MoE layer of 256 tokens, one CTA per SM: 3 -> 5 slots 589 -> 567 us; dense M = 2048: 2 -> 4 slots no
+// change), the packed tiles are not what a K step waits for.
+template <int TOK, int STAGES, int MODE, int CTAS, int WST>
 __global__ void __launch_bounds__(kTcThreads, CTAS)
 qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err_word,
                     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
@@ -195,7 +199,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   static_assert(STAGES <= kTcMaxStages, "barrier arrays");
   constexpr uint32_t kBBytes = TOK * 128;              // TOK token rows x 64 bf16
   constexpr int kStageTok = tc_stage_tok(TOK, CTAS);   // tokens the output staging tile holds
-  constexpr int kWStages = tc_wstages(TOK, CTAS);
+  constexpr int kWStages = tc_wstages(TOK, CTAS, WST);
+  static_assert(kWStages <= kTcWStages, "barrier arrays");
   constexpr uint32_t kStagingOff = STAGES * kBBytes;   // [kStageTok tokens][128 weight rows] bf16
   constexpr uint32_t kWOff = kStagingOff + kStageTok * 256;  // packed weight ring: [128 rows][144 bytes] each
   constexpr int kAccBufs = (TOK > 128 || CTAS > 1) ? 1 : 2;  // accumulator buffers at the start of the allocation
@@ -617,11 +622,11 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int TOK, int STAGES, int MODE, int CTAS = 1>
+template <int TOK, int STAGES, int MODE, int CTAS = 1, int WST = 0>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const TcGroup& grp, int w_rows_total,
               cudaStream_t s) {
   const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(tc_stage_tok(TOK, CTAS)) * 256 +
-                      static_cast<size_t>(tc_wstages(TOK, CTAS)) * kTcWBytes + 1024;
+                      static_cast<size_t>(tc_wstages(TOK, CTAS, WST)) * kTcWBytes + 1024;
   const int sms = ub::num_sms();
   int grid = sms * CTAS;  // grouped launches learn their tile count on the device; idle CTAs leave at once
   if (MODE == 0) {
@@ -653,7 +658,7 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ub::fail(UB_ERR_UNSUPPORTED);
-  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS>;
+  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS, WST>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);

@@ -67,6 +67,22 @@ def repack_to_interleaved(interleaved, split, nblocks: int, is_q4k: bool, stream
           "ub_repack_to_interleaved")
 
 
+# ----------------------------------------------------------------------------- GGUF tensor blobs (dispatch on the type tag)
+def gguf_tensor_bytes(ggml_type: int, numel: int) -> int:
+    return lib().ub_gguf_tensor_bytes(ggml_type, numel)
+
+
+def dequantize_gguf(out, blob, ggml_type: int, numel: int, out_dtype: int, stream=None) -> None:
+    check(lib().ub_dequant_gguf(_p(out), _p(blob), ggml_type, numel, out_dtype, _s(stream)), "ub_dequant_gguf")
+
+
+def qmatmul_gguf(y, x, blob, ggml_type: int, M: int, N: int, K: int, *, x_dtype: int, out_dtype: int, workspace=None,
+                 ws_bytes: int = 0, stream=None) -> None:
+    """y[M,N] = x[M,K] . W^T for a GGUF tensor blob of N rows x K values of the given GGML type."""
+    check(lib().ub_qmatmul_gguf(_p(y), _p(x), _p(blob), ggml_type, M, N, K, x_dtype, out_dtype, _p(workspace), ws_bytes,
+                                _s(stream)), "ub_qmatmul_gguf")
+
+
 # ----------------------------------------------------------------------------- quantized matmul
 def qmatmul_workspace_bytes(M: int, N: int, K: int, is_q4k: bool) -> int:
     return lib().ub_qmatmul_workspace_bytes(M, N, K, int(is_q4k))
@@ -163,6 +179,13 @@ def fused_moe_q4k_gemm(C, A, Bq, topk_weights, sorted_ids, experts_ids, num_toke
                                       _p(num_tokens_post_pad), M, K, N, E, topk_ids_size, top_k, block_size,
                                       int(mul_routed_weight), int(act_silu_mul), _p(workspace), ws_bytes, _s(stream)),
           "ub_fused_moe_q4k_gemm")
+
+
+def indexed_moe_q4k(out, inp, wq, indices, N: int, K: int, M: int, batch: int, topk: int, num_experts: int, dtype: int,
+                    stream=None) -> None:
+    """out[b,t,:] = inp[b,(M==1?0:t),:] . dequant(wq[indices[b,t]])^T for Q4_K expert matrices."""
+    check(lib().ub_indexed_moe_q4k(_p(out), _p(inp), _p(wq), _p(indices), N, K, M, batch, topk, num_experts, dtype,
+                                   _s(stream)), "ub_indexed_moe_q4k")
 
 
 def moe_layer_q4k_workspace_bytes(T: int, H: int, I: int, E: int, top_k: int, block_size: int) -> int:
