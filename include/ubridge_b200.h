@@ -179,6 +179,15 @@ int ub_qmatmul_q8_0_f32(void* y, const void* x, const void* wq, int M, int N, in
  * result here has the bits of that sequence (gate and up rounded to the output type first).  One token with K a
  * multiple of 2048 up to 12288 is one launch and needs no workspace; other shapes need
  * ub_qmatmul_q4k_gate_up_workspace_bytes. */
+/* RMSNorm in front of the matmul.  topsaten_rms_norm is the reference's stand-alone norm (src/ffi.rs:719-728):
+ * output[t,:] = T(T(input[t,:] * rsqrt(mean(input[t,:]^2) + epsilon)) * gamma), dtype_code f32 / f16 / bf16.
+ * ub_qmatmul_q4k_rmsnorm_bf16 runs the Q4_K matmul (gate_up == 0: y[M,N] = xn . W^T; gate_up != 0: W = [gate
+ * rows; up rows] of 2 N rows and y[M,N] = silu(xn . Wgate^T) * (xn . Wup^T)) on xn = that norm of x: for one
+ * token with K a multiple of 2048 up to 12288 as ONE launch (every CTA normalises the row in its prologue),
+ * otherwise norm into the workspace, then matmul (ub_qmatmul_q4k_rmsnorm_workspace_bytes). */
+int topsaten_rms_norm(void* output, const void* input, const void* gamma, int num_tokens, int hidden_size, float epsilon, int dtype_code, void* stream);
+size_t ub_qmatmul_q4k_rmsnorm_workspace_bytes(int M, int N, int K, int gate_up);
+int ub_qmatmul_q4k_rmsnorm_bf16(void* y, const void* x, const void* gamma, float eps, const void* wq, int M, int N, int K, int gate_up, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 size_t ub_qmatmul_q4k_gate_up_workspace_bytes(int M, int I, int K);
 int ub_qmatmul_q4k_gate_up_bf16(void* y, const void* x, const void* wq, int M, int I, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
 int ub_qmatmul_q8_0_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* workspace, size_t ws_bytes, void* stream);
@@ -312,6 +321,10 @@ unsigned ub_allreduce_oneshot_set_spin_limit(unsigned polls);
  * last CTA of the grid completes the exchange: ONE launch; other shapes run the matmul and then the one-shot
  * exchange.  world <= 1 is the plain matmul.  No reference counterpart as an entry point. */
 int ub_qmatmul_q4k_allreduce_bf16(void* y, const void* x, const void* wq, int M, int N, int K, void* const* staging, int rank, int world, size_t max_bytes, void* stream);
+/* The same with the residual add of a decoder layer in the exchange's epilogue: y = residual + sum over the
+ * ranks (residual bf16 [M,N], may be NULL, must not alias y; the residual enters the rank-ordered f32 sum first,
+ * one rounding).  world <= 1: y = residual + x . W^T, for one token in the matmul's own epilogue. */
+int ub_qmatmul_q4k_allreduce_residual_bf16(void* y, const void* x, const void* wq, const void* residual, int M, int N, int K, void* const* staging, int rank, int world, size_t max_bytes, void* stream);
 
 /* ------------------------------------------------------------------ collectives
  * ECCL-shaped surface (src/eccllib.rs:7-169, src/eccl.rs:14-426) forwarding to NCCL over

@@ -397,6 +397,15 @@ def fused_moe(A, B_f32, topk_w, sorted_ids, experts_ids, num_post_pad, top_k, bl
     return C
 
 
+def rms_norm(x_f32: np.ndarray, gamma_f32: np.ndarray, eps: float, dtype: int) -> np.ndarray:
+    """RMSNorm as the reference's stand-alone op is used (src/ffi.rs:719-728): the row times rsqrt(mean(x^2) + eps),
+    rounded to the storage type, then times gamma, rounded again."""
+    x = np.asarray(x_f32, dtype=np.float32)
+    ms = (x.astype(np.float64) ** 2).mean(axis=-1, keepdims=True)
+    xn = round_through((x * (1.0 / np.sqrt(ms + eps)).astype(np.float32)).astype(np.float32), dtype)
+    return round_through(xn * np.asarray(gamma_f32, dtype=np.float32), dtype)
+
+
 def silu_and_mul(x_f32: np.ndarray, dtype: int) -> np.ndarray:
     """kernels/topsaten_ops_wrapper.cpp:375-391: out[:, :D] = silu(x[:, :D]) * x[:, D:]."""
     x = np.asarray(x_f32, dtype=np.float32)

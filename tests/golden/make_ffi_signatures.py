@@ -19,7 +19,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # the declarations on the quantized-linear / fused-MoE path (the rest of ffi.rs is out of scope)
 ON_PATH = re.compile(r"^(moe_(f16|bf16)|indexed_moe_(f16|bf16)|dequant_(f16|bf16)|moe_align_block_size|"
                      r"invoke_fused_moe_(f16|bf16)|topk_softmax_(f32|f16|bf16)|topsaten_topk_softmax_f32|"
-                     r"topsaten_moe_align_block_size|topsaten_fused_moe_gemm|topsaten_release_graph_workspace_pool)$")
+                     r"topsaten_moe_align_block_size|topsaten_fused_moe_gemm|topsaten_release_graph_workspace_pool|"
+                     r"topsaten_rms_norm)$")
 
 
 def rust_kind(t: str) -> str:

@@ -60,7 +60,7 @@ def test_fixture_is_current_when_the_reference_is_present():
 def test_every_reference_named_export_matches_ffi_rs():
     ref = _load()["ffi"]
     decls = _header_decls()
-    assert len(ref) == 16
+    assert len(ref) == 17
     for name, sig in sorted(ref.items()):
         assert name in decls, "reference FFI function missing from the header: " + name
         ret, items = decls[name]

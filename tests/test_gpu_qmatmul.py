@@ -287,3 +287,65 @@ def test_gate_up_silu_matches_the_two_call_sequence(dev, M, I, K):
     gu = o.round_through(o.c_qmatmul(x, w, 2 * I, K, True), o.UB_BF16)
     want = o.silu_and_mul(gu, o.UB_BF16)
     assert o.rel_l2(got, want) < (1e-2 if M > 8 else 5e-3)
+
+
+# ----------------------------------------------------------------------------- RMSNorm in front, residual behind
+@pytest.mark.parametrize("dtype", [DTYPE_F32, DTYPE_F16, DTYPE_BF16])
+def test_rms_norm_standalone(dev, dtype):
+    rng = np.random.default_rng(21)
+    T, H = 7, 1000
+    x = o.round_through(rng.standard_normal((T, H)).astype(np.float32) * 3, {DTYPE_F32: o.UB_F32, DTYPE_F16: o.UB_F16, DTYPE_BF16: o.UB_BF16}[dtype])
+    g = o.round_through(rng.uniform(0.5, 1.5, size=H).astype(np.float32), {DTYPE_F32: o.UB_F32, DTYPE_F16: o.UB_F16, DTYPE_BF16: o.UB_BF16}[dtype])
+    want = o.rms_norm(x, g, 1e-5, {DTYPE_F32: o.UB_F32, DTYPE_F16: o.UB_F16, DTYPE_BF16: o.UB_BF16}[dtype])
+    d_out = dev.alloc(T * H * ESIZE[dtype])
+    ops.rms_norm(d_out, dev.htod_sync_copy(to_storage(x, dtype)), dev.htod_sync_copy(to_storage(g, dtype)), T, H, 1e-5,
+                 dtype, stream=dev.stream)
+    got = fetch(dev, d_out, dtype, (T, H))
+    # f32 vs f64 mean and rsqrt: a value on a rounding boundary may fall the other way, by one unit of the type
+    assert o.rel_l2(got, want) < {DTYPE_F32: 1e-6, DTYPE_F16: 1e-3, DTYPE_BF16: 4e-3}[dtype]
+
+
+@pytest.mark.parametrize("M,N,K,gate_up", [(1, 1000, 4096, False), (1, 640, 2048, False), (1, 520, 8192, False),
+                                           (1, 700, 8192, True), (1, 96, 1024, False), (3, 200, 2048, True),
+                                           (20, 136, 1024, False)])
+def test_matmul_on_rms_norm(dev, M, N, K, gate_up):
+    """ub_qmatmul_q4k_rmsnorm_bf16: one launch for one token (the norm in the matmul's prologue), norm + matmul
+    otherwise; against the oracle's norm -> exact matmul (-> SiLU.up)."""
+    rng = np.random.default_rng(M + N + K)
+    rows = 2 * N if gate_up else N
+    w = o.gen_q4k_weight(rng, rows, K)
+    x = o.gen_activation(rng, M, K, True) * 2.5
+    x = o.round_through(x, o.UB_BF16)
+    g = o.round_through(rng.uniform(0.5, 1.5, size=K).astype(np.float32), o.UB_BF16)
+    xn = o.rms_norm(x, g, 1e-5, o.UB_BF16)
+    full = o.c_qmatmul(xn, w, rows, K, True)
+    want = o.silu_and_mul(o.round_through(full, o.UB_BF16), o.UB_BF16) if gate_up else full
+    ws_bytes = ops.qmatmul_q4k_rmsnorm_workspace_bytes(M, N, K, gate_up)
+    ws = dev.alloc(max(ws_bytes, 256))
+    d_y = dev.alloc(M * N * 2)
+    ops.qmatmul_q4k_rmsnorm(d_y, dev.htod_sync_copy(to_storage(x, DTYPE_BF16)), dev.htod_sync_copy(to_storage(g, DTYPE_BF16)),
+                            1e-5, dev.htod_sync_copy(w), M, N, K, gate_up=gate_up, out_dtype=DTYPE_BF16, workspace=ws,
+                            ws_bytes=ws_bytes, stream=dev.stream)
+    got = fetch(dev, d_y, DTYPE_BF16, (M, N))
+    # bf16 activations after the norm (a boundary case may round the other way) and bf16 output
+    assert o.rel_l2(got, want) < 8e-3
+
+
+@pytest.mark.parametrize("N,K", [(1024, 4096), (520, 8192), (200, 1024)])
+def test_matmul_with_residual_on_one_rank(dev, N, K):
+    import ctypes
+
+    from ubridge_b200._lib import check, lib
+
+    rng = np.random.default_rng(N + K)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, 1, K, True)
+    r = o.round_through(rng.standard_normal((1, N)).astype(np.float32), o.UB_BF16)
+    want = r + o.c_qmatmul(x, w, N, K, True)
+    d_y = dev.alloc(N * 2)
+    d = [dev.htod_sync_copy(v) for v in (to_storage(x, DTYPE_BF16), w, to_storage(r, DTYPE_BF16))]
+    check(lib().ub_qmatmul_q4k_allreduce_residual_bf16(ctypes.c_void_p(d_y.ptr), ctypes.c_void_p(d[0].ptr),
+                                                       ctypes.c_void_p(d[1].ptr), ctypes.c_void_p(d[2].ptr), 1, N, K,
+                                                       None, 0, 1, 0, dev.stream), "residual matmul")
+    got = fetch(dev, d_y, DTYPE_BF16, (1, N))
+    assert o.rel_l2(got, want) < 5e-3

@@ -113,6 +113,12 @@ _SIGS = {
     "ub_qmatmul_q4k_gate_up_bf16": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "ub_qmatmul_q4k_allreduce_bf16": (c_int, [_P, _P, _P, c_int, c_int, c_int, ctypes.POINTER(_P), c_int, c_int,
                                               c_size_t, _P]),
+    "ub_qmatmul_q4k_allreduce_residual_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, ctypes.POINTER(_P), c_int,
+                                                       c_int, c_size_t, _P]),
+    "topsaten_rms_norm": (c_int, [_P, _P, _P, c_int, c_int, ctypes.c_float, c_int, _P]),
+    "ub_qmatmul_q4k_rmsnorm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "ub_qmatmul_q4k_rmsnorm_bf16": (c_int, [_P, _P, _P, ctypes.c_float, _P, c_int, c_int, c_int, c_int, c_int, _P,
+                                            c_size_t, _P]),
     "ub_qmatmul_q4k_f32_static": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "topk_softmax_f32": (None, [_P, _P, _P, c_int32, c_int32, c_int32, c_int32, _P]),
     "topk_softmax_f16": (None, [_P, _P, _P, c_int32, c_int32, c_int32, c_int32, _P]),

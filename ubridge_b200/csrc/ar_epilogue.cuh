@@ -27,6 +27,14 @@ struct ArParams {
   int rank, world;                   // world <= 1: no exchange, rows go straight to y
   uint32_t spin_limit;
   size_t max_bytes;
+  const __nv_bfloat16* residual;     // optional [n]: y = residual + sum (the residual add of a decoder layer), else null
+};
+
+// Optional pieces of a one-token matmul launch, all off when null / zero.
+struct M1Extras {
+  const void* gamma;   // RMSNorm weight [K] in the activation type: the matmul runs on rmsnorm(x)
+  float eps;
+  const ArParams* ar;  // exchange over the ranks (world > 1) and / or a residual row added to the output
 };
 
 __device__ __forceinline__ uint32_t ar_epoch(const ArParams& ar) {
@@ -78,6 +86,15 @@ __device__ __forceinline__ void ar_finish(const ArParams& ar, uint32_t epoch, vo
     float acc[8];
 #pragma unroll
     for (int e = 0; e < 8; e++) acc[e] = 0.f;
+    if (ar.residual) {  // the residual comes first, then the ranks in order: the same bits on every rank
+      const uint4 r = __ldg(reinterpret_cast<const uint4*>(ar.residual) + i);
+      const uint32_t r4[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        acc[2 * e] = __uint_as_float(r4[e] << 16);
+        acc[2 * e + 1] = __uint_as_float(r4[e] & 0xFFFF0000u);
+      }
+    }
     for (int p = 0; p < ar.world; p++) {
       uint4 v;  // written by a peer: not through L1
       asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"

@@ -125,6 +125,23 @@ struct Raw8<__nv_bfloat16> {
   }
 };
 
+// a normalised activation as a stand-alone RMSNorm kernel would have stored it (rounded to the activation type)
+__device__ __forceinline__ float round_as(float v, const float*) { return v; }
+__device__ __forceinline__ float round_as(float v, const __nv_bfloat16*) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// RMSNorm scale of the row from the per-warp sums of squares: every warp adds the kW partials in the same order
+__device__ __forceinline__ float rms_scale(float my_ss, float* ssq, int warp, int lane, int K, float eps) {
+  my_ss = warp_sum(my_ss);
+  if (lane == 0) ssq[warp] = my_ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kW; w++) tot += ssq[w];
+  return rsqrtf(tot / static_cast<float>(K) + eps);
+}
+
 __device__ __forceinline__ void st_out(void* y, size_t idx, int dtype, float v) {
   if (dtype == UB_DTYPE_F32)
     static_cast<float*>(y)[idx] = v;
@@ -139,7 +156,8 @@ __device__ __forceinline__ void st_out(void* y, size_t idx, int dtype, float v) 
 template <typename XT, int SBW>
 __global__ void __launch_bounds__(kThreadsM1, 2)
 qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y_dtype, int S, int early,
-                    int* err_word, const ArParams ar, const __grid_constant__ CUtensorMap w_map) {
+                    int* err_word, const XT* __restrict__ gamma, float eps, const ArParams ar,
+                    const __grid_constant__ CUtensorMap w_map) {
   constexpr int kRowStride = 8 * SBW * UB_Q4K_BYTES;  // 1152 or 2304: whole 128-byte lines
   constexpr int kStageBytes = 16 * kRowStride;
   extern __shared__ __align__(128) unsigned char m1_smem_raw[];
@@ -148,6 +166,7 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
       m1_smem_raw + ((1024u - (static_cast<uint32_t>(__cvta_generic_to_shared(m1_smem_raw)) & 1023u)) & 1023u);
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStagesM1];  // full[S], empty[S]
   __shared__ float red[kW][kBatchTiles][16];
+  __shared__ float ssq[kW];  // per-warp sums of squares of the activations (RMSNorm prologue)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(sm));
@@ -198,11 +217,30 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
 #pragma unroll
     for (int k = 0; k < SBW; k++) raw[k].load(x + static_cast<size_t>(warp + 8 * k) * 256 + 8 * lane);
     // the rest of the ring goes out right behind the activation loads
+    Raw8<XT> graw[SBW];
+    if (gamma)
+#pragma unroll
+      for (int k = 0; k < SBW; k++) graw[k].load(gamma + static_cast<size_t>(warp + 8 * k) * 256 + 8 * lane);
     if (threadIdx.x == 0)
       for (int n = n_early; n < min(S, my_tiles); n++) issue_tile(n);
     float v[SBW][8];
 #pragma unroll
     for (int k = 0; k < SBW; k++) raw[k].unpack(v[k]);
+    if (gamma) {  // RMSNorm in front of the matmul: x * rsqrt(mean(x^2) + eps) * gamma, rounded to the activation type
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < SBW; k++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss = fmaf(v[k][e], v[k][e], ss);
+      const float scale = rms_scale(ss, ssq, warp, lane, 2048 * SBW, eps);
+#pragma unroll
+      for (int k = 0; k < SBW; k++) {
+        float gv[8];
+        graw[k].unpack(gv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[k][e] = round_as(round_as(v[k][e] * scale, x) * gv[e], x);
+      }
+    }
 #pragma unroll
     for (int k = 0; k < SBW; k++) {
       float amax = 0.f;
@@ -351,7 +389,7 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
         if (ar.world > 1)
           ar_push(ar, epoch, row, tot);
         else
-          st_out(y, row, y_dtype, tot);
+          st_out(y, row, y_dtype, ar.residual ? tot + __bfloat162float(ar.residual[row]) : tot);
       }
     }
     if (b + 1 < nbatches) __syncthreads();  // before the next batch overwrites the partial sums
@@ -361,8 +399,8 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
 }
 
 template <typename XT, int SBW>
-int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const ArParams& ar,
-              cudaStream_t s) {
+int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const XT* gamma,
+              float eps, const ArParams& ar, cudaStream_t s) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -403,7 +441,7 @@ int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, y_dtype, S, early, ub::device_error_word(), ar, wmap);
+  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, y_dtype, S, early, ub::device_error_word(), gamma, eps, ar, wmap);
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
@@ -430,7 +468,8 @@ constexpr int kMaxChunks = 6;
 template <typename XT, bool GU>
 __global__ void __launch_bounds__(kThreadsM1, 2)
 qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int nch, int y_dtype, int S, int early,
-                         int* err_word, const ArParams ar, const __grid_constant__ CUtensorMap w_map) {
+                         int* err_word, const XT* __restrict__ gamma, float eps, const ArParams ar,
+                         const __grid_constant__ CUtensorMap w_map) {
   constexpr int kRowStride = 8 * UB_Q4K_BYTES;  // 1152 = 9 lines
   constexpr int kStageBytes = 16 * kRowStride;
   extern __shared__ __align__(128) unsigned char m1_smem_raw[];
@@ -438,6 +477,7 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
       m1_smem_raw + ((1024u - (static_cast<uint32_t>(__cvta_generic_to_shared(m1_smem_raw)) & 1023u)) & 1023u);
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStagesM1];
   __shared__ float red[kW][kBatchTiles][16];
+  __shared__ float ssq[kW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(sm));
@@ -491,13 +531,37 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
 #pragma unroll
     for (int c = 0; c < kMaxChunks; c++)
       if (c < nch) raw[c].load(x + static_cast<size_t>(8 * c + warp) * 256 + 8 * lane);
+    Raw8<XT> graw[kMaxChunks];
+    if (gamma)
+#pragma unroll
+      for (int c = 0; c < kMaxChunks; c++)
+        if (c < nch) graw[c].load(gamma + static_cast<size_t>(8 * c + warp) * 256 + 8 * lane);
     if (threadIdx.x == 0)
       for (int n = n_early; n < min(S, my_items); n++) issue_item(n);
+    float scale = 1.f;
+    if (gamma) {  // RMSNorm in front of the matmul
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < kMaxChunks; c++) {
+        if (c >= nch) break;
+        float v[8];
+        raw[c].unpack(v);
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss = fmaf(v[e], v[e], ss);
+      }
+      scale = rms_scale(ss, ssq, warp, lane, 2048 * nch, eps);
+    }
 #pragma unroll
     for (int c = 0; c < kMaxChunks; c++) {
       if (c >= nch) break;
       float v[8];
       raw[c].unpack(v);
+      if (gamma) {
+        float gv[8];
+        graw[c].unpack(gv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = round_as(round_as(v[e] * scale, x) * gv[e], x);
+      }
       float amax = 0.f;
 #pragma unroll
       for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[e]));
@@ -641,7 +705,7 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
         if (ar.world > 1)
           ar_push(ar, epoch, row, tot);
         else
-          st_out(y, row, y_dtype, tot);
+          st_out(y, row, y_dtype, ar.residual ? tot + __bfloat162float(ar.residual[row]) : tot);
       }
     }
     if (b + 1 < nbatches) __syncthreads();
@@ -651,8 +715,8 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
 }
 
 template <typename XT, bool GU>
-int launch_m1_long(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const ArParams& ar,
-                   cudaStream_t s) {
+int launch_m1_long(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const XT* gamma,
+                   float eps, const ArParams& ar, cudaStream_t s) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -693,7 +757,7 @@ int launch_m1_long(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, nch, y_dtype, S, early, ub::device_error_word(), ar, wmap);
+  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, nch, y_dtype, S, early, ub::device_error_word(), gamma, eps, ar, wmap);
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
@@ -708,36 +772,49 @@ namespace ub {
 // y[N] = dequant(Wq) . x for one token; UB_ERR_UNSUPPORTED (without touching the thread's status) for shapes
 // these kernels do not take (K not a multiple of 2048 or beyond 12288, unaligned weights, no tensor-map encoder).
 // fresh: the weight bytes may have been written by the kernel launched just before on the same stream.
-// ar: when ar->world > 1 the launch ends with the all-reduce over the ranks (y bf16, N % 8 == 0).
 template <typename XT>
-int q4k_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const ArParams* ar,
-                cudaStream_t s) {
+int q4k_gemv_m1x(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const M1Extras& ex,
+                 cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
   if (reinterpret_cast<uintptr_t>(w) & 15) return UB_ERR_UNSUPPORTED;
   ArParams none;
   memset(&none, 0, sizeof(none));
-  const ArParams& a = ar ? *ar : none;
-  if (K == 4096) return launch_m1<XT, 2>(w, x, y, N, K, y_dtype, fresh, a, s);
-  if (K == 2048) return launch_m1<XT, 1>(w, x, y, N, K, y_dtype, fresh, a, s);
-  if (K % 2048 == 0) return launch_m1_long<XT, false>(w, x, y, N, K, y_dtype, fresh, a, s);  // up to 12288
+  const ArParams& a = ex.ar ? *ex.ar : none;
+  const XT* gamma = static_cast<const XT*>(ex.gamma);
+  if (K == 4096) return launch_m1<XT, 2>(w, x, y, N, K, y_dtype, fresh, gamma, ex.eps, a, s);
+  if (K == 2048) return launch_m1<XT, 1>(w, x, y, N, K, y_dtype, fresh, gamma, ex.eps, a, s);
+  if (K % 2048 == 0) return launch_m1_long<XT, false>(w, x, y, N, K, y_dtype, fresh, gamma, ex.eps, a, s);  // <= 12288
   return UB_ERR_UNSUPPORTED;
 }
 
-// y[N] = silu(Wgate . x) * (Wup . x) for one token, wq = [gate rows; up rows] (2 N rows of K); same contract.
 template <typename XT>
-int q4k_gemv_m1_gate_up(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
+int q4k_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const ArParams* ar,
+                cudaStream_t s) {
+  const M1Extras ex = {nullptr, 0.f, ar};
+  return q4k_gemv_m1x<XT>(wq, x, y, N, K, y_dtype, fresh, ex, s);
+}
+
+// y[N] = silu(Wgate . x) * (Wup . x) for one token, wq = [gate rows; up rows] (2 N rows of K); same contract;
+// gamma != null: on rmsnorm(x).
+template <typename XT>
+int q4k_gemv_m1_gate_up(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const void* gamma,
+                        float eps, cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
   if ((reinterpret_cast<uintptr_t>(w) & 15) || K % 2048) return UB_ERR_UNSUPPORTED;
   ArParams none;
   memset(&none, 0, sizeof(none));
-  return launch_m1_long<XT, true>(w, x, y, N, K, y_dtype, fresh, none, s);
+  return launch_m1_long<XT, true>(w, x, y, N, K, y_dtype, fresh, static_cast<const XT*>(gamma), eps, none, s);
 }
 
+template int q4k_gemv_m1x<float>(const void*, const float*, void*, int, int, int, bool, const M1Extras&, cudaStream_t);
+template int q4k_gemv_m1x<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, bool, const M1Extras&,
+                                         cudaStream_t);
 template int q4k_gemv_m1<float>(const void*, const float*, void*, int, int, int, bool, const ArParams*, cudaStream_t);
 template int q4k_gemv_m1<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, bool, const ArParams*,
                                         cudaStream_t);
-template int q4k_gemv_m1_gate_up<float>(const void*, const float*, void*, int, int, int, bool, cudaStream_t);
-template int q4k_gemv_m1_gate_up<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, bool,
-                                                cudaStream_t);
+template int q4k_gemv_m1_gate_up<float>(const void*, const float*, void*, int, int, int, bool, const void*, float,
+                                        cudaStream_t);
+template int q4k_gemv_m1_gate_up<__nv_bfloat16>(const void*, const __nv_bfloat16*, void*, int, int, int, bool, const void*,
+                                                float, cudaStream_t);
 
 }  // namespace ub

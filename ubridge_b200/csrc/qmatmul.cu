@@ -24,7 +24,11 @@ template <typename XT>
 int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
              const ArParams* ar, cudaStream_t s);
 template <typename XT>
-int q4k_gemv_m1_gate_up(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+int q4k_gemv_m1_gate_up(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const void* gamma,
+                        float eps, cudaStream_t s);
+template <typename XT>
+int q4k_gemv_m1x(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const M1Extras& ex,
+                 cudaStream_t s);
 int q4k_gemm_mma(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
 uint32_t oneshot_spin_limit();
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
@@ -46,6 +50,34 @@ __global__ void convert_bf16_to_kernel(T* __restrict__ out, const __nv_bfloat16*
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<size_t>(gridDim.x) * blockDim.x)
     out[i] = ub::from_f32<T>(__bfloat162float(in[i]));
+}
+
+// RMSNorm of rows: out = T(T(x * rsqrt(mean(x^2) + eps)) * gamma), the normalised value rounded to the storage
+// type before the weight is applied (the usual definition).  One warp per row.
+template <typename T>
+__global__ void __launch_bounds__(256) rms_norm_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                       const T* __restrict__ gamma, int rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* x = in + static_cast<size_t>(row) * H;
+  float ss = 0.f;
+  for (int k = lane; k < H; k += 32) {
+    const float v = ub::to_f32(x[k]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = ub::warp_sum(ss);
+  const float scale = rsqrtf(ss / static_cast<float>(H) + eps);
+  T* o = out + static_cast<size_t>(row) * H;
+  for (int k = lane; k < H; k += 32)
+    o[k] = ub::from_f32<T>(ub::to_f32(ub::from_f32<T>(ub::to_f32(x[k]) * scale)) * ub::to_f32(gamma[k]));
+}
+
+// y += r (bf16), the residual add behind a matmul that could not carry it in its epilogue
+__global__ void add_bf16_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ r, size_t n) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    y[i] = __float2bfloat16_rn(__bfloat162float(r[i]) + __bfloat162float(y[i]));
 }
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -196,7 +228,7 @@ int ub_qmatmul_q4k_gate_up_bf16(void* y, const void* x, const void* wq, int M, i
   if (ub::take_weights_written(s)) fresh = true;
   if (M == 1) {
     const int st = ub::q4k_gemv_m1_gate_up<__nv_bfloat16>(wq, static_cast<const __nv_bfloat16*>(x), y, I, K, out_dtype,
-                                                         fresh, s);
+                                                         fresh, nullptr, 0.f, s);
     if (st != UB_ERR_UNSUPPORTED) return st;
   }
   const size_t need = ub_qmatmul_q4k_gate_up_workspace_bytes(M, I, K);
@@ -212,6 +244,61 @@ int ub_qmatmul_q4k_gate_up_bf16(void* y, const void* x, const void* wq, int M, i
   return ub_silu_and_mul(y, ws, M, I, out_dtype, stream);
 }
 
+// ---- RMSNorm in front of the matmul ----
+// The reference's stand-alone norm (src/ffi.rs:719-728): output[t,:] = rmsnorm(input[t,:]) * gamma.
+int topsaten_rms_norm(void* output, const void* input, const void* gamma, int num_tokens, int hidden_size, float epsilon,
+                      int dtype_code, void* stream) {
+  if (num_tokens == 0 || hidden_size == 0) return ub::fail(UB_OK);
+  if (!output || !input || !gamma || num_tokens < 0 || hidden_size < 0) return ub::fail(UB_ERR_INVALID_ARG);
+  const int grid = (num_tokens + 7) / 8;
+  cudaStream_t s = ub::as_stream(stream);
+  UB_DISPATCH_FLOAT(dtype_code, T, (rms_norm_kernel<T><<<grid, 256, 0, s>>>(static_cast<T*>(output),
+                                                                          static_cast<const T*>(input),
+                                                                          static_cast<const T*>(gamma), num_tokens,
+                                                                          hidden_size, epsilon)));
+  return ub::check_launch();
+}
+
+size_t ub_qmatmul_q4k_rmsnorm_workspace_bytes(int M, int N, int K, int gate_up) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const size_t inner = gate_up ? ub_qmatmul_q4k_gate_up_workspace_bytes(M, N, K) : ub_qmatmul_workspace_bytes(M, N, K, 1);
+  return align_up(static_cast<size_t>(M) * K * 2, 256) + align_up(inner, 256);
+}
+
+// y = rmsnorm(x; gamma, eps) . W^T (gate_up == 0, y [M,N]) or silu(. Wgate^T) * (. Wup^T) (gate_up != 0, y [M,N] with
+// W = [gate rows; up rows] of 2 N rows), x and gamma bf16.  One token with K a multiple of 2048 up to 12288 is one
+// launch: every CTA of the matmul normalises the activation row in its prologue.  Other shapes run
+// topsaten_rms_norm into the workspace and then the matmul.
+int ub_qmatmul_q4k_rmsnorm_bf16(void* y, const void* x, const void* gamma, float eps, const void* wq, int M, int N,
+                                int K, int gate_up, int out_dtype, void* workspace, size_t ws_bytes, void* stream) {
+  if (M == 0 || N == 0) return ub::fail(UB_OK);
+  if (!y || !x || !gamma || !wq || M < 0 || N < 0 || K <= 0 || K % UB_QK_K) return ub::fail(UB_ERR_INVALID_ARG);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(gamma) & 15) ||
+      (reinterpret_cast<uintptr_t>(wq) & 15))
+    return ub::fail(UB_ERR_INVALID_ARG);
+  cudaStream_t s = ub::as_stream(stream);
+  if (M == 1) {
+    const bool fresh = ub::take_weights_written(s);
+    int st;
+    if (gate_up) {
+      st = ub::q4k_gemv_m1_gate_up<__nv_bfloat16>(wq, static_cast<const __nv_bfloat16*>(x), y, N, K, out_dtype, fresh,
+                                                  gamma, eps, s);
+    } else {
+      const ub::M1Extras ex = {gamma, eps, nullptr};
+      st = ub::q4k_gemv_m1x<__nv_bfloat16>(wq, static_cast<const __nv_bfloat16*>(x), y, N, K, out_dtype, fresh, ex, s);
+    }
+    if (st != UB_ERR_UNSUPPORTED) return st;
+  }
+  const size_t need = ub_qmatmul_q4k_rmsnorm_workspace_bytes(M, N, K, gate_up);
+  if (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return ub::fail(UB_ERR_WORKSPACE);
+  char* ws = static_cast<char*>(workspace);
+  const size_t xn_bytes = align_up(static_cast<size_t>(M) * K * 2, 256);
+  int st = topsaten_rms_norm(ws, x, gamma, M, K, eps, UB_DTYPE_BF16, stream);
+  if (st != UB_OK) return st;
+  if (gate_up) return ub_qmatmul_q4k_gate_up_bf16(y, ws, wq, M, N, K, out_dtype, ws + xn_bytes, ws_bytes - xn_bytes, stream);
+  return qmatmul(true, UB_DTYPE_BF16, y, ws, wq, M, N, K, out_dtype, ws + xn_bytes, ws_bytes - xn_bytes, stream);
+}
+
 // ---- row-split matmul with the all-reduce over the ranks in its epilogue ----
 // y[M, N] (bf16, summed over the ranks, identical bits on every rank) = sum_r x_r[M, K] . W_r^T.  `staging`,
 // rank, world, max_bytes as for ub_allreduce_oneshot_bf16 (the same buffers serve both; M*N*2 <= max_bytes).
@@ -219,9 +306,40 @@ int ub_qmatmul_q4k_gate_up_bf16(void* y, const void* x, const void* wq, int M, i
 // peers, the last CTA completes the exchange); other shapes run the matmul and then the one-shot exchange.
 int ub_qmatmul_q4k_allreduce_bf16(void* y, const void* x, const void* wq, int M, int N, int K, void* const* staging,
                                   int rank, int world, size_t max_bytes, void* stream) {
+  return ub_qmatmul_q4k_allreduce_residual_bf16(y, x, wq, nullptr, M, N, K, staging, rank, world, max_bytes, stream);
+}
+
+// The same with the residual add of a decoder layer: y = residual + sum over the ranks (residual bf16 [M,N], may
+// be null, must not alias y).  world <= 1: y = residual + x . W^T in the matmul's epilogue for one token.
+int ub_qmatmul_q4k_allreduce_residual_bf16(void* y, const void* x, const void* wq, const void* residual, int M, int N,
+                                           int K, void* const* staging, int rank, int world, size_t max_bytes,
+                                           void* stream) {
   if (M == 0 || N == 0) return ub::fail(UB_OK);
   if (!y || !x || !wq || M < 0 || N < 0 || K <= 0 || K % UB_QK_K) return ub::fail(UB_ERR_INVALID_ARG);
-  if (world <= 1) return qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, UB_DTYPE_BF16, nullptr, 0, stream);
+  if (residual && (residual == y || (reinterpret_cast<uintptr_t>(residual) & 15))) return ub::fail(UB_ERR_INVALID_ARG);
+  const size_t n_out = static_cast<size_t>(M) * N;
+  auto add_residual = [&]() -> int {
+    if (!residual) return UB_OK;
+    size_t blocks = (n_out + 255) / 256;
+    const size_t cap = static_cast<size_t>(ub::num_sms()) * 8;
+    add_bf16_kernel<<<static_cast<unsigned>(blocks > cap ? cap : blocks), 256, 0, ub::as_stream(stream)>>>(
+        static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(residual), n_out);
+    return ub::check_launch();
+  };
+  if (world <= 1) {
+    if (M == 1 && residual && !(reinterpret_cast<uintptr_t>(x) & 15)) {
+      ub::ArParams ar;
+      memset(&ar, 0, sizeof(ar));
+      ar.residual = static_cast<const __nv_bfloat16*>(residual);
+      const ub::M1Extras ex = {nullptr, 0.f, &ar};
+      const int st = ub::q4k_gemv_m1x<__nv_bfloat16>(wq, static_cast<const __nv_bfloat16*>(x), y, N, K, UB_DTYPE_BF16,
+                                                     ub::take_weights_written(ub::as_stream(stream)), ex,
+                                                     ub::as_stream(stream));
+      if (st != UB_ERR_UNSUPPORTED) return st;
+    }
+    const int st = qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, UB_DTYPE_BF16, nullptr, 0, stream);
+    return st != UB_OK ? st : add_residual();
+  }
   if (!staging || world > ub::kArMaxWorld || rank < 0 || rank >= world || (max_bytes & 15))
     return ub::fail(UB_ERR_INVALID_ARG);
   const size_t count = static_cast<size_t>(M) * N;
@@ -238,15 +356,17 @@ int ub_qmatmul_q4k_allreduce_bf16(void* y, const void* x, const void* wq, int M,
       if (!ar.base[p] || (reinterpret_cast<uintptr_t>(ar.base[p]) & 15)) return ub::fail(UB_ERR_INVALID_ARG);
     }
     ar.rank = rank, ar.world = world, ar.max_bytes = max_bytes;
+    ar.residual = static_cast<const __nv_bfloat16*>(residual);
     ar.spin_limit = ub::oneshot_spin_limit();
     const bool fresh = ub::take_weights_written(s);
     const int st = ub::qgemv_ar<__nv_bfloat16>(true, y, static_cast<const __nv_bfloat16*>(x), wq, 1, N, K, UB_DTYPE_BF16,
                                                fresh, &ar, s);
     if (st != UB_ERR_UNSUPPORTED) return st;
   }
-  const int st = qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, UB_DTYPE_BF16, nullptr, 0, stream);
+  int st = qmatmul(true, UB_DTYPE_BF16, y, x, wq, M, N, K, UB_DTYPE_BF16, nullptr, 0, stream);
   if (st != UB_OK) return st;
-  return ub_allreduce_oneshot_bf16(y, count, staging, rank, world, max_bytes, stream);
+  st = ub_allreduce_oneshot_bf16(y, count, staging, rank, world, max_bytes, stream);
+  return st != UB_OK ? st : add_residual();
 }
 
 // ub_qmatmul_q4k_f32 for callers that have no way to hand over a workspace: the type-conversion

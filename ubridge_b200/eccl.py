@@ -197,13 +197,13 @@ class OneShotAllReduce:
                                                    _p(stream if stream is not None else self.dev.stream)),
                    "ub_allreduce_oneshot_bf16")
 
-    def matmul_all_reduce(self, y, x, wq, M: int, N: int, K: int, stream=None) -> None:
-        """y[M, N] (bf16) = sum over the ranks of x_r[M, K] . W_r^T for a row-split Q4_K matrix, through
-        ``ub_qmatmul_q4k_allreduce_bf16``: with one token the exchange is the matmul kernel's own epilogue."""
-        _lib.check(lib().ub_qmatmul_q4k_allreduce_bf16(_p(y), _p(x), _p(wq), M, N, K, self._table, self.rank, self.world,
-                                                       self.max_bytes,
-                                                       _p(stream if stream is not None else self.dev.stream)),
-                   "ub_qmatmul_q4k_allreduce_bf16")
+    def matmul_all_reduce(self, y, x, wq, M: int, N: int, K: int, stream=None, residual=None) -> None:
+        """y[M, N] (bf16) = [residual +] sum over the ranks of x_r[M, K] . W_r^T for a row-split Q4_K matrix,
+        through ``ub_qmatmul_q4k_allreduce_residual_bf16``: with one token the exchange (and the residual add) is
+        the matmul kernel's own epilogue."""
+        _lib.check(lib().ub_qmatmul_q4k_allreduce_residual_bf16(
+            _p(y), _p(x), _p(wq), _p(residual), M, N, K, self._table, self.rank, self.world, self.max_bytes,
+            _p(stream if stream is not None else self.dev.stream)), "ub_qmatmul_q4k_allreduce_residual_bf16")
 
     def close(self) -> None:
         """Call after a barrier: no peer may still be pushing into this rank's buffer."""

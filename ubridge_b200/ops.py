@@ -109,6 +109,23 @@ def qmatmul_q4k_gate_up(y, x, wq, M: int, I: int, K: int, *, out_dtype: int, wor
                                             _s(stream)), "ub_qmatmul_q4k_gate_up_bf16")
 
 
+def rms_norm(out, inp, gamma, num_tokens: int, hidden_size: int, eps: float, dtype: int, stream=None) -> None:
+    """out[t,:] = rmsnorm(inp[t,:]) * gamma (the reference's topsaten_rms_norm, src/ffi.rs:719-728)."""
+    check(lib().topsaten_rms_norm(_p(out), _p(inp), _p(gamma), num_tokens, hidden_size, eps, dtype, _s(stream)),
+          "topsaten_rms_norm")
+
+
+def qmatmul_q4k_rmsnorm_workspace_bytes(M: int, N: int, K: int, gate_up: bool) -> int:
+    return lib().ub_qmatmul_q4k_rmsnorm_workspace_bytes(M, N, K, int(gate_up))
+
+
+def qmatmul_q4k_rmsnorm(y, x, gamma, eps: float, wq, M: int, N: int, K: int, *, gate_up: bool = False, out_dtype: int,
+                        workspace=None, ws_bytes: int = 0, stream=None) -> None:
+    """Q4_K matmul (or gate/up + SiLU.up when gate_up) on rmsnorm(x; gamma, eps); one launch for one token."""
+    check(lib().ub_qmatmul_q4k_rmsnorm_bf16(_p(y), _p(x), _p(gamma), eps, _p(wq), M, N, K, int(gate_up), out_dtype,
+                                            _p(workspace), ws_bytes, _s(stream)), "ub_qmatmul_q4k_rmsnorm_bf16")
+
+
 def qmatmul_q4k_f32_static(y, x, wq, M: int, N: int, K: int, out_dtype: int, stream=None) -> None:
     """Q4_K matmul with f32 activations that takes no workspace and allocates nothing: its scratch is a
     fixed 8 MiB array inside the library (so roughly M*(K+N) <= 4M elements, else UB_ERR_TOO_LARGE).
