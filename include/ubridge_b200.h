@@ -33,7 +33,8 @@ enum {
   UB_ERR_BAD_INDEX = 5,     /* device saw an expert id / slot outside its range      */
   UB_ERR_TIMEOUT = 6,       /* a bounded device-side wait ran out                    */
   UB_ERR_NCCL = 7,          /* NCCL missing or a collective call failed              */
-  UB_ERR_TOO_LARGE = 8      /* size beyond a fixed limit of the entry point          */
+  UB_ERR_TOO_LARGE = 8,     /* size beyond a fixed limit of the entry point          */
+  UB_ERR_NOT_READY = 9      /* ub_stream_query: work is still pending on the stream  */
 };
 
 /* element type codes: the reference's DATATYPE enum, src/lib.rs:87-106 (kernels/utils/utils.h:31-49) */
@@ -89,6 +90,10 @@ int ub_memcpy_dtod(ub_device* dev, void* dst, const void* src, size_t bytes);   
 /* strided rows: `height` rows of `width_bytes`, source/destination pitches in bytes */
 int ub_memcpy_dtod_2d(ub_device* dev, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t height); /* gcu_device.rs:422-498 */
 int ub_synchronize(ub_device* dev);                                /* gcu_device.rs:610-618 */
+/* Non-blocking: UB_OK once everything enqueued on `stream` has completed, UB_ERR_NOT_READY while work is
+ * pending.  What a host polls against a deadline instead of blocking in ub_synchronize when a peer rank may
+ * have gone away (no counterpart in the reference, whose synchronize blocks: gcu_device.rs:610-618). */
+int ub_stream_query(void* stream);
 
 /* ------------------------------------------------------------------ name -> launcher registry
  * Mirrors DeviceExecutor.function_map + GcuDevice::get_or_load_func + GcuFunction::launch
@@ -355,6 +360,10 @@ ecclResult_t ecclSend(const void* sendbuff, size_t count, ecclDataType_t datatyp
 ecclResult_t ecclRecv(void* recvbuff, size_t count, ecclDataType_t datatype, int peer, ecclComm_t comm, void* stream);                                                 /* eccllib.rs:150-161 */
 ecclResult_t ecclGroupStart(void);                                                                      /* eccllib.rs:167-169 */
 ecclResult_t ecclGroupEnd(void);                                                                        /* eccllib.rs:163-165 */
+/* Asynchronous error state of a communicator (ncclCommGetAsyncError): *async_error = ecclSuccess while all is
+ * well.  Not part of eccllib.rs; together with ub_stream_query it lets the host bound a collective by a deadline
+ * and call ecclCommAbort (what the reference's Drop does, src/eccl.rs:63-70) instead of blocking for ever. */
+ecclResult_t ub_eccl_comm_async_error(ecclComm_t comm, ecclResult_t* async_error);
 
 #ifdef __cplusplus
 }

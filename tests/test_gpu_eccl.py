@@ -29,6 +29,10 @@ def test_single_rank_collectives(dev):
     comm.all_gather(d_x, d_y, x.size, eccl.Float32, stream=dev.stream)
     assert np.array_equal(dev.dtoh_sync_copy(d_y, np.float32), x)
     comm.broadcast(d_x, d_y, x.size, eccl.Float32, 0, stream=dev.stream)
+    # the host's deadline-bounded wait: polls the stream and the communicator's asynchronous error state
+    comm.wait(dev.stream, 10.0)
+    assert comm.async_error() == 0
+    assert ub.lib().ub_stream_query(dev.stream) == 0  # drained
     dev.synchronize()
     comm.destroy()
 

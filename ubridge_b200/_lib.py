@@ -21,6 +21,7 @@ UB_ERR_BAD_INDEX = 5
 UB_ERR_TIMEOUT = 6
 UB_ERR_NCCL = 7
 UB_ERR_TOO_LARGE = 8
+UB_ERR_NOT_READY = 9
 
 # element type codes (the reference's DATATYPE enum, src/lib.rs:87-106)
 DTYPE_I8, DTYPE_U8, DTYPE_F16, DTYPE_BF16, DTYPE_I32, DTYPE_F32 = 0, 1, 4, 5, 6, 8
@@ -84,6 +85,7 @@ _SIGS = {
     "ub_allreduce_oneshot_bf16": (c_int, [_P, c_size_t, ctypes.POINTER(_P), c_int, c_int, c_size_t, _P]),
     "ub_allreduce_oneshot_set_spin_limit": (ctypes.c_uint, [ctypes.c_uint]),
     "ub_synchronize": (c_int, [_P]),
+    "ub_stream_query": (c_int, [_P]),
     "ub_get_function": (_P, [c_char_p, c_char_p]),
     "ub_has_function": (c_int, [c_char_p, c_char_p]),
     "ub_function_count": (c_int, []),
@@ -160,6 +162,7 @@ _SIGS = {
     "ecclRecv": (c_int, [_P, c_size_t, c_int, c_int, _P, _P]),
     "ecclGroupStart": (c_int, []),
     "ecclGroupEnd": (c_int, []),
+    "ub_eccl_comm_async_error": (c_int, [_P, POINTER(c_int)]),
 }
 
 EXPORTED_SYMBOLS = tuple(sorted(_SIGS))

@@ -37,6 +37,7 @@ struct Nccl {
   int (*Recv)(void*, size_t, int, int, ecclComm_t, cudaStream_t) = nullptr;
   int (*GroupStart)() = nullptr;
   int (*GroupEnd)() = nullptr;
+  int (*CommGetAsyncError)(ecclComm_t, int*) = nullptr;  // optional
 };
 
 Nccl g_nccl;
@@ -67,6 +68,7 @@ Nccl* nccl() {
                 sym(h, "ncclReduceScatter", g_nccl.ReduceScatter) && sym(h, "ncclAllGather", g_nccl.AllGather) &&
                 sym(h, "ncclSend", g_nccl.Send) && sym(h, "ncclRecv", g_nccl.Recv) &&
                 sym(h, "ncclGroupStart", g_nccl.GroupStart) && sym(h, "ncclGroupEnd", g_nccl.GroupEnd);
+      sym(h, "ncclCommGetAsyncError", g_nccl.CommGetAsyncError);
       if (ok)
         g_nccl.handle = h;
       else
@@ -168,6 +170,14 @@ ecclResult_t ecclGroupStart(void) {
 ecclResult_t ecclGroupEnd(void) {
   UB_NCCL_OR_FAIL();
   return done(n->GroupEnd());
+}
+ecclResult_t ub_eccl_comm_async_error(ecclComm_t comm, ecclResult_t* async_error) {
+  UB_NCCL_OR_FAIL();
+  if (!async_error || !n->CommGetAsyncError) return done(ecclInvalidArgument);
+  int st = 0;
+  const int rc = n->CommGetAsyncError(comm, &st);
+  *async_error = static_cast<ecclResult_t>(st);
+  return done(rc);
 }
 
 }  // extern "C"

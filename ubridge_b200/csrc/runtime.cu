@@ -224,4 +224,15 @@ int ub_synchronize(ub_device* dev) {
   return ub::fail(UB_OK);
 }
 
+int ub_stream_query(void* stream) {
+  const cudaError_t e = cudaStreamQuery(ub::as_stream(stream));
+  if (e == cudaSuccess) return ub::fail(UB_OK);
+  if (e == cudaErrorNotReady) {
+    cudaGetLastError();  // not an error: clear it
+    return ub::fail(UB_ERR_NOT_READY);
+  }
+  ub::set_cuda_error(e);
+  return ub::fail(UB_ERR_CUDA);
+}
+
 }  // extern "C"

@@ -7,6 +7,7 @@ device's single stream in the reference, src/eccl.rs:209-413).
 from __future__ import annotations
 
 import ctypes
+import time
 
 from . import _lib
 from ._lib import EcclUniqueId, lib
@@ -16,6 +17,14 @@ class EcclError(RuntimeError):
     def __init__(self, code: int, what: str):
         super().__init__("eccl: %s failed with result %d" % (what, code))
         self.code = code
+
+
+class EcclTimeout(EcclError):
+    """A collective did not complete within the host's deadline; the communicator has been aborted."""
+
+    def __init__(self, what: str, seconds: float):
+        RuntimeError.__init__(self, "eccl: %s did not complete within %.3f s; communicator aborted" % (what, seconds))
+        self.code = 6  # UB_ERR_TIMEOUT
 
 
 class ReduceOp:
@@ -137,6 +146,38 @@ class Comm:
 
     def recv(self, buf, count: int, dtype: int, peer: int, stream=None) -> None:
         _ok(lib().ecclRecv(_p(buf), count, dtype, peer, self._comm, _p(stream)), "ecclRecv")
+
+    def async_error(self) -> int:
+        """ncclCommGetAsyncError: 0 while the communicator is healthy."""
+        v = ctypes.c_int()
+        _ok(lib().ub_eccl_comm_async_error(self._comm, ctypes.byref(v)), "ub_eccl_comm_async_error")
+        return v.value
+
+    def wait(self, stream, timeout_s: float, poll_s: float = 0.0005, what: str = "collective", query=None,
+             clock=time.monotonic, sleep=time.sleep) -> None:
+        """Bound the work enqueued on `stream` (collectives of this communicator among it) by a host deadline:
+        poll the stream and the communicator's asynchronous error state; on an error or on expiry abort the
+        communicator (what the reference's Drop does, src/eccl.rs:63-70) and raise, so that the caller is never
+        left blocking on a peer that has gone away.  `query` returns UB_OK / UB_ERR_NOT_READY / an error code
+        (default: ub_stream_query on `stream`)."""
+        if query is None:
+            query = lambda: lib().ub_stream_query(_p(stream))  # noqa: E731
+        deadline = clock() + timeout_s
+        while True:
+            st = query()
+            if st == _lib.UB_OK:
+                return
+            if st != _lib.UB_ERR_NOT_READY:
+                self.abort()
+                raise EcclError(st, what + " (stream)")
+            err = self.async_error()
+            if err not in (0, 7):  # ecclSuccess, ecclInProgress
+                self.abort()
+                raise EcclError(err, what + " (asynchronous error)")
+            if clock() >= deadline:
+                self.abort()
+                raise EcclTimeout(what, timeout_s)
+            sleep(poll_s)
 
     def destroy(self) -> None:
         if self._comm:
