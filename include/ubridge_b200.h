@@ -85,6 +85,8 @@ int ub_alloc(ub_device* dev, size_t bytes, void** out);            /* gcu_device
 int ub_alloc_zeros(ub_device* dev, size_t bytes, void** out);      /* gcu_device.rs:262-324 */
 int ub_free(ub_device* dev, void* ptr);                            /* gcu_slice.rs:62-101 (stream-ordered free) */
 int ub_memcpy_htod(ub_device* dev, void* dst, const void* host_src, size_t bytes); /* gcu_device.rs:337-420 */
+/* Enqueues the copy on the device's stream and returns: the host bytes are valid only after ub_synchronize
+ * (the reference's dtoh_sync_copy synchronises itself; the Python mirror's dtoh_sync_copy does the same). */
 int ub_memcpy_dtoh(ub_device* dev, void* host_dst, const void* src, size_t bytes); /* gcu_device.rs:500-588 */
 int ub_memcpy_dtod(ub_device* dev, void* dst, const void* src, size_t bytes);      /* gcu_device.rs:422-498 */
 /* strided rows: `height` rows of `width_bytes`, source/destination pitches in bytes */
@@ -206,7 +208,9 @@ int ub_qmatmul_q4k_bf16(void* y, const void* x, const void* wq, int M, int N, in
  * process exits); the call allocates nothing.  Limit: ub_qmatmul_workspace_bytes(M,N,K,1) <= 8 MiB,
  * i.e. about M*(K+N) <= 4M elements; beyond it the call returns UB_ERR_TOO_LARGE.  The first call on a
  * device looks up the array's address and should come before any stream capture.  Calls share the
- * array: do not let two of them overlap on one GPU. */
+ * array: do not let two of them overlap on one GPU.  The array used is the one of the CURRENT device of the
+ * calling thread, which must be the device `stream` belongs to (device ordinals up to 63; UB_ERR_INVALID_ARG
+ * beyond). */
 int ub_qmatmul_q4k_f32_static(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* stream);
 
 /* ------------------------------------------------------------------ GGUF tensor blobs

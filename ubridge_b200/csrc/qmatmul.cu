@@ -160,10 +160,11 @@ void* g_static_ptr[64] = {nullptr};
 int static_scratch(void** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+  if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
   }
+  if (dev < 0 || dev >= 64) return ub::fail(UB_ERR_INVALID_ARG);  // more devices than the address table holds
   std::lock_guard<std::mutex> lk(g_static_mu);
   if (!g_static_ptr[dev]) {
     void* p = nullptr;

@@ -145,7 +145,10 @@ int ub_device_new(int ordinal, ub_device** out) {
   cudaStream_t s = nullptr;
   UB_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
   ub_device* d = new (std::nothrow) ub_device{ordinal, s};
-  if (!d) return ub::fail(UB_ERR_INVALID_ARG);
+  if (!d) {
+    cudaStreamDestroy(s);
+    return ub::fail(UB_ERR_CUDA);
+  }
   *out = d;
   return ub::fail(UB_OK);
 }
