@@ -252,6 +252,8 @@ WORKLOADS = {
                desc="Q4_K 14336x4096 prefill GEMM, M=2048"),
     "c3_m1024": dict(N=14336, K=4096, M=1024, is_q4k=True, x_bf16=True, unit="TFLOP/s", seed=1002, copies=2,
                      cpu_rows=64, desc="Q4_K 14336x4096 prefill GEMM, M=1024 (the small case profiled under ncu)"),
+    "c1_m512": dict(N=4096, K=4096, M=512, is_q4k=False, x_bf16=True, unit="TFLOP/s", seed=1001, copies=8, cpu_rows=64,
+                    desc="Q8_0 4096x4096 prefill GEMM, M=512"),
     # sharded workloads.  N, K, M, cpu_rows describe the matrix the CPU arm samples (one expert's gate
     # projection; a quarter of the gate projection of the 70B-shaped MLP).
     "c4": dict(kind="ep", T=256, H=4096, I=14336, E=8, top_k=2, block=64, unit="tok/s", seed=1004, is_q4k=True,
@@ -369,7 +371,10 @@ def run_linear(wl_name, wl, steps, warmup, min_seconds, rank, world, torch, with
         # decode kernel: up to eight rows per pass; bf16 in and out from nine rows on: one tensor-core launch
         launches_per_call = 1 if M > 16 or (M > 8 and wl["x_bf16"]) else (M + 7) // 8
     elif fmt == "Q8_0":
-        launches_per_call = (M + 7) // 8 if K % 2048 == 0 else decode_launches(M)
+        if M > 16 and K % 256 == 0:
+            launches_per_call = 1  # tensor-core kernel (bf16 in and out here: no conversion launches)
+        else:
+            launches_per_call = (M + 7) // 8 if K % 2048 == 0 else decode_launches(M)
     else:
         launches_per_call = decode_launches(M)
     calls_per_step = k * copies * passes

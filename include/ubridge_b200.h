@@ -96,6 +96,9 @@ int ub_synchronize(ub_device* dev);                                /* gcu_device
  * pending.  What a host polls against a deadline instead of blocking in ub_synchronize when a peer rank may
  * have gone away (no counterpart in the reference, whose synchronize blocks: gcu_device.rs:610-618). */
 int ub_stream_query(void* stream);
+/* Free and total bytes of the device's memory (the mem_get_info the reference's own allocation test reads,
+ * src/gcu_device.rs:708-718). */
+int ub_mem_info(ub_device* dev, size_t* free_bytes, size_t* total_bytes);
 
 /* ------------------------------------------------------------------ name -> launcher registry
  * Mirrors DeviceExecutor.function_map + GcuDevice::get_or_load_func + GcuFunction::launch
@@ -165,8 +168,10 @@ int ub_qmatmul_q6k_bf16(void* y, const void* x, const void* wq, int M, int N, in
  * kernels/third_party/matmul_decoding.h:12-570).  The suffix names the activation type;
  * out_dtype is UB_DTYPE_F32 / UB_DTYPE_BF16 / UB_DTYPE_F16.  M <= 16 runs the
  * bandwidth-bound decode kernel (Q4_K with bf16 activations and bf16 output: M <= 8), larger M
- * the tensor-core kernel (Q4_K) — see ub_qmatmul_workspace_bytes for the scratch each needs
- * (0 whenever M <= 16).
+ * the tensor-core kernel — see ub_qmatmul_workspace_bytes for the scratch it needs when the
+ * activation or output type is not bf16 (0 whenever M <= 16).  Q8_0 takes the tensor-core kernel when
+ * K % 256 == 0 and wq is 16-byte aligned; otherwise, or when called without the scratch, it runs the
+ * decode kernel in passes of eight tokens (same result within the matmul tolerance, slower).
  *
  * Precondition on the weights.  The decode kernels (M <= 16) are launched with programmatic dependent launch
  * and request their first weight tiles BEFORE they wait for the kernel in front of them on the stream.  The

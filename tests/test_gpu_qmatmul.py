@@ -112,13 +112,57 @@ def test_q4k_general_m(dev, M):
     assert o.rel_l2(got32, want) < TOL_TENSOR
 
 
-def test_q8_0_general_m(dev):
-    rng = np.random.default_rng(400)
-    M, N, K = 40, 96, 512
+def _bf16_weights_product(x, w, N, K):
+    """x . W^T with the dequantised Q8_0 weights rounded to bf16 first: what the tensor-core kernel multiplies."""
+    wd = o.round_through(o.c_dequant(w, False).reshape(N, K), o.UB_BF16)
+    return x.astype(np.float64) @ wd.astype(np.float64).T
+
+
+@pytest.mark.parametrize("M", [17, 64, 65, 130, 300])
+def test_q8_0_general_m(dev, M):
+    """Q8_0 with more than 16 tokens: the tcgen05 kernel with the Q8_0 producer (K % 256 == 0, aligned weights)."""
+    rng = np.random.default_rng(400 + M)
+    N, K = 264, 1024
+    w = o.gen_q8_0_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    want = o.c_qmatmul(x, w, N, K, False)
+    got = _run(dev, w, x, M, N, K, False, DTYPE_BF16, DTYPE_BF16)
+    assert o.rel_l2(got, want) < TOL_TENSOR
+    # the only differences from the exact product: weights rounded to bf16 once, output rounded to bf16 once
+    assert o.rel_l2(got, _bf16_weights_product(x, w, N, K)) < 3e-3
+    got32 = _run(dev, w, x, M, N, K, False, DTYPE_F32, DTYPE_F16)  # converted through the workspace
+    assert o.rel_l2(got32, want) < TOL_TENSOR
+
+
+def test_q8_0_general_m_without_tensor_core_preconditions(dev):
+    """Rows that are not whole 16-byte pieces, or no workspace for the conversions: the decode kernel in passes."""
+    rng = np.random.default_rng(401)
+    M, N, K = 40, 96, 288
     w = o.gen_q8_0_weight(rng, N, K)
     x = o.gen_activation(rng, M, K, True)
     got = _run(dev, w, x, M, N, K, False, DTYPE_BF16, DTYPE_F32)
     assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, False)) < TOL_DECODE
+    M, N, K = 40, 96, 512
+    w = o.gen_q8_0_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, False)
+    d_w, d_x, d_y = dev.htod_sync_copy(w), dev.htod_sync_copy(x), dev.alloc(M * N * 4)
+    ops.qmatmul(d_y, d_x, d_w, M, N, K, is_q4k=False, x_dtype=DTYPE_F32, out_dtype=DTYPE_F32, stream=dev.stream)
+    assert o.rel_l2(fetch(dev, d_y, DTYPE_F32, (M, N)), o.c_qmatmul(x, w, N, K, False)) < TOL_DECODE
+
+
+def test_q8_0_prefill_full_size(dev):
+    """Q8_0 4096x4096 (the C1 weight) with 512 bf16 tokens."""
+    rng = np.random.default_rng(1001)
+    N = K = 4096
+    M = 512
+    w = o.gen_q8_0_weight(rng, N, K)
+    x = o.gen_activation(np.random.default_rng(1003), M, K, True)
+    got = _run(dev, w, x, M, N, K, False, DTYPE_BF16, DTYPE_BF16)
+    want = x @ o.c_dequant(w, False).reshape(N, K).T
+    assert o.rel_l2(got, want) < TOL_TENSOR
+    assert o.rel_l2(got, want) < 3e-3
+    got2 = _run(dev, w, 2 * x[:64], 64, N, K, False, DTYPE_BF16, DTYPE_BF16)
+    assert np.array_equal(got2, 2 * got[:64])
 
 
 def test_workspace_is_required_when_types_need_conversion(dev):

@@ -89,16 +89,15 @@ def test_static_scratch_entry_at_its_limit(dev):
 def test_static_scratch_entry_leaves_free_memory_unchanged(dev):
     """The property in the entry point's name: after a first call (which may load code lazily), further calls
     change nothing in the device's free memory."""
-    torch = pytest.importorskip("torch")
     rng = np.random.default_rng(7)
     M, N, K = 64, 512, 1024
     w, x = o.gen_q4k_weight(rng, N, K), o.gen_activation(rng, M, K, False)
     d_w, d_x, d_y = dev.htod_sync_copy(w), dev.htod_sync_copy(x), dev.alloc(M * N * 4)
     ops.qmatmul_q4k_f32_static(d_y, d_x, d_w, M, N, K, DTYPE_F32, stream=dev.stream)
     dev.synchronize()
-    free0, _total = torch.cuda.mem_get_info(dev.ordinal)
+    free0, _total = dev.mem_info()
     for _ in range(3):
         ops.qmatmul_q4k_f32_static(d_y, d_x, d_w, M, N, K, DTYPE_F32, stream=dev.stream)
     dev.synchronize()
-    free1, _total = torch.cuda.mem_get_info(dev.ordinal)
+    free1, _total = dev.mem_info()
     assert free1 == free0

@@ -86,6 +86,7 @@ _SIGS = {
     "ub_allreduce_oneshot_set_spin_limit": (ctypes.c_uint, [ctypes.c_uint]),
     "ub_synchronize": (c_int, [_P]),
     "ub_stream_query": (c_int, [_P]),
+    "ub_mem_info": (c_int, [_P, POINTER(c_size_t), POINTER(c_size_t)]),
     "ub_get_function": (_P, [c_char_p, c_char_p]),
     "ub_has_function": (c_int, [c_char_p, c_char_p]),
     "ub_function_count": (c_int, []),

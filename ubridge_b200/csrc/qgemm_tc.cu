@@ -140,6 +140,16 @@ __device__ __forceinline__ uint32_t deq_pair(uint32_t w4, __nv_bfloat162 dsc, __
   return bf162_bits(__hfma2(q, dsc, ndm));
 }
 
+// Two signed bytes A and B of a word (given as its low seven bits and its sign bits) -> packed bf16 (d*qA, d*qB):
+// 0x43 over the low seven bits is bf16 (128 + m), 0x43 over the sign bit is 128 or 256, their difference is q.
+template <int SEL>
+__device__ __forceinline__ uint32_t deq8_pair(uint32_t lo7, uint32_t sg, __nv_bfloat162 dh, __nv_bfloat162 dl) {
+  const uint32_t biased = __byte_perm(lo7, 0x43434343u, SEL), off = __byte_perm(sg, 0x43434343u, SEL);
+  const __nv_bfloat162 q = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&biased),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&off));
+  return bf162_bits(__hfma2(q, dh, __hmul2(q, dl)));
+}
+
 constexpr int kTcMaxStages = 8;
 constexpr int kTcWStages = 8;                        // most slots a ring of packed weight tiles has
 // Shared-memory plan per token-tile size: the 256-token tile spends its memory on token stages (the
@@ -150,7 +160,11 @@ constexpr int tc_wstages(int tok, int ctas, int wst = 0) { return wst ? wst : ((
 constexpr int tc_stage_tok(int tok, int ctas) {  // staging rows
   return (tok > 128 || ctas > 1) ? 64 : (tok < 128 ? tok : 128);
 }
-constexpr uint32_t kTcWBytes = 128 * UB_Q4K_BYTES;   // 128 rows x 144 bytes
+// One slot of the packed-weight ring holds 256 K values of 128 rows: a Q4_K super-block (144 bytes) or eight
+// Q8_0 blocks (272 bytes, the shortest run of 34-byte blocks that is a whole number of 16-byte pieces).
+constexpr uint32_t kTcQ8RowBytes = 8 * 34;
+constexpr uint32_t tc_wrow(int fmt) { return fmt ? kTcQ8RowBytes : UB_Q4K_BYTES; }
+constexpr uint32_t tc_wbytes(int fmt) { return 128 * tc_wrow(fmt); }
 
 constexpr int kTcMaxRuns = 256;  // token runs (consecutive alignment blocks of one expert) a grouped launch handles
 
@@ -186,7 +200,8 @@ struct TcShared {
 // WST: slots of the packed-weight ring (0: the default of tc_wstages).  Measured on B200: deeper rings do not
 // help (MoE layer of 256 tokens, one CTA per SM: 3 -> 5 slots 589 -> 567 us; dense M = 2048: 2 -> 4 slots no
 // change), the packed tiles are not what a K step waits for.
-template <int TOK, int STAGES, int MODE, int CTAS, int WST>
+// FMT: 0 = Q4_K super-blocks, 1 = Q8_0 blocks (dense mode only).
+template <int TOK, int STAGES, int MODE, int CTAS, int WST, int FMT>
 __global__ void __launch_bounds__(kTcThreads, CTAS)
 qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err_word,
                     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
@@ -201,6 +216,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   constexpr int kStageTok = tc_stage_tok(TOK, CTAS);   // tokens the output staging tile holds
   constexpr int kWStages = tc_wstages(TOK, CTAS, WST);
   static_assert(kWStages <= kTcWStages, "barrier arrays");
+  static_assert(FMT == 0 || MODE == 0, "the grouped modes take Q4_K experts");
+  constexpr uint32_t kTcWBytes = tc_wbytes(FMT);
+  constexpr uint32_t kWRow = tc_wrow(FMT);
   constexpr uint32_t kStagingOff = STAGES * kBBytes;   // [kStageTok tokens][128 weight rows] bf16
   constexpr uint32_t kWOff = kStagingOff + kStageTok * 256;  // packed weight ring: [128 rows][144 bytes] each
   constexpr int kAccBufs = (TOK > 128 || CTAS > 1) ? 1 : 2;  // accumulator buffers at the start of the allocation
@@ -450,7 +468,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     const int nsb = K >> 8;
     const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const int total_sb = my_tiles * nsb;  // super-block iterations
-    const unsigned char* const w_ring = tiles + kWOff + wrow * UB_Q4K_BYTES;
+    const unsigned char* const w_ring = tiles + kWOff + wrow * kWRow;
     const uint32_t a_lane = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kATmemCol;
 
     int s = set;  // stage of the step being dequantised
@@ -466,30 +484,54 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
       ok = __all_sync(0xFFFFFFFFu, tc_wait(wfull_bar(ws), wphase, abort_flag));
       if (!ok) return;
       const unsigned char* blk = w_ring + ws * kTcWBytes;
-      const uint4 hdr = *reinterpret_cast<const uint4*>(blk);  // rows past N arrive as zeros: d = dmin = 0
-      const float d = half_bits_to_f32(hdr.x), dmin = half_bits_to_f32(hdr.x >> 16);
-      uint32_t scw[2], mnw[2];
-      q4k_unpack_scales(hdr.y, hdr.z, hdr.w, scw[0], scw[1], mnw[0], mnw[1]);
+      uint32_t scw[2] = {0, 0}, mnw[2] = {0, 0};
+      float d = 0.f, dmin = 0.f;
+      if (FMT == 0) {
+        const uint4 hdr = *reinterpret_cast<const uint4*>(blk);  // rows past N arrive as zeros: d = dmin = 0
+        d = half_bits_to_f32(hdr.x), dmin = half_bits_to_f32(hdr.x >> 16);
+        q4k_unpack_scales(hdr.y, hdr.z, hdr.w, scw[0], scw[1], mnw[0], mnw[1]);
+      }
 #pragma unroll
       for (int Gi = 0; Gi < 4 / kTcProducerSets; Gi++) {
         constexpr int kSets = kTcProducerSets;
         const int G = kSets * Gi + SET;
-        const int j = 2 * G + HALF;
-        const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
-        const __nv_bfloat162 dsc = __float2bfloat162_rn(d * static_cast<float>(sc));
-        const __nv_bfloat162 ndm = __float2bfloat162_rn(-dmin * static_cast<float>(mn));
-        const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * G);
-        const uint4 qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * G);
-        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
         uint32_t ot[16];  // this thread's 32 values of the step = 16 TMEM columns of packed pairs
+        if (FMT == 0) {
+          const int j = 2 * G + HALF;
+          const uint32_t sc = (scw[j >> 2] >> (8 * (j & 3))) & 0xFF, mn = (mnw[j >> 2] >> (8 * (j & 3))) & 0xFF;
+          const __nv_bfloat162 dsc = __float2bfloat162_rn(d * static_cast<float>(sc));
+          const __nv_bfloat162 ndm = __float2bfloat162_rn(-dmin * static_cast<float>(mn));
+          const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * G);
+          const uint4 qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * G);
+          const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
-        for (int cc = 0; cc < 4; cc++) {  // 8 values = bytes 8cc .. 8cc+7
-          const uint32_t w0 = HALF ? (w[2 * cc] >> 4) & 0x0F0F0F0Fu : w[2 * cc] & 0x0F0F0F0Fu;
-          const uint32_t w1 = HALF ? (w[2 * cc + 1] >> 4) & 0x0F0F0F0Fu : w[2 * cc + 1] & 0x0F0F0F0Fu;
-          ot[4 * cc] = deq_pair<0x4140>(w0, dsc, ndm);
-          ot[4 * cc + 1] = deq_pair<0x4342>(w0, dsc, ndm);
-          ot[4 * cc + 2] = deq_pair<0x4140>(w1, dsc, ndm);
-          ot[4 * cc + 3] = deq_pair<0x4342>(w1, dsc, ndm);
+          for (int cc = 0; cc < 4; cc++) {  // 8 values = bytes 8cc .. 8cc+7
+            const uint32_t w0 = HALF ? (w[2 * cc] >> 4) & 0x0F0F0F0Fu : w[2 * cc] & 0x0F0F0F0Fu;
+            const uint32_t w1 = HALF ? (w[2 * cc + 1] >> 4) & 0x0F0F0F0Fu : w[2 * cc + 1] & 0x0F0F0F0Fu;
+            ot[4 * cc] = deq_pair<0x4140>(w0, dsc, ndm);
+            ot[4 * cc + 1] = deq_pair<0x4342>(w0, dsc, ndm);
+            ot[4 * cc + 2] = deq_pair<0x4140>(w1, dsc, ndm);
+            ot[4 * cc + 3] = deq_pair<0x4342>(w1, dsc, ndm);
+          }
+        } else {
+          // Q8_0 block 2G + HALF of the row's eight: 34 bytes at byte 34 (2G + HALF) of a 272-byte row, i.e. three
+          // aligned 16-byte pieces from piece (34 (2G + HALF)) / 16; inside them the f16 scale sits at byte
+          // 4G + 2 HALF and the 32 signed bytes follow it, so the even blocks' words straddle two loaded words.
+          const uint4* pc = reinterpret_cast<const uint4*>(blk) + ((34 * (2 * G + HALF)) >> 4);
+          const uint4 p0 = pc[0], p1 = pc[1], p2 = pc[2];
+          const uint32_t c[12] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w, p2.x, p2.y, p2.z, p2.w};
+          const float df = half_bits_to_f32(HALF ? c[G] >> 16 : c[G]);
+          const __nv_bfloat16 dh1 = __float2bfloat16_rn(df);
+          // d = dh + dl in two bf16 pieces: fma(q, dh, q * dl) is the f32 product d * q rounded once
+          const __nv_bfloat162 dh = __bfloat162bfloat162(dh1);
+          const __nv_bfloat162 dl = __float2bfloat162_rn(df - __bfloat162float(dh1));
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const uint32_t w = HALF ? c[G + 1 + i] : __funnelshift_r(c[G + i], c[G + i + 1], 16);
+            const uint32_t lo7 = w & 0x7F7F7F7Fu, sg = w & 0x80808080u;
+            ot[2 * i] = deq8_pair<0x4140>(lo7, sg, dh, dl);
+            ot[2 * i + 1] = deq8_pair<0x4342>(lo7, sg, dh, dl);
+          }
         }
         // the MMAs that read this weight stage one ring turn ago must have completed
         ok = __all_sync(0xFFFFFFFFu, tc_wait(empty_bar(s), phase ^ 1, abort_flag));
@@ -552,13 +594,13 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
                 "r"(smem_base + kWOff + ws * kTcWBytes),
-            "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * UB_Q4K_BYTES), "r"(wrow0)
+            "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * (FMT ? kWRow / 2 : kWRow)), "r"(wrow0)
             : "memory");
         if (MODE == 1)  // second half of the tile: the up rows matching the 64 gate rows (box = 64 rows)
           asm volatile(
               "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
                   "r"(smem_base + kWOff + ws * kTcWBytes + kTcWBytes / 2),
-              "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * UB_Q4K_BYTES), "r"(wrow0 + N)
+              "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(bar), "r"(sb * kWRow), "r"(wrow0 + N)
               : "memory");
         wq_next++;
         if (++ws == kWStages) {
@@ -622,11 +664,12 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int TOK, int STAGES, int MODE, int CTAS = 1, int WST = 0>
+template <int TOK, int STAGES, int MODE, int CTAS = 1, int WST = 0, int FMT = 0>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const TcGroup& grp, int w_rows_total,
               cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(tc_stage_tok(TOK, CTAS)) * 256 +
-                      static_cast<size_t>(tc_wstages(TOK, CTAS, WST)) * kTcWBytes + 1024;
+  constexpr size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(tc_stage_tok(TOK, CTAS)) * 256 +
+                          static_cast<size_t>(tc_wstages(TOK, CTAS, WST)) * tc_wbytes(FMT) + 1024;
+  static_assert(smem <= 227 * 1024, "shared memory plan");
   const int sms = ub::num_sms();
   int grid = sms * CTAS;  // grouped launches learn their tile count on the device; idle CTAs leave at once
   if (MODE == 0) {
@@ -648,17 +691,19 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const
     return ub::fail(UB_ERR_UNSUPPORTED);
   // packed weights as a 2-D byte tensor: inner dimension = one row's bytes, outer = all weight rows (of all
   // experts); box = one super-block (144 bytes) of 128 rows (64 for the gate/up halves of mode 1), no
-  // swizzle; rows beyond the tensor read as zeros
+  // swizzle; rows beyond the tensor read as zeros.  Q8_0: a box of eight blocks is 272 bytes, wider than the
+  // 256 elements a box may have, so that map counts 16-bit elements (136 per box).
   CUtensorMap wmap;
-  const cuuint64_t row_bytes = static_cast<cuuint64_t>(K / UB_QK_K) * UB_Q4K_BYTES;
-  const cuuint64_t wdims[2] = {row_bytes, static_cast<cuuint64_t>(w_rows_total)};
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(K / UB_QK_K) * tc_wrow(FMT);
+  const cuuint64_t wdims[2] = {FMT ? row_bytes / 2 : row_bytes, static_cast<cuuint64_t>(w_rows_total)};
   const cuuint64_t wstrides[1] = {row_bytes};
-  const cuuint32_t wbox[2] = {UB_Q4K_BYTES, MODE == 1 ? 64u : 128u};
-  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(wq), wdims, wstrides, wbox, estr,
+  const cuuint32_t wbox[2] = {FMT ? tc_wrow(FMT) / 2 : tc_wrow(FMT), MODE == 1 ? 64u : 128u};
+  if (enc(&wmap, FMT ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(wq), wdims,
+          wstrides, wbox, estr,
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ub::fail(UB_ERR_UNSUPPORTED);
-  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS, WST>;
+  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS, WST, FMT>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
@@ -699,6 +744,19 @@ int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cud
   if (M <= 64) return launch_tc<64, 6, 0>(y, x, wq, M, N, K, none, N, s);
   if (M <= 128) return launch_tc<128, 6, 0>(y, x, wq, M, N, K, none, N, s);
   return launch_tc<256, 5, 0>(y, x, wq, M, N, K, none, N, s);
+}
+
+// Same product for Q8_0 rows (K/32 blocks of 34 bytes); K % 256 == 0 (a row must be whole 16-byte pieces) and wq
+// 16-byte aligned, else UB_ERR_UNSUPPORTED and the caller keeps the decode kernel.  The 272-byte slots of the
+// packed ring leave room for four token stages at 256 tokens.  Measured on B200, 4096x4096 with 512 tokens
+// (64 tiles of 256 tokens on 148 SMs): 505 TFLOP/s; with 128-token tiles (128 tiles) 400: the producers'
+// work per flop doubles, which costs more than the idle SMs.
+int q8_0_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
+  if (K % UB_QK_K || (reinterpret_cast<uintptr_t>(wq) & 15)) return UB_ERR_UNSUPPORTED;
+  const TcGroup none = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
+  if (M <= 64) return launch_tc<64, 6, 0, 1, 0, 1>(y, x, wq, M, N, K, none, N, s);
+  if (M <= 128) return launch_tc<128, 6, 0, 1, 2, 1>(y, x, wq, M, N, K, none, N, s);
+  return launch_tc<256, 4, 0, 1, 0, 1>(y, x, wq, M, N, K, none, N, s);
 }
 
 // Limits of the grouped tcgen05 path; outside them the caller keeps the mma.sync kernels.

@@ -8,7 +8,8 @@
 //                     instead (one pass of it is faster than two passes of eight tokens; no workspace either);
 //   M  > 16, Q4_K     tcgen05 tensor-core GEMM with in-kernel dequantisation (bf16 activations and output;
 //                     other types are converted through the caller's workspace);
-//   M  > 16, Q8_0     the decode kernel in passes of four rows.
+//   M  > 16, Q8_0     the same tensor-core kernel with a Q8_0 producer (K % 256 == 0, 16-byte aligned weights,
+//                     workspace as for Q4_K when the types are not bf16); otherwise the decode kernel in passes.
 #include <string.h>
 
 #include <mutex>
@@ -31,7 +32,9 @@ int q4k_gemv_m1x(const void* wq, const XT* x, void* y, int N, int K, int y_dtype
                  cudaStream_t s);
 int q4k_gemm_mma(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
 uint32_t oneshot_spin_limit();
+void* tensor_map_encoder();
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
+int q8_0_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
 }  // namespace ub
 
 namespace {
@@ -111,17 +114,26 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
     const int st = ub::q4k_gemm_tc(y, x, wq, M, N, K, s);
     if (st != UB_ERR_UNSUPPORTED) return st;  // unsupported shape or driver: the decode kernel below
   }
-  if (M <= kDecodeMaxM || !is_q4k) {
+  auto decode = [&]() {
     if (x_dtype == UB_DTYPE_F32)
       return ub::qgemv<float>(is_q4k, y, static_cast<const float*>(x), wq, M, N, K, out_dtype, fresh, s);
     return ub::qgemv<__nv_bfloat16>(is_q4k, y, static_cast<const __nv_bfloat16*>(x), wq, M, N, K, out_dtype, fresh, s);
-  }
+  };
+  if (M <= kDecodeMaxM) return decode();
 
   // tensor-core path: bf16 in, bf16 out; convert around it when the caller's types differ
   const size_t need = ub_qmatmul_workspace_bytes(M, N, K, 1);
   const bool conv_in = x_dtype != UB_DTYPE_BF16, conv_out = out_dtype != UB_DTYPE_BF16;
-  if ((conv_in || conv_out) && (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)))
+  const bool ws_ok = workspace && ws_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 255);
+  if (!is_q4k) {
+    // Q8_0 keeps the decode kernel (passes of eight tokens) where the tensor-core kernel cannot run: rows that are
+    // not whole 16-byte pieces, unaligned weights, or a caller that brought no workspace for the conversions
+    if (K % UB_QK_K || (reinterpret_cast<uintptr_t>(wq) & 15) || ((conv_in || conv_out) && !ws_ok) ||
+        !ub::tensor_map_encoder())
+      return decode();
+  } else if ((conv_in || conv_out) && !ws_ok) {
     return ub::fail(UB_ERR_WORKSPACE);
+  }
   char* ws = static_cast<char*>(workspace);
   const void* xin = x;
   void* yout = y;
@@ -132,9 +144,9 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
     xin = xb;
   }
   if (conv_out) yout = ws + align_up(static_cast<size_t>(M) * K * 2, 256);
-  int st = ub::q4k_gemm_tc(yout, xin, wq, M, N, K, s);
+  int st = is_q4k ? ub::q4k_gemm_tc(yout, xin, wq, M, N, K, s) : ub::q8_0_gemm_tc(yout, xin, wq, M, N, K, s);
   // no tensor-map encoder in this driver: the mma.sync kernel computes the same product
-  if (st == UB_ERR_UNSUPPORTED) st = ub::q4k_gemm_mma(yout, xin, wq, M, N, K, s);
+  if (st == UB_ERR_UNSUPPORTED && is_q4k) st = ub::q4k_gemm_mma(yout, xin, wq, M, N, K, s);
   if (st != UB_OK) return st;
   if (conv_out) {
     const size_t n = static_cast<size_t>(M) * N;
@@ -184,9 +196,11 @@ int static_scratch(void** out) {
 extern "C" {
 
 // Scratch for the tensor-core path when the caller's activation or output type is not bf16:
-// a bf16 copy of x and a bf16 staging copy of y.  0 for the decode kernel and for Q8_0.
+// a bf16 copy of x and a bf16 staging copy of y.  0 for the decode kernel.  Q8_0 (is_q4k == 0) may be called
+// without it: it then keeps the decode kernel in passes of eight tokens.
 size_t ub_qmatmul_workspace_bytes(int M, int N, int K, int is_q4k) {
-  if (M <= kDecodeMaxM || !is_q4k || M <= 0 || N <= 0 || K <= 0) return 0;
+  (void)is_q4k;
+  if (M <= kDecodeMaxM || M <= 0 || N <= 0 || K <= 0) return 0;
   return align_up(static_cast<size_t>(M) * K * 2, 256) + align_up(static_cast<size_t>(M) * N * 2, 256);
 }
 

@@ -227,6 +227,13 @@ int ub_synchronize(ub_device* dev) {
   return ub::fail(UB_OK);
 }
 
+int ub_mem_info(ub_device* dev, size_t* free_bytes, size_t* total_bytes) {
+  if (!dev || !free_bytes || !total_bytes) return ub::fail(UB_ERR_INVALID_ARG);
+  UB_CUDA_TRY(cudaSetDevice(dev->ordinal));
+  UB_CUDA_TRY(cudaMemGetInfo(free_bytes, total_bytes));
+  return ub::fail(UB_OK);
+}
+
 int ub_stream_query(void* stream) {
   const cudaError_t e = cudaStreamQuery(ub::as_stream(stream));
   if (e == cudaSuccess) return ub::fail(UB_OK);

@@ -189,6 +189,12 @@ class GcuDevice:
         self.synchronize()
         return out.reshape(shape) if shape is not None else out
 
+    def mem_info(self):
+        """(free, total) bytes of device memory."""
+        f, t = ctypes.c_size_t(), ctypes.c_size_t()
+        check(lib().ub_mem_info(self._handle, ctypes.byref(f), ctypes.byref(t)), "ub_mem_info")
+        return f.value, t.value
+
     def dtod_copy(self, src: GcuSlice, dst: GcuSlice) -> None:
         check(lib().ub_memcpy_dtod(self._handle, ctypes.c_void_p(dst.ptr), ctypes.c_void_p(src.ptr), src.nbytes),
               "dtod")
