@@ -423,7 +423,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
               const float g0 = __uint_as_float(gw[i] << 16), g1 = __uint_as_float(gw[i] & 0xFFFF0000u);
               const float u0 = __uint_as_float(uw[i] << 16), u1 = __uint_as_float(uw[i] & 0xFFFF0000u);
               const __nv_bfloat162 o2 =
-                  __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                  __floats2bfloat162_rn(__fdividef(g0, 1.f + __expf(-g0)) * u0, __fdividef(g1, 1.f + __expf(-g1)) * u1);
               ow[i] = bf162_bits(o2);
             }
             if (n_in)
@@ -478,7 +478,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     bool ok = true;
 
     // one super-block (four K steps); HALF is a compile-time copy of `half` so that nibble selection and
-    // the scale bytes' positions are immediate operands
+    // the scale bytes' positions are immediate operands.  (Measured on B200: one rolled code path for both
+    // halves, with the half as a run-time shift, is no faster, although instruction fetch is the second largest
+    // stall of the grouped launches.)
     auto super_block = [&](auto half_c, auto set_c) {
       constexpr int HALF = decltype(half_c)::value, SET = decltype(set_c)::value;
       ok = __all_sync(0xFFFFFFFFu, tc_wait(wfull_bar(ws), wphase, abort_flag));
@@ -557,13 +559,13 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     };
     using I0 = std::integral_constant<int, 0>;
     using I1 = std::integral_constant<int, 1>;
-    if (set == 0) {
+    if (kTcProducerSets == 1 || set == 0) {
       if (half) {
         for (int q = 0; q < total_sb && ok; q++) super_block(I1{}, I0{});
       } else {
         for (int q = 0; q < total_sb && ok; q++) super_block(I0{}, I0{});
       }
-    } else {
+    } else if constexpr (kTcProducerSets > 1) {
       if (half) {
         for (int q = 0; q < total_sb && ok; q++) super_block(I1{}, I1{});
       } else {
