@@ -191,6 +191,43 @@ def test_config3_q4k_prefill_full_size(dev):
     assert np.array_equal(got2, 2 * got[:64])
 
 
+# ----------------------------------------------------------------------------- two to four tokens (K = 2048 / 4096)
+@pytest.mark.parametrize("x_dtype", [DTYPE_F32, DTYPE_BF16])
+@pytest.mark.parametrize("out_dtype", [DTYPE_F32, DTYPE_BF16, DTYPE_F16])
+@pytest.mark.parametrize("M,N,K", [(2, 1, 4096), (2, 4747, 4096), (3, 17, 2048), (3, 5000, 4096), (4, 4736, 2048),
+                                   (4, 30000, 4096), (2, 20000, 2048)])
+def test_q4k_two_to_four_tokens(dev, x_dtype, out_dtype, M, N, K):
+    """Token pairs in the MMA columns, two CTAs per SM; N not a multiple of 16, more tiles than CTA slots, an odd
+    token count (the pair's second token multiplies by zero)."""
+    rng = np.random.default_rng(N + K + M)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, x_dtype == DTYPE_BF16)
+    want = o.c_qmatmul(x, w, N, K, True)
+    got = _run(dev, w, x, M, N, K, True, x_dtype, out_dtype)
+    if out_dtype == DTYPE_F32:
+        assert o.rel_l2(got, want) < (1e-4 if N >= 1000 else TOL_DECODE)
+    else:
+        assert o.rel_l2(got, want) < 4e-3  # storage rounding of y
+    again = _run(dev, w, x, M, N, K, True, x_dtype, out_dtype)
+    assert np.array_equal(got, again)  # fixed summation order
+
+
+def test_q4k_two_to_four_tokens_rows_differ(dev):
+    """Every token meets its own activations: rows of x that differ by orders of magnitude, one all-zero row."""
+    rng = np.random.default_rng(99)
+    M, N, K = 4, 1000, 4096
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    x[1] *= 4096.0
+    x[2] = 0.0
+    x[3] *= 2.0 ** -10
+    got = _run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_F32)
+    want = o.c_qmatmul(x, w, N, K, True)
+    for m in (0, 1, 3):
+        assert o.rel_l2(got[m], want[m]) < 1e-4, m
+    assert not got[2].any()
+
+
 # ----------------------------------------------------------------------------- single-token kernel (K = 2048 / 4096)
 @pytest.mark.parametrize("x_dtype", [DTYPE_F32, DTYPE_BF16])
 @pytest.mark.parametrize("out_dtype", [DTYPE_F32, DTYPE_BF16, DTYPE_F16])

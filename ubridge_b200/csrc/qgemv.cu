@@ -934,6 +934,8 @@ int q4k_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype,
                 cudaStream_t s);
 
 template <typename XT>
+int q4k_gemv_mt(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+template <typename XT>
 int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
              const ArParams* ar, cudaStream_t s);
 
@@ -961,8 +963,11 @@ int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, in
     int st;
     if ((reinterpret_cast<uintptr_t>(wq) & 15) == 0) {
       const int mi = left >= 8 ? 8 : left;
-      // a single token at K = 2048 / 4096: the two-CTAs-per-SM kernel; everything else: token pairs / quads
-      st = (is_q4k && mi == 1) ? q4k_gemv_m1<XT>(wq, xp, yp, N, K, y_dtype, fresh, ar, s) : UB_ERR_UNSUPPORTED;
+      // one token, or two to four at K = 2048 / 4096: the two-CTAs-per-SM kernels; everything else: the
+      // one-CTA-per-SM kernels with token pairs / quads
+      st = UB_ERR_UNSUPPORTED;
+      if (is_q4k && mi == 1) st = q4k_gemv_m1<XT>(wq, xp, yp, N, K, y_dtype, fresh, ar, s);
+      if (is_q4k && mi >= 2 && mi <= 4 && !ar) st = q4k_gemv_mt<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, s);
       if (st == UB_ERR_UNSUPPORTED)
         st = is_q4k ? q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, ar, s)
                     : q8_0_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, s);
