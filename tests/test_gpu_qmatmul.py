@@ -191,6 +191,41 @@ def test_config3_q4k_prefill_full_size(dev):
     assert np.array_equal(got2, 2 * got[:64])
 
 
+# ----------------------------------------------------------------------------- Q8_0, one token (K = 2048 / 4096)
+@pytest.mark.parametrize("x_dtype", [DTYPE_F32, DTYPE_BF16])
+@pytest.mark.parametrize("out_dtype", [DTYPE_F32, DTYPE_BF16, DTYPE_F16])
+@pytest.mark.parametrize("N,K", [(1, 4096), (17, 2048), (4096, 4096), (4747, 4096), (4740, 2048), (30000, 4096),
+                                 (20001, 2048)])
+def test_q8_0_single_token_kernel(dev, x_dtype, out_dtype, N, K):
+    """Eight-row tiles, two CTAs per SM; N not a multiple of 8, fewer and more tiles than CTA slots."""
+    rng = np.random.default_rng(N + K)
+    w = o.gen_q8_0_weight(rng, N, K)
+    x = o.gen_activation(rng, 1, K, x_dtype == DTYPE_BF16)
+    want = o.c_qmatmul(x, w, N, K, False)
+    got = _run(dev, w, x, 1, N, K, False, x_dtype, out_dtype)
+    if out_dtype == DTYPE_F32:
+        assert o.rel_l2(got, want) < (1e-4 if N >= 1000 else TOL_DECODE)
+    else:
+        assert o.rel_l2(got, want) < 4e-3  # storage rounding of y
+    assert np.array_equal(got, _run(dev, w, x, 1, N, K, False, x_dtype, out_dtype))  # fixed summation order
+
+
+def test_q8_0_single_token_extreme_blocks(dev):
+    """Weight bytes -128 and 127, activation blocks that are all zero or differ by orders of magnitude."""
+    rng = np.random.default_rng(5)
+    N, K = 520, 4096
+    w = o.gen_q8_0_weight(rng, N, K).reshape(N, K // 32, 34).copy()
+    w[:, ::3, 2:] = 0x80   # -128
+    w[:, 1::3, 2:] = 0x7F  # 127
+    w = w.reshape(-1)
+    x = o.gen_activation(rng, 1, K, False)
+    x[0, :32] = 0.0
+    x[0, 32:64] *= 8192.0
+    x[0, 2048:2080] *= 2.0 ** -12
+    got = _run(dev, w, x, 1, N, K, False, DTYPE_F32, DTYPE_F32)
+    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, False)) < 1e-4
+
+
 # ----------------------------------------------------------------------------- two to four tokens (K = 2048 / 4096)
 @pytest.mark.parametrize("x_dtype", [DTYPE_F32, DTYPE_BF16])
 @pytest.mark.parametrize("out_dtype", [DTYPE_F32, DTYPE_BF16, DTYPE_F16])

@@ -936,6 +936,8 @@ int q4k_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype,
 template <typename XT>
 int q4k_gemv_mt(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
 template <typename XT>
+int q8_0_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+template <typename XT>
 int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
              const ArParams* ar, cudaStream_t s);
 
@@ -968,6 +970,7 @@ int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, in
       st = UB_ERR_UNSUPPORTED;
       if (is_q4k && mi == 1) st = q4k_gemv_m1<XT>(wq, xp, yp, N, K, y_dtype, fresh, ar, s);
       if (is_q4k && mi >= 2 && mi <= 4 && !ar) st = q4k_gemv_mt<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, s);
+      if (!is_q4k && mi == 1) st = q8_0_gemv_m1<XT>(wq, xp, yp, N, K, y_dtype, fresh, s);
       if (st == UB_ERR_UNSUPPORTED)
         st = is_q4k ? q4k_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, ar, s)
                     : q8_0_gemv_imma<XT>(wq, xp, yp, mi, N, K, y_dtype, fresh, s);
