@@ -306,16 +306,24 @@ def test_q4k_single_token_zero_and_huge_activations(dev):
 
 
 # ----------------------------------------------------------------------------- large K: every kernel the sharded stack uses
-@pytest.mark.parametrize("N,K", [(512, 28672), (512, 14336), (640, 8192), (384, 7168), (256, 3584)])
+@pytest.mark.parametrize("N,K", [(512, 28672), (512, 14336), (640, 8192), (384, 7168), (256, 3584), (8192, 28672),
+                                 (5000, 16384), (19200, 14336)])
 @pytest.mark.parametrize("M", [1, 2])
 def test_q4k_decode_large_k(dev, M, N, K):
     """Row lengths of the 70B-shaped stack and of its tensor-parallel shards (down projection 28672 / tp; others
-    8192): K = 28672 does not fit the integer-MMA kernel's fragment area and takes the streaming kernel."""
+    8192).  One token beyond 12288 values runs in passes over K (four at 28672, two at 14336 / 16384) as long as a
+    CTA's tiles fit one batch (19200 rows do not: the streaming kernel); two tokens take the older kernels."""
     rng = np.random.default_rng(K + M)
     w = o.gen_q4k_weight(rng, N, K)
     x = o.gen_activation(rng, M, K, True)
     got = _run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_F32)
-    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, True)) < TOL_DECODE
+    want = o.c_qmatmul(x, w, N, K, True)
+    assert o.rel_l2(got, want) < TOL_DECODE
+    if M == 1:
+        assert o.rel_l2(got, want) < 1e-4
+        assert np.array_equal(got, _run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_F32))
+        got32 = _run(dev, w, x.astype(np.float32), M, N, K, True, DTYPE_F32, DTYPE_F32)  # f32 activations
+        assert o.rel_l2(got32, want) < 1e-4
 
 
 # ----------------------------------------------------------------------------- weights written just before the matmul

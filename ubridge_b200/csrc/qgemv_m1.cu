@@ -451,8 +451,8 @@ int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype
 
 
 // =====================================================================================================
-// The same kernel for longer rows (K a multiple of 2048 up to 12288: the 8192-wide projections of a 70B-shaped
-// stack).  A stage is 16 rows x 8 super-blocks (18 KB), a tile takes K / 2048 stages and warp w owns
+// The same kernel for longer rows (K a multiple of 2048: the 8192-wide projections of a 70B-shaped stack in one
+// pass, its 28672-wide down projection in four).  A stage is 16 rows x 8 super-blocks (18 KB), a tile takes K / 2048 stages and warp w owns
 // super-block 8c + w of every stage c.  The activation fragments no longer fit the register file: each warp
 // writes those of its own super-blocks to shared memory once per launch (one word per MMA and lane: the
 // half of the B operand that is zero by construction is not stored, the main loop puts the word into the
@@ -465,10 +465,11 @@ constexpr int kMaxChunks = 6;
 // rows 8T..8T+7 in its rows 0-7 and the matching up rows in its rows 8-15 (two 8-row copies), so that the two
 // halves of every MMA row pair meet in one thread of the epilogue.  Gate and up are rounded to the output type
 // before the activation, which gives the bits of the two-kernel sequence (matmul, then ub_silu_and_mul).
-template <typename XT, bool GU>
+// MULTI: K is consumed in `npass` passes (rows too long for all activation fragments to be resident at once).
+template <typename XT, bool GU, bool MULTI>
 __global__ void __launch_bounds__(kThreadsM1, 2)
-qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int nch, int y_dtype, int S, int early,
-                         int* err_word, const XT* __restrict__ gamma, float eps, const ArParams ar,
+qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int nch, int npass, int y_dtype, int S,
+                         int early, int* err_word, const XT* __restrict__ gamma, float eps, const ArParams ar,
                          const __grid_constant__ CUtensorMap w_map) {
   constexpr int kRowStride = 8 * UB_Q4K_BYTES;  // 1152 = 9 lines
   constexpr int kStageBytes = 16 * kRowStride;
@@ -500,9 +501,20 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
   }
   __syncthreads();
 
-  // item n of this CTA = (tile n / nch, stage n % nch) -> ring slot n % S
+  // K in passes of cpp stages (npass > 1: rows too long for all activation fragments to be resident at once; the
+  // launcher then guarantees a single batch of tiles): items run pass by pass, inside a pass tile by tile.
+  const int cpp = (nch + npass - 1) / npass;
+  // item n of this CTA -> (tile, stage) -> ring slot n % S
   auto issue_item = [&](int n) {
-    const int tile = n / nch, c = n - tile * nch;
+    int tile, c;
+    if (!MULTI) {
+      tile = n / nch, c = n - tile * nch;
+    } else {
+      int p = 0, r = n;
+      while (r >= my_tiles * min(cpp, nch - p * cpp)) r -= my_tiles * min(cpp, nch - p * cpp), p++;
+      const int cn = min(cpp, nch - p * cpp);
+      tile = r / cn, c = p * cpp + (r - tile * cn);
+    }
     const uint32_t full = bars_s + 8 * (n % S);
     const int row0 = kTileRows * (static_cast<int>(blockIdx.x) + tile * static_cast<int>(gridDim.x));
     mb_expect_tx(full, kStageBytes);
@@ -525,25 +537,29 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t epoch = ar.world > 1 ? ar_epoch(ar) : 0;  // of the fused all-reduce, read after the wait
 
-  // ---- activations of this warp's super-blocks (8c + warp) -> fragments in shared memory ----
-  {
+  // ---- activations of this warp's super-blocks of one pass (stages c0 .. c0 + cn - 1, super-block 8c + warp) ->
+  // fragments in shared memory, slot c - c0.  Only this warp reads them back, so a pass may overwrite them
+  // behind a warp-level barrier.
+  // (Fetching the next pass's activations into shared memory with asynchronous copies while the current pass
+  // computes was measured and is no faster: 37.0 against 35.7 us at 8192 x 28672; it costs a ring stage.)
+  auto quantise = [&](int c0, int cn, bool first) {
     Raw8<XT> raw[kMaxChunks];
 #pragma unroll
     for (int c = 0; c < kMaxChunks; c++)
-      if (c < nch) raw[c].load(x + static_cast<size_t>(8 * c + warp) * 256 + 8 * lane);
+      if (c < cn) raw[c].load(x + static_cast<size_t>(8 * (c0 + c) + warp) * 256 + 8 * lane);
     Raw8<XT> graw[kMaxChunks];
     if (gamma)
 #pragma unroll
       for (int c = 0; c < kMaxChunks; c++)
-        if (c < nch) graw[c].load(gamma + static_cast<size_t>(8 * c + warp) * 256 + 8 * lane);
-    if (threadIdx.x == 0)
+        if (c < cn) graw[c].load(gamma + static_cast<size_t>(8 * (c0 + c) + warp) * 256 + 8 * lane);
+    if (first && threadIdx.x == 0)
       for (int n = n_early; n < min(S, my_items); n++) issue_item(n);
     float scale = 1.f;
     if (gamma) {  // RMSNorm in front of the matmul
       float ss = 0.f;
 #pragma unroll
       for (int c = 0; c < kMaxChunks; c++) {
-        if (c >= nch) break;
+        if (c >= cn) break;
         float v[8];
         raw[c].unpack(v);
 #pragma unroll
@@ -553,7 +569,7 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
     }
 #pragma unroll
     for (int c = 0; c < kMaxChunks; c++) {
-      if (c >= nch) break;
+      if (c >= cn) break;
       float v[8];
       raw[c].unpack(v);
       if (gamma) {
@@ -600,7 +616,8 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
       if (lane == 0) *reinterpret_cast<float*>(f + 1024 + 32) = amax * (1.f / kXQMaxM1);
     }
     __syncwarp();
-  }
+  };
+  if (!MULTI) quantise(0, nch, true);
 
   uint32_t off_h, off_q[4];
   {
@@ -615,14 +632,18 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
   const uint32_t mlo = g < 4 ? 0xFFFFFFFFu : 0u, mhi = ~mlo;  // which half of the k range this lane's columns use
 
   bool ok = true;
-  int slot = 0, round = 0, item = 0, tile = 0;
+  int slot = 0, round = 0, item = 0;
   for (int b = 0; b < nbatches; b++) {
     const int n_mt = min(kBatchTiles, my_tiles - b * kBatchTiles);
 #pragma unroll 1
-    for (int mt = 0; mt < n_mt; mt++, tile++) {
+    for (int pass = 0; pass < (MULTI ? npass : 1); pass++) {
+    const int c_lo = MULTI ? pass * cpp : 0, c_n = MULTI ? min(cpp, nch - c_lo) : nch;
+    if (MULTI) quantise(c_lo, c_n, pass == 0);
+#pragma unroll 1
+    for (int mt = 0; mt < n_mt; mt++) {
       float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < nch; c++, item++) {
+      for (int c = 0; c < c_n; c++, item++) {
         if (ok) ok = mb_wait(bars_s + 8 * slot, round & 1);
         const unsigned char* rowA = sm + static_cast<size_t>(slot) * kStageBytes;
         const unsigned char* rowB = rowA + 8 * kRowStride;
@@ -681,7 +702,13 @@ qgemv_q4k_m1_long_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, 
       acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 1);
       acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
       acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 2);
-      if (t == 0) red[warp][mt][g] = acc0, red[warp][mt][8 + g] = acc1;
+      if (t == 0) {  // later passes add to what this same thread stored in the first
+        if (!MULTI || pass == 0)
+          red[warp][mt][g] = acc0, red[warp][mt][8 + g] = acc1;
+        else
+          red[warp][mt][g] += acc0, red[warp][mt][8 + g] += acc1;
+      }
+    }
     }
     __syncthreads();
     if (static_cast<int>(threadIdx.x) < n_mt * kTileRows) {
@@ -725,8 +752,21 @@ int launch_m1_long(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_
   constexpr int kRowStride = 8 * UB_Q4K_BYTES;
   constexpr int kStageBytes = 16 * kRowStride;
   const int nch = K / 2048;
-  const size_t frag_bytes = static_cast<size_t>(nch) * 8 * kFragBytesPerSb;
-  if (nch > kMaxChunks || frag_bytes + 3 * static_cast<size_t>(kStageBytes) > kRingBudget) return UB_ERR_UNSUPPORTED;
+  const int tiles = GU ? (N + 7) / 8 : (N + 15) / 16;
+  const int slots = 2 * ub::num_sms();
+  const int grid = tiles < slots ? tiles : slots;
+  // Rows beyond 12288 values: the activation fragments of a whole row no longer fit beside the ring, so K is
+  // consumed in passes of at most four stages whose fragments replace one another (the 28672-wide down
+  // projection of a 70B-shaped stack: four passes).  Needs every CTA's tiles to fit one batch, and the
+  // whole-row RMSNorm prologue is not available.
+  int npass = 1;
+  if (nch > kMaxChunks) {
+    if (GU || gamma || tiles > kBatchTiles * grid) return UB_ERR_UNSUPPORTED;
+    npass = (nch + 3) / 4;
+  }
+  const int cpp = (nch + npass - 1) / npass;
+  const size_t frag_bytes = static_cast<size_t>(cpp) * 8 * kFragBytesPerSb;
+  if (frag_bytes + 3 * static_cast<size_t>(kStageBytes) > kRingBudget) return UB_ERR_UNSUPPORTED;
   int S = static_cast<int>((kRingBudget - frag_bytes) / kStageBytes);
   if (S > kMaxStagesM1) S = kMaxStagesM1;
   CUtensorMap wmap;
@@ -740,15 +780,12 @@ int launch_m1_long(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return UB_ERR_UNSUPPORTED;
   const size_t smem = static_cast<size_t>(S) * kStageBytes + frag_bytes + 1024;
-  auto kernel = qgemv_q4k_m1_long_kernel<XT, GU>;
+  auto kernel = npass > 1 ? qgemv_q4k_m1_long_kernel<XT, false, true> : qgemv_q4k_m1_long_kernel<XT, GU, false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
   }
-  const int tiles = GU ? (N + 7) / 8 : (N + 15) / 16;
-  const int slots = 2 * ub::num_sms();
-  const int grid = tiles < slots ? tiles : slots;
   const int early = fresh ? 0 : 2;  // 36 KB per CTA ahead of the dependency wait, as in the short-row kernel
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -757,7 +794,8 @@ int launch_m1_long(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, nch, y_dtype, S, early, ub::device_error_word(), gamma, eps, ar, wmap);
+  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, nch, npass, y_dtype, S, early, ub::device_error_word(), gamma, eps, ar,
+                         wmap);
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
@@ -770,7 +808,8 @@ int launch_m1_long(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_
 namespace ub {
 
 // y[N] = dequant(Wq) . x for one token; UB_ERR_UNSUPPORTED (without touching the thread's status) for shapes
-// these kernels do not take (K not a multiple of 2048 or beyond 12288, unaligned weights, no tensor-map encoder).
+// these kernels do not take (K not a multiple of 2048; beyond 12288: more rows than one batch of tiles per CTA, or
+// with the RMSNorm prologue; unaligned weights; no tensor-map encoder).
 // fresh: the weight bytes may have been written by the kernel launched just before on the same stream.
 template <typename XT>
 int q4k_gemv_m1x(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, const M1Extras& ex,
@@ -783,7 +822,7 @@ int q4k_gemv_m1x(const void* wq, const XT* x, void* y, int N, int K, int y_dtype
   const XT* gamma = static_cast<const XT*>(ex.gamma);
   if (K == 4096) return launch_m1<XT, 2>(w, x, y, N, K, y_dtype, fresh, gamma, ex.eps, a, s);
   if (K == 2048) return launch_m1<XT, 1>(w, x, y, N, K, y_dtype, fresh, gamma, ex.eps, a, s);
-  if (K % 2048 == 0) return launch_m1_long<XT, false>(w, x, y, N, K, y_dtype, fresh, gamma, ex.eps, a, s);  // <= 12288
+  if (K % 2048 == 0) return launch_m1_long<XT, false>(w, x, y, N, K, y_dtype, fresh, gamma, ex.eps, a, s);
   return UB_ERR_UNSUPPORTED;
 }
 
