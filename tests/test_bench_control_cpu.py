@@ -79,5 +79,8 @@ def test_timed_region_sizing_and_profile_lookup():
     assert bench.replays_for(2.0, 20, 1.0) == 1
     assert bench.replays_for(2.0, 20, 0.0) == 1
     # roofline.traffic comes from the profile summaries, not from a constant in the script
-    assert bench.profile_traffic("c1") == 17896448
+    for wl, name in bench.PROFILE_OF.items():
+        text = open(os.path.join(os.path.dirname(bench.__file__), "profiles", name)).read()
+        assert "dram_bytes_per_launch = %d" % bench.profile_traffic(wl) in text, wl
+    assert bench.profile_traffic("c1") == 17868032
     assert bench.profile_traffic("c5_m1") is None
