@@ -42,10 +42,12 @@ namespace {
 using namespace ub;
 
 constexpr int kTcProducerWarps = 8;   // warps that dequantise one K step (128 rows x 2 nibble halves)
-// Sets of such warps; set i takes the K steps with step % sets == i.  Measured on B200: a second set does
-// not help (C3 204 us against 191 us with one), the producers are not bound by their own latency chain.
-constexpr int kTcProducerSets = 1;
-constexpr int kTcThreads = (5 + kTcProducerWarps * kTcProducerSets + 1) * 32;
+// Sets of such warps (template parameter SETS); set i takes the K steps with step % SETS == i.  Measured on B200:
+// a second set does not help, neither with 256-token tiles (C3 204 us against 191 us with one) nor with 16 to 128
+// tokens (14336x4096: 27.9 us against 26.1 us at 16 tokens, where a K step takes 0.42 us whatever the token
+// count: 0.20 us of producer arithmetic, 0.10 us until tcgen05.st has landed, 0.20 us for the issuing thread to
+// get four MMAs and a commit out).  Every launch uses one set.
+constexpr int tc_threads(int sets) { return (5 + kTcProducerWarps * sets + 1) * 32; }
 constexpr int kTcBK = 64;
 constexpr uint32_t kTcWaitLimit = 2000000;
 
@@ -201,8 +203,8 @@ struct TcShared {
 // help (MoE layer of 256 tokens, one CTA per SM: 3 -> 5 slots 589 -> 567 us; dense M = 2048: 2 -> 4 slots no
 // change), the packed tiles are not what a K step waits for.
 // FMT: 0 = Q4_K super-blocks, 1 = Q8_0 blocks (dense mode only).
-template <int TOK, int STAGES, int MODE, int CTAS, int WST, int FMT>
-__global__ void __launch_bounds__(kTcThreads, CTAS)
+template <int TOK, int STAGES, int MODE, int CTAS, int WST, int FMT, int SETS>
+__global__ void __launch_bounds__(tc_threads(SETS), CTAS)
 qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err_word,
                     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                     const TcGroup grp) {
@@ -251,7 +253,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     const int padded = *grp.num_post_pad;
     int nblocks = padded > 0 ? (padded + grp.block - 1) / grp.block : 0;
     if (nblocks > kTcMaxRuns) nblocks = kTcMaxRuns;  // the launcher guarantees this never cuts
-    for (int i = threadIdx.x; i < nblocks; i += kTcThreads) ids[i] = grp.experts_ids[i];
+    for (int i = threadIdx.x; i < nblocks; i += tc_threads(SETS)) ids[i] = grp.experts_ids[i];
     __syncthreads();
     if (threadIdx.x == 0) {
       int n = 0;
@@ -294,7 +296,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     }
     for (int b = 0; b < kWStages; b++) {
       tc_mbar_init(wfull_bar(b), 1);
-      tc_mbar_init(wempty_bar(b), kTcProducerWarps * kTcProducerSets);
+      tc_mbar_init(wempty_bar(b), kTcProducerWarps * SETS);
     }
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -454,14 +456,14 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
         acc_phase ^= 1;
       }
     }
-  } else if (warp <= 4 + kTcProducerWarps * kTcProducerSets) {
+  } else if (warp <= 4 + kTcProducerWarps * SETS) {
     // ------------------------------------------------------------ weight producers (256 threads per set)
     // One flat loop over (tile, super-block); the super-block's four K steps (its four 64-value groups) are
     // dealt round robin to the producer sets.  Packed weights arrive in shared memory as
     // [128 rows][144 bytes] per super-block; a thread owns one weight row (= its TMEM lane) and one nibble
     // half and reads its row's header and 32-byte pieces from there (rows are 144 bytes apart, so a
     // quarter-warp's 16-byte reads hit all 32 banks once).
-    static_assert(STAGES % kTcProducerSets == 0, "a set must return to the same stages every ring turn");
+    static_assert(STAGES % SETS == 0, "a set must return to the same stages every ring turn");
     // weight row inside the tile = the TMEM lane this warp may access (32 * (warp % 4) + lane);
     // half: 0 = low nibbles (even sub-blocks), 1 = high nibbles
     const int wrow = 32 * (warp & 3) + lane, half = ((warp - 5) >> 2) & 1, set = (warp - 5) >> 3;
@@ -494,8 +496,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
         q4k_unpack_scales(hdr.y, hdr.z, hdr.w, scw[0], scw[1], mnw[0], mnw[1]);
       }
 #pragma unroll
-      for (int Gi = 0; Gi < 4 / kTcProducerSets; Gi++) {
-        constexpr int kSets = kTcProducerSets;
+      for (int Gi = 0; Gi < 4 / SETS; Gi++) {
+        constexpr int kSets = SETS;
         const int G = kSets * Gi + SET;
         uint32_t ot[16];  // this thread's 32 values of the step = 16 TMEM columns of packed pairs
         if (FMT == 0) {
@@ -544,7 +546,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) tc_mbar_arrive(full_bar(s));
-        s += kTcProducerSets;
+        s += SETS;
         if (s >= STAGES) {
           s -= STAGES;
           phase ^= 1;
@@ -559,13 +561,13 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     };
     using I0 = std::integral_constant<int, 0>;
     using I1 = std::integral_constant<int, 1>;
-    if (kTcProducerSets == 1 || set == 0) {
+    if (SETS == 1 || set == 0) {
       if (half) {
         for (int q = 0; q < total_sb && ok; q++) super_block(I1{}, I0{});
       } else {
         for (int q = 0; q < total_sb && ok; q++) super_block(I0{}, I0{});
       }
-    } else if constexpr (kTcProducerSets > 1) {
+    } else if constexpr (SETS > 1) {
       if (half) {
         for (int q = 0; q < total_sb && ok; q++) super_block(I1{}, I1{});
       } else {
@@ -666,7 +668,7 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int TOK, int STAGES, int MODE, int CTAS = 1, int WST = 0, int FMT = 0>
+template <int TOK, int STAGES, int MODE, int CTAS = 1, int WST = 0, int FMT = 0, int SETS = 1>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const TcGroup& grp, int w_rows_total,
               cudaStream_t s) {
   constexpr size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(tc_stage_tok(TOK, CTAS)) * 256 +
@@ -705,13 +707,13 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ub::fail(UB_ERR_UNSUPPORTED);
-  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS, WST, FMT>;
+  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS, WST, FMT, SETS>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
   }
-  kernel<<<grid, kTcThreads, smem, s>>>(static_cast<__nv_bfloat16*>(y), M, N, K, ub::device_error_word(), map, wmap,
+  kernel<<<grid, tc_threads(SETS), smem, s>>>(static_cast<__nv_bfloat16*>(y), M, N, K, ub::device_error_word(), map, wmap,
                                         grp);
   return ub::check_launch();
 }
