@@ -326,6 +326,18 @@ def test_q4k_decode_large_k(dev, M, N, K):
         assert o.rel_l2(got32, want) < 1e-4
 
 
+@pytest.mark.parametrize("is_q4k,M,N,K", [(True, 4, 48, 12544), (False, 4, 40, 16640), (True, 3, 33, 12800),
+                                          (False, 2, 19, 16896)])
+def test_decode_rows_too_long_for_the_staged_kernels(dev, is_q4k, M, N, K):
+    """Several tokens with rows whose activations fit none of the staged kernels' shared-memory plans: the plain
+    warp-per-row kernels (the last fallback of the dispatch) compute them."""
+    rng = np.random.default_rng(K + M)
+    w = (o.gen_q4k_weight if is_q4k else o.gen_q8_0_weight)(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    got = _run(dev, w, x, M, N, K, is_q4k, DTYPE_BF16, DTYPE_F32)
+    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, is_q4k)) < 1e-4
+
+
 # ----------------------------------------------------------------------------- weights written just before the matmul
 def test_quantize_then_matmul_back_to_back(dev):
     """ub_quantize_q8_0 and the Q8_0 matmul on one stream with nothing in between: the matmul must not request
