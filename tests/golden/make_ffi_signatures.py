@@ -71,7 +71,9 @@ def extract(ref_root: str) -> dict:
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_ffi_signatures.py <path of an Ubridge checkout>")
+    root = sys.argv[1]
     data = extract(root)
     with open(os.path.join(HERE, "ffi_signatures.json"), "w") as f:
         json.dump(data, f, indent=1, sort_keys=True)

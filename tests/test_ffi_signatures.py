@@ -10,7 +10,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLDEN = os.path.join(ROOT, "tests", "golden", "ffi_signatures.json")
-REFERENCE = "/root/reference"
+REFERENCE = os.environ.get("UB_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))  # a checkout of Ubridge, if any
 
 
 def _c_kind(t: str) -> str:

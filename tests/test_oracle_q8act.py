@@ -1,6 +1,6 @@
 """CPU: the informational "q8act" arm (activation rows quantised to 8-bit blocks, integer block dots, the way
-GGML-family CPU back ends multiply) - its two restatements agree and its distance to the exact arm is what the
-survey predicted: above the 1e-3 gate, so the gate stays on the exact arm."""
+GGML-family CPU back ends multiply) - its two restatements agree and its distance to the exact arm is several
+times the 1e-3 gate of the decode matmul, so the gate stays on the exact arm."""
 import numpy as np
 import pytest
 
