@@ -294,6 +294,23 @@ def test_q4k_single_token_many_tiles_per_cta(dev):
     assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, True)) < 1e-4
 
 
+@pytest.mark.parametrize("K", [2048, 4096])
+@pytest.mark.parametrize("N", [4792, 4816, 14336, 5328, 7120])
+def test_q4k_single_token_left_over_tiles_in_halves(dev, K, N):
+    """Row counts whose 16-row tiles leave a few over after the full rounds of the grid (296 CTAs on 148 SMs): the
+    left-over tiles are dealt as 8-row halves.  4792 rows: the last half lies wholly past the matrix; 5328: 37 left over,
+    the most that are cut; 7120: more left over than that, so whole tiles again.  A row's arithmetic does not
+    depend on which CTA or which half computes it: the last rows equal those of a small matrix of the same bytes."""
+    rng = np.random.default_rng(N + K)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, 1, K, True)
+    got = _run(dev, w, x, 1, N, K, True, DTYPE_BF16, DTYPE_F32)
+    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, True)) < 1e-4
+    tail = 200
+    w_tail = np.ascontiguousarray(w.reshape(N, -1)[N - tail:])
+    assert np.array_equal(got.reshape(-1)[N - tail:], _run(dev, w_tail, x, 1, tail, K, True, DTYPE_BF16, DTYPE_F32).reshape(-1))
+
+
 def test_q4k_single_token_zero_and_huge_activations(dev):
     rng = np.random.default_rng(5)
     N, K = 300, 4096
@@ -442,6 +459,7 @@ def test_rms_norm_standalone(dev, dtype):
 
 
 @pytest.mark.parametrize("M,N,K,gate_up", [(1, 1000, 4096, False), (1, 640, 2048, False), (1, 520, 8192, False),
+                                           (1, 4816, 4096, False), (1, 2408, 4096, True),
                                            (1, 700, 8192, True), (1, 96, 1024, False), (3, 200, 2048, True),
                                            (20, 136, 1024, False)])
 def test_matmul_on_rms_norm(dev, M, N, K, gate_up):
@@ -467,7 +485,7 @@ def test_matmul_on_rms_norm(dev, M, N, K, gate_up):
     assert o.rel_l2(got, want) < 8e-3
 
 
-@pytest.mark.parametrize("N,K", [(1024, 4096), (520, 8192), (200, 1024)])
+@pytest.mark.parametrize("N,K", [(1024, 4096), (520, 8192), (200, 1024), (4816, 4096)])
 def test_matmul_with_residual_on_one_rank(dev, N, K):
     import ctypes
 

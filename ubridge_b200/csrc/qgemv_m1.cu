@@ -155,9 +155,9 @@ __device__ __forceinline__ void st_out(void* y, size_t idx, int dtype, float v) 
 // early: stages requested before the wait for the previous kernel (0 when the weights may be fresh).
 template <typename XT, int SBW>
 __global__ void __launch_bounds__(kThreadsM1, 2)
-qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y_dtype, int S, int early,
+qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y_dtype, int S, int early, int split,
                     int* err_word, const XT* __restrict__ gamma, float eps, const ArParams ar,
-                    const __grid_constant__ CUtensorMap w_map) {
+                    const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap w_map8) {
   constexpr int kRowStride = 8 * SBW * UB_Q4K_BYTES;  // 1152 or 2304: whole 128-byte lines
   constexpr int kStageBytes = 16 * kRowStride;
   extern __shared__ __align__(128) unsigned char m1_smem_raw[];
@@ -172,9 +172,25 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
   const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(sm));
   const uint32_t bars_s = static_cast<uint32_t>(__cvta_generic_to_shared(bars));
   const int total_tiles = (N + 15) >> 4;
+  // split > 0: the `split` tiles left over after the full rounds are not dealt as a last tile to `split` CTAs, which
+  // would then finish a whole tile later than everybody else and hold back the next launch; they are cut in halves
+  // of eight rows, one for each of the first 2 * split CTAs (the last tile of such a CTA, rows 0-7 of its stage).
+  const int rounds = total_tiles / static_cast<int>(gridDim.x);
+  const bool has_half = split > 0 && static_cast<int>(blockIdx.x) < 2 * split;
   const int my_tiles =
-      static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      split > 0 ? rounds + (has_half ? 1 : 0)
+                : (static_cast<int>(blockIdx.x) < total_tiles
+                       ? (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                             static_cast<int>(gridDim.x)
+                       : 0);
   const int nbatches = (my_tiles + kBatchTiles - 1) / kBatchTiles;
+  // first row of this CTA's tile n
+  auto tile_row0 = [&](int n) {
+    if (has_half && n == my_tiles - 1)
+      return 16 * (rounds * static_cast<int>(gridDim.x) + (static_cast<int>(blockIdx.x) >> 1)) +
+             8 * (static_cast<int>(blockIdx.x) & 1);
+    return 16 * (static_cast<int>(blockIdx.x) + n * static_cast<int>(gridDim.x));
+  };
 
   // The next kernel in the stream may start as soon as every CTA of this grid has passed this point: its
   // CTAs take over SMs as ours retire.
@@ -192,12 +208,12 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
   // swizzle; rows past N arrive as zeros
   auto issue_tile = [&](int n) {
     const uint32_t full = bars_s + 8 * (n % S);
-    mb_expect_tx(full, kStageBytes);
+    const bool half = has_half && n == my_tiles - 1;  // eight rows through the map with the eight-row box
+    mb_expect_tx(full, half ? kStageBytes / 2 : kStageBytes);
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::
             "r"(ring_s + (n % S) * kStageBytes),
-        "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(full), "r"(0), "r"(0),
-        "r"(16 * (static_cast<int>(blockIdx.x) + n * static_cast<int>(gridDim.x)))
+        "l"(reinterpret_cast<uint64_t>(half ? &w_map8 : &w_map)), "r"(full), "r"(0), "r"(0), "r"(tile_row0(n))
         : "memory");
   };
   const int n_early = min(min(early, S), my_tiles);
@@ -313,16 +329,22 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
       if (ok) ok = mb_wait(bars_s + 8 * slot, round & 1);
       const unsigned char* rowA = sm + static_cast<size_t>(slot) * kStageBytes;
       const unsigned char* rowB = rowA + 8 * kRowStride;
+      const bool half = has_half && tile == my_tiles - 1;  // rows 8-15 of the stage hold nothing of this tile
       uint4 hA[SBW], hB[SBW];
       uint2 wA[SBW][4], wB[SBW][4];
 #pragma unroll
       for (int i = 0; i < SBW; i++) {
         hA[i] = *reinterpret_cast<const uint4*>(rowA + off_h[i]);
-        hB[i] = *reinterpret_cast<const uint4*>(rowB + off_h[i]);
 #pragma unroll
-        for (int G = 0; G < 4; G++) {
-          wA[i][G] = *reinterpret_cast<const uint2*>(rowA + off_q[i][G]);
-          wB[i][G] = *reinterpret_cast<const uint2*>(rowB + off_q[i][G]);
+        for (int G = 0; G < 4; G++) wA[i][G] = *reinterpret_cast<const uint2*>(rowA + off_q[i][G]);
+        if (!half) {
+          hB[i] = *reinterpret_cast<const uint4*>(rowB + off_h[i]);
+#pragma unroll
+          for (int G = 0; G < 4; G++) wB[i][G] = *reinterpret_cast<const uint2*>(rowB + off_q[i][G]);
+        } else {
+          hB[i] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int G = 0; G < 4; G++) wB[i][G] = make_uint2(0, 0);
         }
       }
       // everything this warp needs from the stage is in registers: hand the slot back (the arrive is a
@@ -350,25 +372,28 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
         // 6-bit scales and mins of sub-blocks t and 4 + t (kernels/quant.cpp:356-363), rows g (A) and g + 8 (B)
         const uint32_t a0 = __byte_perm(hA[i].y, 0, selb), a1 = __byte_perm(hA[i].z, 0, selb),
                        a2 = __byte_perm(hA[i].w, 0, selb);
-        const uint32_t b0 = __byte_perm(hB[i].y, 0, selb), b1 = __byte_perm(hB[i].z, 0, selb),
-                       b2 = __byte_perm(hB[i].w, 0, selb);
         const int scA0 = a0 & 63, mnA0 = a1 & 63, scA1 = (a2 & 15) | ((a0 >> 2) & 0x30),
                   mnA1 = (a2 >> 4) | ((a1 >> 2) & 0x30);
-        const int scB0 = b0 & 63, mnB0 = b1 & 63, scB1 = (b2 & 15) | ((b0 >> 2) & 0x30),
-                  mnB1 = (b2 >> 4) | ((b1 >> 2) & 0x30);
         // columns 2t, 2t+1 of d: high- and low-limb dots of sub-block 4q + t
         const int hiA = d[0][0] * scA0 + d[1][0] * scA1, loA = d[0][1] * scA0 + d[1][1] * scA1;
-        const int hiB = d[0][2] * scB0 + d[1][2] * scB1, loB = d[0][3] * scB0 + d[1][3] * scB1;
-        const int tA = mnA0 * Sa[i] + mnA1 * Sb[i], tB = mnB0 * Sa[i] + mnB1 * Sb[i];
+        const int tA = mnA0 * Sa[i] + mnA1 * Sb[i];
         const float dA = half_bits_to_f32(hA[i].x), dminA = half_bits_to_f32(hA[i].x >> 16);
-        const float dB = half_bits_to_f32(hB[i].x), dminB = half_bits_to_f32(hB[i].x >> 16);
         const float fA = fmaf(static_cast<float>(hiA), 254.f, static_cast<float>(loA));
-        const float fB = fmaf(static_cast<float>(hiB), 254.f, static_cast<float>(loB));
         const float xsm = xs[i] * odd16;
         acc0 = fmaf(fA, dA * xsm, acc0);
         acc0 = fmaf(-static_cast<float>(tA), dminA * xs[i], acc0);
-        acc1 = fmaf(fB, dB * xsm, acc1);
-        acc1 = fmaf(-static_cast<float>(tB), dminB * xs[i], acc1);
+        if (!half) {  // rows 8-15
+          const uint32_t b0 = __byte_perm(hB[i].y, 0, selb), b1 = __byte_perm(hB[i].z, 0, selb),
+                         b2 = __byte_perm(hB[i].w, 0, selb);
+          const int scB0 = b0 & 63, mnB0 = b1 & 63, scB1 = (b2 & 15) | ((b0 >> 2) & 0x30),
+                    mnB1 = (b2 >> 4) | ((b1 >> 2) & 0x30);
+          const int hiB = d[0][2] * scB0 + d[1][2] * scB1, loB = d[0][3] * scB0 + d[1][3] * scB1;
+          const int tB = mnB0 * Sa[i] + mnB1 * Sb[i];
+          const float dB = half_bits_to_f32(hB[i].x), dminB = half_bits_to_f32(hB[i].x >> 16);
+          const float fB = fmaf(static_cast<float>(hiB), 254.f, static_cast<float>(loB));
+          acc1 = fmaf(fB, dB * xsm, acc1);
+          acc1 = fmaf(-static_cast<float>(tB), dminB * xs[i], acc1);
+        }
       }
       // rows g and g + 8 of this tile: add the four lanes of a row (fixed order), park the warp's partial sums
       acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1);
@@ -381,8 +406,9 @@ qgemv_q4k_m1_kernel(const XT* __restrict__ x, void* __restrict__ y, int N, int y
     __syncthreads();  // partial sums of the batch are complete
     if (static_cast<int>(threadIdx.x) < n_mt * 16) {
       const int mt = threadIdx.x >> 4, r = threadIdx.x & 15;
-      const int row = 16 * (static_cast<int>(blockIdx.x) + (b * kBatchTiles + mt) * static_cast<int>(gridDim.x)) + r;
-      if (row < N) {
+      const int n = b * kBatchTiles + mt;
+      const int row = tile_row0(n) + r;
+      if (row < N && !(has_half && n == my_tiles - 1 && r >= 8)) {
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < kW; w++) tot += red[w][mt][r];  // fixed order: deterministic
@@ -419,6 +445,13 @@ int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return UB_ERR_UNSUPPORTED;
+  // the same rows through a box of eight: the halves of the tiles left over after the full rounds
+  CUtensorMap wmap8;
+  const cuuint32_t box8[3] = {128, static_cast<cuuint32_t>(kRowStride / 128), 8};
+  if (enc(&wmap8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(wq), dims, strides, box8, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return UB_ERR_UNSUPPORTED;
   int S = static_cast<int>(kRingBudget / kStageBytes);
   if (S > kMaxStagesM1) S = kMaxStagesM1;
   const size_t smem = static_cast<size_t>(S) * kStageBytes + 1024;
@@ -434,6 +467,11 @@ int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype
   // one 36 KB stage (two 18 KB ones) ahead of the dependency wait; none when the weights may still be
   // in flight from the previous kernel
   const int early = fresh ? 0 : (SBW == 2 ? 1 : 2);
+  // A few tiles left over after the full rounds (8 of 896 on 296 CTAs at 14336 rows) would make as many CTAs
+  // finish a tile later than the rest, and the next launch waits for the last CTA: cut them in halves instead.
+  // Only for a few: with 88 of 384 left over (6144 rows) halves measured 1 % slower than whole tiles.
+  const int rem = tiles % grid;
+  const int split = (tiles > grid && rem > 0 && 8 * rem <= grid) ? rem : 0;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kThreadsM1), cfg.dynamicSmemBytes = smem, cfg.stream = s;
@@ -441,7 +479,8 @@ int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, y_dtype, S, early, ub::device_error_word(), gamma, eps, ar, wmap);
+  e = cudaLaunchKernelEx(&cfg, kernel, x, y, N, y_dtype, S, early, split, ub::device_error_word(), gamma, eps, ar, wmap,
+                         wmap8);
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
