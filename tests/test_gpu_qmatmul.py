@@ -118,6 +118,26 @@ def _bf16_weights_product(x, w, N, K):
     return x.astype(np.float64) @ wd.astype(np.float64).T
 
 
+@pytest.mark.parametrize("is_q4k", [True, False])
+@pytest.mark.parametrize("M,N,K", [(5, 4096, 4096), (16, 4096, 4096), (64, 4096, 4096), (33, 8192, 4096), (16, 14336, 4096),
+                                   (7, 1000, 2048), (16, 130, 512), (20, 30000, 2048), (48, 20000, 1024),
+                                   (9, 300, 8192), (64, 640, 28672)])
+def test_few_tokens_k_split(dev, is_q4k, M, N, K):
+    """5 to 64 tokens on the tensor-core kernel: tiles split along K over clusters of 2, 4 or 8 CTAs (4096 rows of 4096:
+    8; 8192 rows: 4; 14336: 2), partial sums exchanged through the cluster's shared memory; more tiles than clusters
+    (30000 and 20000 rows, so the exchange buffers are reused), ragged last tiles, every token count's owner pattern.
+    Fixed summation order: two runs agree bit for bit."""
+    rng = np.random.default_rng(M + N + K)
+    w = o.gen_q4k_weight(rng, N, K) if is_q4k else o.gen_q8_0_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    got = _run(dev, w, x, M, N, K, is_q4k, DTYPE_BF16, DTYPE_BF16)
+    want = x @ o.c_dequant(w, is_q4k).reshape(N, K).T
+    err = o.rel_l2(got, want)
+    # weights and outputs pass through bf16 (2^-9 each): ~3e-3 overall; a misplaced partial sum would show as 0.1-1
+    assert err < 5e-3, err
+    assert np.array_equal(got, _run(dev, w, x, M, N, K, is_q4k, DTYPE_BF16, DTYPE_BF16))
+
+
 @pytest.mark.parametrize("M", [17, 64, 65, 130, 300])
 def test_q8_0_general_m(dev, M):
     """Q8_0 with more than 16 tokens: the tcgen05 kernel with the Q8_0 producer (K % 256 == 0, aligned weights)."""
@@ -161,8 +181,11 @@ def test_q8_0_prefill_full_size(dev):
     want = x @ o.c_dequant(w, False).reshape(N, K).T
     assert o.rel_l2(got, want) < TOL_TENSOR
     assert o.rel_l2(got, want) < 3e-3
+    # linearity: doubling the activations doubles every output exactly (powers of two commute with rounding)
+    got1 = _run(dev, w, x[:64], 64, N, K, False, DTYPE_BF16, DTYPE_BF16)
     got2 = _run(dev, w, 2 * x[:64], 64, N, K, False, DTYPE_BF16, DTYPE_BF16)
-    assert np.array_equal(got2, 2 * got[:64])
+    assert np.array_equal(got2, 2 * got1)
+    assert o.rel_l2(got1, got[:64]) < 1e-3  # 64 tokens split K over several CTAs: another summation order
 
 
 def test_workspace_is_required_when_types_need_conversion(dev):
@@ -187,8 +210,10 @@ def test_config3_q4k_prefill_full_size(dev):
     want = x @ wd.T  # f32 BLAS on the host: the full-size check is against 1e-2, not bit-exactness
     assert o.rel_l2(got, want) < TOL_TENSOR
     # linearity: doubling the activations doubles every output exactly (powers of two commute with rounding)
+    got1 = _run(dev, w, x[:64], 64, N, K, True, DTYPE_BF16, DTYPE_BF16)
     got2 = _run(dev, w, 2 * x[:64], 64, N, K, True, DTYPE_BF16, DTYPE_BF16)
-    assert np.array_equal(got2, 2 * got[:64])
+    assert np.array_equal(got2, 2 * got1)
+    assert o.rel_l2(got1, got[:64]) < 1e-3  # 64 tokens split K over several CTAs: another summation order
 
 
 # ----------------------------------------------------------------------------- Q8_0, one token (K = 2048 / 4096)
@@ -261,6 +286,62 @@ def test_q4k_two_to_four_tokens_rows_differ(dev):
     for m in (0, 1, 3):
         assert o.rel_l2(got[m], want[m]) < 1e-4, m
     assert not got[2].any()
+
+
+# ----------------------------------------------------------------------------- five to eight tokens in the MMA columns
+@pytest.mark.parametrize("x_dtype,out_dtype", [(DTYPE_BF16, DTYPE_F32), (DTYPE_F32, DTYPE_F32), (DTYPE_BF16, DTYPE_BF16),
+                                               (DTYPE_F32, DTYPE_F16)])
+@pytest.mark.parametrize("M,N,K", [(5, 1, 4096), (5, 17, 2048), (8, 4747, 4096), (6, 4736, 2048), (7, 30000, 4096),
+                                   (8, 20000, 2048), (8, 14336, 4096), (7, 5000, 8192), (8, 130, 8192), (6, 63, 4096)])
+def test_q4k_five_to_eight_tokens(dev, x_dtype, out_dtype, M, N, K):
+    """Tokens in the columns of the integer MMA, activation fragments shared by clusters of four CTAs: fewer tiles than
+    CTAs (CTAs without a tile still quantise their share), ragged last tile, more tiles per CTA than ring stages
+    (30000 rows), 8192-value rows."""
+    rng = np.random.default_rng(M + N + K)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, x_dtype == DTYPE_BF16)
+    want = o.c_qmatmul(x, w, N, K, True)
+    got = _run(dev, w, x, M, N, K, True, x_dtype, out_dtype)
+    if out_dtype == DTYPE_F32:
+        # 15-bit block fixed-point activations: ~1e-5 over thousands of outputs; a handful of outputs is a handful
+        # of samples of that noise, so only the task's tolerance is asserted there
+        assert o.rel_l2(got, want) < (1e-4 if M * N >= 1000 else TOL_DECODE)
+        assert np.array_equal(got, _run(dev, w, x, M, N, K, True, x_dtype, out_dtype))  # fixed summation order
+    else:
+        assert np.array_equal(got, o.round_through(_run(dev, w, x, M, N, K, True, x_dtype, DTYPE_F32),
+                                                   o.UB_BF16 if out_dtype == DTYPE_BF16 else o.UB_F16))
+
+
+@pytest.mark.parametrize("M,N,K", [(13, 1000, 4096), (16, 600, 2048), (11, 300, 8192)])
+def test_q4k_more_tokens_in_passes_of_eight(dev, M, N, K):
+    """Nine to sixteen tokens with f32 on either side: a pass of eight, then five to eight (or the smaller kernels)."""
+    rng = np.random.default_rng(M + N + K)
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, False)
+    got = _run(dev, w, x, M, N, K, True, DTYPE_F32, DTYPE_F32)
+    assert o.rel_l2(got, o.c_qmatmul(x, w, N, K, True)) < 1e-4
+
+
+def test_q4k_five_to_eight_tokens_rows_differ(dev):
+    """Every token has its own scale per 256 values: tokens of very different magnitude, a token of zeros, a
+    super-block of zeros in one token and a large one in another."""
+    rng = np.random.default_rng(77)
+    M, N, K = 7, 600, 4096
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    x[1] *= 4096.0
+    x[2] *= 1.0 / 1024.0
+    x[3] = 0.0
+    x[4, :256] = 0.0
+    x[5, 256:512] *= 8192.0
+    x[6] *= 64.0
+    got = _run(dev, w, x, M, N, K, True, DTYPE_BF16, DTYPE_F32)
+    want = o.c_qmatmul(x, w, N, K, True)
+    for m in range(M):
+        if m == 3:
+            assert not got[m].any()
+        else:
+            assert o.rel_l2(got[m], want[m]) < 1e-4, m
 
 
 # ----------------------------------------------------------------------------- single-token kernel (K = 2048 / 4096)

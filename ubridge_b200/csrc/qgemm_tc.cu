@@ -78,6 +78,51 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
   return false;
 }
 
+// The same bounded wait with acquire semantics at cluster scope: what other CTAs of the cluster wrote into this
+// CTA's shared memory before their (release) arrivals is visible afterwards.
+__device__ __forceinline__ bool tc_mbar_try_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool tc_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (tc_mbar_try_cluster(bar, parity)) return true;
+  for (uint32_t i = 0; i < kTcWaitLimit; i++) {
+    if (tc_mbar_try_cluster(bar, parity)) return true;
+    if (i > 16) __nanosleep(i > 256 ? 256 : 32);
+    if ((i & 255) == 255 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+// address of this CTA's shared-memory location `addr` in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t tc_peer_addr(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void tc_peer_arrive(uint32_t peer_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_bar) : "memory");
+}
+// four bytes into another CTA's shared memory, counted on a barrier of that CTA (no fence on this side)
+__device__ __forceinline__ void tc_peer_store_tx(uint32_t peer_addr, uint32_t v, uint32_t peer_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(peer_addr), "r"(v),
+               "r"(peer_bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the same without ordering memory: only "every CTA of the cluster has come this far"
+__device__ __forceinline__ void tc_cluster_sync_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
   // K-major, 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), LBO unused (1), descriptor version 1
   uint64_t d = 0;
@@ -162,6 +207,13 @@ constexpr int tc_wstages(int tok, int ctas, int wst = 0) { return wst ? wst : ((
 constexpr int tc_stage_tok(int tok, int ctas) {  // staging rows
   return (tok > 128 || ctas > 1) ? 64 : (tok < 128 ? tok : 128);
 }
+// Shared memory of a launch: token stages, output staging tile (none with a K split: those store from registers),
+// packed-weight ring, f32 partial sums of a K split ([source rank][TOK / KS tokens][128 rows]), 1 KB for alignment.
+constexpr size_t tc_smem_bytes(int tok, int stages, int ctas, int wst, int fmt, int ks) {
+  return static_cast<size_t>(stages) * (tok * 128) + (ks > 1 ? 0 : static_cast<size_t>(tc_stage_tok(tok, ctas)) * 256) +
+         static_cast<size_t>(tc_wstages(tok, ctas, wst)) * (128 * (fmt ? 8 * 34 : 144)) +
+         (ks > 1 ? static_cast<size_t>(tok) * 512 : 0) + 1024;
+}
 // One slot of the packed-weight ring holds 256 K values of 128 rows: a Q4_K super-block (144 bytes) or eight
 // Q8_0 blocks (272 bytes, the shortest run of 34-byte blocks that is a whole number of 16-byte pieces).
 constexpr uint32_t kTcQ8RowBytes = 8 * 34;
@@ -188,6 +240,7 @@ struct TcRun {
 struct TcShared {
   unsigned long long full[kTcMaxStages], empty[kTcMaxStages], tmem_full[2], tmem_empty[2];
   unsigned long long wfull[kTcWStages], wempty[kTcWStages];
+  unsigned long long pfull, pempty;  // partial sums of a K split: all arrived here / all read everywhere else
   uint32_t tmem_base;
   int abort_flag;
   int nruns;
@@ -203,11 +256,26 @@ struct TcShared {
 // help (MoE layer of 256 tokens, one CTA per SM: 3 -> 5 slots 589 -> 567 us; dense M = 2048: 2 -> 4 slots no
 // change), the packed tiles are not what a K step waits for.
 // FMT: 0 = Q4_K super-blocks, 1 = Q8_0 blocks (dense mode only).
-template <int TOK, int STAGES, int MODE, int CTAS, int WST, int FMT, int SETS>
+// KS: K split (dense mode, up to 64 tokens).  A tile then belongs to a thread-block cluster of KS CTAs, each of which
+// runs K / KS of the reduction into an accumulator of its own.  With so few tokens a K step costs the same 0.4 us of
+// barrier round trips whatever it computes, and 14336 rows are only 112 tiles: the split puts more of those chains
+// side by side (two CTAs per SM).  The partial sums meet in shared memory: token t of the tile belongs to rank
+// t % KS, every rank writes its 128 partial sums of that token into the owner's buffer (st.async, counted in bytes on
+// a barrier of the owner), and the owner adds the KS slots in rank order (deterministic) and stores the row.
+// These launches also overlap with their neighbours in the stream (programmatic dependent launch): barriers and
+// tensor memory are set up before the dependency wait, every access to global memory comes after it.
+template <int TOK, int STAGES, int MODE, int CTAS, int WST, int FMT, int SETS, int KS>
 __global__ void __launch_bounds__(tc_threads(SETS), CTAS)
 qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err_word,
                     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                     const TcGroup grp) {
+  if (KS > 1) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 0) {  // the copies' descriptors are on their way before the first copy needs them
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&x_map)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&w_map)) : "memory");
+    }
+  }
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   __shared__ TcShared sh;
   __shared__ TcRun runs[MODE == 0 ? 1 : kTcMaxRuns];
@@ -222,8 +290,10 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   constexpr uint32_t kTcWBytes = tc_wbytes(FMT);
   constexpr uint32_t kWRow = tc_wrow(FMT);
   constexpr uint32_t kStagingOff = STAGES * kBBytes;   // [kStageTok tokens][128 weight rows] bf16
-  constexpr uint32_t kWOff = kStagingOff + kStageTok * 256;  // packed weight ring: [128 rows][144 bytes] each
-  constexpr int kAccBufs = (TOK > 128 || CTAS > 1) ? 1 : 2;  // accumulator buffers at the start of the allocation
+  constexpr uint32_t kWOff = kStagingOff + (KS > 1 ? 0 : kStageTok * 256);  // packed weight ring: [128 rows][144 bytes] each
+  constexpr uint32_t kPartOff = kWOff + kWStages * kTcWBytes;  // [KS source ranks][TOK / KS tokens][128 rows] f32
+  static_assert(KS == 1 || (MODE == 0 && TOK <= 64 && TOK % KS == 0), "K split: dense mode, few tokens");
+  constexpr int kAccBufs = (TOK > 128 || CTAS > 1 || KS > 1) ? 1 : 2;  // accumulator buffers at the start of the allocation
   constexpr uint32_t kAccStride = 128;
   constexpr uint32_t kTmemCols = CTAS > 1 ? 256 : 512;        // columns this CTA allocates
   constexpr uint32_t kATmemCol = CTAS > 1 ? 128 : 256;        // first column of the weight stages (32 each)
@@ -240,11 +310,17 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   auto tempty_bar = [&](int b) { return bars + 16u * kTcMaxStages + 16u + 8u * b; };
   auto wfull_bar = [&](int b) { return bars + 16u * kTcMaxStages + 32u + 8u * b; };
   auto wempty_bar = [&](int b) { return bars + 16u * kTcMaxStages + 32u + 8u * kTcWStages + 8u * b; };
+  const uint32_t pfull_bar = bars + 16u * kTcMaxStages + 32u + 16u * kTcWStages;
+  const uint32_t pempty_bar = pfull_bar + 8u;
+  // K split: rank of this CTA in its cluster (= which part of K it takes); clusters walk over the tiles
+  uint32_t krank = 0;
+  if (KS > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(krank));
+  const int vblock = static_cast<int>(blockIdx.x) / KS, vgrid = static_cast<int>(gridDim.x) / KS;
   volatile int* abort_flag = &sh.abort_flag;
 
   constexpr int kTileCols = MODE == 1 ? 64 : 128;  // output columns per tile
   const int w_tiles = (N + kTileCols - 1) / kTileCols, t_tiles = (M + TOK - 1) / TOK;
-  const int ksteps = K / kTcBK;
+  const int ksteps = K / kTcBK / KS;  // of this CTA
 
   if (MODE != 0) {
     // Token runs: consecutive alignment blocks of one expert, merged up to TOK tokens.  Every CTA builds
@@ -298,10 +374,13 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
       tc_mbar_init(wfull_bar(b), 1);
       tc_mbar_init(wempty_bar(b), kTcProducerWarps * SETS);
     }
+    tc_mbar_init(pfull_bar, 1);
+    tc_mbar_init(pempty_bar, (KS - 1) * 128 + (KS == 1));
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (KS > 1) tc_cluster_sync();  // the other ranks' barriers exist before anything arrives on them
   if (warp == 0) {
     const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(&sh.tmem_base));
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(kTmemCols) : "memory");
@@ -311,6 +390,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = sh.tmem_base;
+  // everything below reads what the previous kernel may have written or writes what it may still read
+  if (KS > 1) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ MMA issuer
@@ -319,7 +400,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
       uint32_t phase = 0, acc_phase = 0;
       int buf = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      for (int tile = vblock; tile < ntiles && ok; tile += vgrid) {
         int m0_, valid, wrow0_, n0_;
         tile_info(tile, m0_, valid, wrow0_, n0_);
         // UMMA N = the tile's valid tokens rounded up to 16 (a ragged last tile costs less)
@@ -362,6 +443,76 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     uint32_t acc_phase = 0;
     int buf = 0;
     bool ok = true;
+    if constexpr (KS > 1) {
+      // K split: partial sums to their owners, then this rank's tokens (t % KS == krank) summed in rank order
+      constexpr int kSlots = TOK / KS;  // tokens a rank owns at most
+      const int row = lane_base + lane;
+      const uint32_t part_s = smem_base + kPartOff;
+      const float* const part = reinterpret_cast<const float*>(tiles + kPartOff);
+      uint32_t it = 0;
+      auto agree = [&](bool mine_ok) {  // the four warps take the same decision
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(all_ok)
+            : "r"(mine_ok ? 1u : 0u)
+            : "memory");
+        return all_ok != 0;
+      };
+      for (int tile = vblock; tile < ntiles && ok; tile += vgrid, it++) {
+        int m0, valid, wrow0_, n0;
+        tile_info(tile, m0, valid, wrow0_, n0);
+        bool mine = tc_wait(tfull_bar(0), acc_phase, abort_flag);
+        // the buffers everywhere have been read for the previous tile before anybody writes them again
+        if (mine && it > 0) mine = tc_wait_cluster(pempty_bar, (it - 1) & 1, abort_flag);
+        ok = agree(mine);
+        if (!ok) break;
+        // bytes the other ranks will send for the tokens this rank owns
+        if (warp == 1 && lane == 0) {
+          const int nown = (valid - static_cast<int>(krank) + KS - 1) / KS;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pfull_bar),
+                       "r"(static_cast<uint32_t>((KS - 1) * (nown > 0 ? nown : 0) * 512))
+                       : "memory");
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int c = 0; c < valid; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + c, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int t = c + j;
+            if (t < valid) {
+              const uint32_t owner = static_cast<uint32_t>(t) & (KS - 1);
+              const uint32_t a = part_s + ((krank * kSlots + (t / KS)) * 128 + row) * 4;
+              if (owner == krank)
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v[j]) : "memory");
+              else
+                tc_peer_store_tx(tc_peer_addr(a, owner), v[j], tc_peer_addr(pfull_bar, owner));
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) tc_mbar_arrive(tempty_bar(0));  // this warp's lanes of the accumulator are drained
+        acc_phase ^= 1;
+        ok = agree(tc_wait_cluster(pfull_bar, it & 1, abort_flag));
+        if (!ok) break;
+        for (int t = krank, i = 0; t < valid; t += KS, i++) {
+          float f = 0.f;
+#pragma unroll
+          for (int r = 0; r < KS; r++) f += part[(r * kSlots + i) * 128 + row];
+          if (n0 + row < N) y[static_cast<size_t>(m0 + t) * N + n0 + row] = __float2bfloat16_rn(f);
+        }
+        if (tile + vgrid < ntiles) {  // the buffers here may be written for the next tile
+#pragma unroll
+          for (uint32_t d = 0; d < KS; d++)
+            if (d != krank) tc_peer_arrive(tc_peer_addr(pempty_bar, d));
+        }
+      }
+    } else
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int m0, valid, wrow0_, n0;
       tile_info(tile, m0, valid, wrow0_, n0);
@@ -467,8 +618,8 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     // weight row inside the tile = the TMEM lane this warp may access (32 * (warp % 4) + lane);
     // half: 0 = low nibbles (even sub-blocks), 1 = high nibbles
     const int wrow = 32 * (warp & 3) + lane, half = ((warp - 5) >> 2) & 1, set = (warp - 5) >> 3;
-    const int nsb = K >> 8;
-    const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int nsb = (K >> 8) / KS;
+    const int my_tiles = vblock < ntiles ? (ntiles - vblock + vgrid - 1) / vgrid : 0;
     const int total_sb = my_tiles * nsb;  // super-block iterations
     const unsigned char* const w_ring = tiles + kWOff + wrow * kWRow;
     const uint32_t a_lane = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kATmemCol;
@@ -580,17 +731,17 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
     // Packed weight tiles run kWStages - 1 super-blocks ahead of the token tiles; token tiles run as far
     // ahead of the MMA as the ring allows.
     if (lane == 0) {
-      const int nsb = K >> 8;
-      const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const int nsb = (K >> 8) / KS, sb0 = static_cast<int>(krank) * nsb;  // this CTA's super-blocks of a row
+      const int my_tiles = vblock < ntiles ? (ntiles - vblock + vgrid - 1) / vgrid : 0;
       const int total_sb = my_tiles * nsb;
       int s = 0, ws = 0;
       uint32_t phase = 0, wphase = 0;
       bool ok = true;
       int wq_next = 0;  // next super-block (flat index) whose packed weights have not been requested
       auto issue_w = [&]() {
-        const int ti = wq_next / nsb, sb = wq_next - ti * nsb;
+        const int ti = wq_next / nsb, sb = sb0 + wq_next - ti * nsb;
         int m0_, valid_, wrow0, n0_;
-        tile_info(blockIdx.x + ti * gridDim.x, m0_, valid_, wrow0, n0_);
+        tile_info(vblock + ti * vgrid, m0_, valid_, wrow0, n0_);
         ok = tc_wait(wempty_bar(ws), wphase ^ 1, abort_flag);
         if (!ok) return;
         const uint32_t bar = wfull_bar(ws);
@@ -616,9 +767,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
       for (int q = 0; q < total_sb && ok; q++) {
         if (wq_next < total_sb) issue_w();
         if (!ok) break;
-        const int ti = q / nsb, sb = q - ti * nsb;
+        const int ti = q / nsb, sb = sb0 + q - ti * nsb;
         int m0, valid_, wrow0_, n0_;
-        tile_info(blockIdx.x + ti * gridDim.x, m0, valid_, wrow0_, n0_);
+        tile_info(vblock + ti * vgrid, m0, valid_, wrow0_, n0_);
         for (int G = 0; G < 4; G++) {
           ok = tc_wait(empty_bar(s), phase ^ 1, abort_flag);
           if (!ok) break;
@@ -641,6 +792,9 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   // ---- teardown: every role arrives here, whether it finished or gave up ----
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  // nobody leaves while another rank may still write or arrive here (after a wait that gave up; otherwise every
+  // rank has received all it was sent by now)
+  if (KS > 1) tc_cluster_sync_relaxed();
   if (threadIdx.x == 0 && sh.abort_flag) report_device_error(err_word, UB_ERR_TIMEOUT);
   if (warp == 0) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -668,17 +822,17 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int TOK, int STAGES, int MODE, int CTAS = 1, int WST = 0, int FMT = 0, int SETS = 1>
+template <int TOK, int STAGES, int MODE, int CTAS = 1, int WST = 0, int FMT = 0, int SETS = 1, int KS = 1>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const TcGroup& grp, int w_rows_total,
               cudaStream_t s) {
-  constexpr size_t smem = static_cast<size_t>(STAGES) * (TOK * 128) + static_cast<size_t>(tc_stage_tok(TOK, CTAS)) * 256 +
-                          static_cast<size_t>(tc_wstages(TOK, CTAS, WST)) * tc_wbytes(FMT) + 1024;
-  static_assert(smem <= 227 * 1024, "shared memory plan");
+  constexpr size_t smem = tc_smem_bytes(TOK, STAGES, CTAS, WST, FMT, KS);
+  static_assert(smem <= 227 * 1024 / CTAS, "shared memory plan");
   const int sms = ub::num_sms();
   int grid = sms * CTAS;  // grouped launches learn their tile count on the device; idle CTAs leave at once
   if (MODE == 0) {
     const int tiles = ((N + 127) / 128) * ((M + TOK - 1) / TOK);
-    grid = tiles < sms ? tiles : sms;
+    const int slots = KS > 1 ? sms * CTAS / KS : sms;  // clusters (CTAs) resident at once
+    grid = (tiles < slots ? tiles : slots) * KS;
   }
   // token matrix as a 2-D tensor map: inner dimension K (bf16), outer M; box = 64 x TOK, 128-byte swizzle;
   // rows beyond M read as zeros
@@ -707,11 +861,28 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ub::fail(UB_ERR_UNSUPPORTED);
-  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS, WST, FMT, SETS>;
+  auto kernel = qgemm_q4k_tc_kernel<TOK, STAGES, MODE, CTAS, WST, FMT, SETS, KS>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
+  }
+  if (KS > 1) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid), cfg.blockDim = dim3(tc_threads(SETS)), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = KS, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 2;
+    e = cudaLaunchKernelEx(&cfg, kernel, static_cast<__nv_bfloat16*>(y), M, N, K, ub::device_error_word(), map, wmap, grp);
+    if (e != cudaSuccess) {
+      ub::set_cuda_error(e);
+      return ub::fail(UB_ERR_CUDA);
+    }
+    return ub::check_launch();
   }
   kernel<<<grid, tc_threads(SETS), smem, s>>>(static_cast<__nv_bfloat16*>(y), M, N, K, ub::device_error_word(), map, wmap,
                                         grp);
@@ -745,7 +916,19 @@ void* tensor_map_encoder() { return reinterpret_cast<void*>(encode_tiled_fn()); 
 // Returns UB_ERR_UNSUPPORTED when the driver offers no tensor-map encoder (the caller falls back).
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
   const TcGroup none = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
-  if (M <= 64) return launch_tc<64, 6, 0>(y, x, wq, M, N, K, none, N, s);
+  if (M <= 64) {
+    // few tokens: K split over clusters, two CTAs per SM; the widest split that still fills one round of CTA slots
+    const int tiles = (N + 127) / 128, slots = 2 * ub::num_sms(), nsb = K / UB_QK_K;
+    // Measured on B200 at 16 tokens: 14336x4096 27.4 us unsplit, 23.1 us in two; 4096x4096 26.4 / 19.3 / 12.7 / 11.3 us
+    // unsplit / in two / four / eight.
+    int ks = 1;
+    while (ks < 8 && tiles * (2 * ks) <= slots && nsb % (2 * ks) == 0 && nsb / (2 * ks) >= 2) ks *= 2;
+    if (ks == 1 && nsb % 2 == 0) ks = 2;
+    if (ks == 8) return launch_tc<64, 4, 0, 2, 0, 0, 1, 8>(y, x, wq, M, N, K, none, N, s);
+    if (ks == 4) return launch_tc<64, 4, 0, 2, 0, 0, 1, 4>(y, x, wq, M, N, K, none, N, s);
+    if (ks == 2) return launch_tc<64, 4, 0, 2, 0, 0, 1, 2>(y, x, wq, M, N, K, none, N, s);
+    return launch_tc<64, 6, 0>(y, x, wq, M, N, K, none, N, s);
+  }
   if (M <= 128) return launch_tc<128, 6, 0>(y, x, wq, M, N, K, none, N, s);
   return launch_tc<256, 5, 0>(y, x, wq, M, N, K, none, N, s);
 }
@@ -758,7 +941,15 @@ int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cud
 int q8_0_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
   if (K % UB_QK_K || (reinterpret_cast<uintptr_t>(wq) & 15)) return UB_ERR_UNSUPPORTED;
   const TcGroup none = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
-  if (M <= 64) return launch_tc<64, 6, 0, 1, 0, 1>(y, x, wq, M, N, K, none, N, s);
+  if (M <= 64) {
+    const int tiles = (N + 127) / 128, slots = ub::num_sms(), nsb = K / UB_QK_K;
+    int ks = 1;
+    while (ks < 8 && tiles * (2 * ks) <= slots && nsb % (2 * ks) == 0 && nsb / (2 * ks) >= 2) ks *= 2;
+    if (ks == 8) return launch_tc<64, 6, 0, 1, 0, 1, 1, 8>(y, x, wq, M, N, K, none, N, s);
+    if (ks == 4) return launch_tc<64, 6, 0, 1, 0, 1, 1, 4>(y, x, wq, M, N, K, none, N, s);
+    if (ks == 2) return launch_tc<64, 6, 0, 1, 0, 1, 1, 2>(y, x, wq, M, N, K, none, N, s);
+    return launch_tc<64, 6, 0, 1, 0, 1>(y, x, wq, M, N, K, none, N, s);
+  }
   if (M <= 128) return launch_tc<128, 6, 0, 1, 2, 1>(y, x, wq, M, N, K, none, N, s);
   return launch_tc<256, 4, 0, 1, 0, 1>(y, x, wq, M, N, K, none, N, s);
 }

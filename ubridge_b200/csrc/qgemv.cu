@@ -938,6 +938,8 @@ int q4k_gemv_mt(const void* wq, const XT* x, void* y, int M, int N, int K, int y
 template <typename XT>
 int q8_0_gemv_m1(const void* wq, const XT* x, void* y, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
 template <typename XT>
+int q4k_gemv_mc(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+template <typename XT>
 int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh,
              const ArParams* ar, cudaStream_t s);
 
@@ -964,6 +966,16 @@ int qgemv_ar(bool is_q4k, void* y, const XT* x, const void* wq, int M, int N, in
     void* yp = static_cast<char*>(y) + static_cast<size_t>(m0) * N * dtype_size(y_dtype);
     int st;
     if ((reinterpret_cast<uintptr_t>(wq) & 15) == 0) {
+      // five to eight tokens at K = 2048 / 4096 / 8192: tokens in the MMA columns, one pass
+      if (is_q4k && !ar && left >= 5) {
+        const int mc = left >= 8 ? 8 : left;
+        st = q4k_gemv_mc<XT>(wq, xp, yp, mc, N, K, y_dtype, fresh, s);
+        if (st == UB_OK) {
+          m0 += mc;
+          continue;
+        }
+        if (st != UB_ERR_UNSUPPORTED) return st;
+      }
       const int mi = left >= 8 ? 8 : left;
       // one token, or two to four at K = 2048 / 4096: the two-CTAs-per-SM kernels; everything else: the
       // one-CTA-per-SM kernels with token pairs / quads
