@@ -11,7 +11,7 @@ streams its weights from HBM); one STEP replays that graph k times, k chosen so 
 to see them.  k is stated in config.workload.
 
 With the default workload the line also carries
-  secondary  (one GPU) the other single-GPU configurations: c1, c2_m4, c2_m16, c3
+  secondary  (one GPU) the other single-GPU configurations: c1, c2_m4, c2_m8, c2_m16, c3
   sharded    (any number of GPUs) the strong-scaling configurations at this GPU count: c5_m1, c5_m512
              (tensor parallel) and c4 (expert parallel), run in the same process group
 (--no-extras leaves both out).
@@ -28,7 +28,7 @@ Printed JSON (one line, rank 0):
 `--impl reference` times that CPU path alone (the reference's own kernels need the vendor toolchain
 and device, so the CPU restatement is the only reference arm that can run).
 
-Other workloads (c1, c2_m4, c2_m16, c3, c4, c5_m1, c5_m512; q6k_m1 for the Q6_K decode kernel) print the same
+Other workloads (c1, c2_m4, c2_m8, c2_m16, c3, c4, c5_m1, c5_m512; q6k_m1 for the Q6_K decode kernel) print the same
 line for the other configurations.  The linear workloads run one replica per GPU (weak scaling); c4 (MoE layer) and c5
 (70B-shaped linear stack) shard over the ranks (expert / tensor parallel, strong scaling) with NCCL
 all-reduces through the eccl entry points.
@@ -244,6 +244,8 @@ WORKLOADS = {
                   desc="Q4_K 14336x4096 decode GEMV, bf16 activations, M=1"),
     "c2_m4": dict(N=14336, K=4096, M=4, is_q4k=True, x_bf16=True, unit="GB/s", seed=1002, copies=32,
                   desc="Q4_K 14336x4096 small-batch decode, M=4"),
+    "c2_m8": dict(N=14336, K=4096, M=8, is_q4k=True, x_bf16=True, unit="GB/s", seed=1002, copies=32,
+                  desc="Q4_K 14336x4096 small-batch decode, M=8"),
     "c2_m16": dict(N=14336, K=4096, M=16, is_q4k=True, x_bf16=True, unit="GB/s", seed=1002, copies=32,
                    desc="Q4_K 14336x4096 small-batch decode, M=16"),
     "q6k_m1": dict(N=14336, K=4096, M=1, is_q4k=False, fmt="Q6_K", x_bf16=True, unit="GB/s", seed=1006, copies=16,
@@ -758,7 +760,7 @@ def short_record(wl_name, wl, n_gpus, res):
 
 
 METRIC_OF = {"GB/s": "weight_GBps", "TFLOP/s": "TFLOPS", "tok/s": "moe_tokens_per_s"}
-SECONDARY = ["c1", "c2_m4", "c2_m16", "c3"]   # single-GPU configurations carried by the default line
+SECONDARY = ["c1", "c2_m4", "c2_m8", "c2_m16", "c3"]   # single-GPU configurations carried by the default line
 SHARDED = ["c5_m1", "c5_m512", "c4"]          # strong-scaling configurations carried at every GPU count
 
 

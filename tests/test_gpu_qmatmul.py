@@ -456,7 +456,7 @@ def test_quantize_then_matmul_back_to_back(dev):
         assert o.rel_l2(got, want) < 1e-4
 
 
-@pytest.mark.parametrize("M,K", [(1, 4096), (2, 4096), (1, 8192)])
+@pytest.mark.parametrize("M,K", [(1, 4096), (2, 4096), (1, 8192), (6, 4096)])
 def test_repack_then_q4k_matmul_back_to_back(dev, M, K):
     from ubridge_b200._lib import UB_QMATMUL_WEIGHTS_FRESH
 
@@ -479,6 +479,32 @@ def test_repack_then_q4k_matmul_back_to_back(dev, M, K):
                     stream=dev.stream)
         got = dev.dtoh_sync_copy(d_y, np.float32, (M, N))
         assert o.rel_l2(got, want) < 1e-4
+
+
+@pytest.mark.parametrize("M", [16, 40])
+def test_repack_then_tensor_core_matmul_back_to_back(dev, M):
+    """The K-split launches request their first weight tiles ahead of the dependency wait unless the weights are
+    fresh: the library tracks its own weight-writing entry points, callers with their own pass the flag."""
+    from ubridge_b200._lib import UB_QMATMUL_WEIGHTS_FRESH
+
+    rng = np.random.default_rng(19)
+    N, K = 2048, 4096
+    w = o.gen_q4k_weight(rng, N, K)
+    x = o.gen_activation(rng, M, K, True)
+    want = x @ o.c_dequant(w, True).reshape(N, K).T
+    nblocks = N * K // 256
+    d_w = dev.htod_sync_copy(w)
+    d_split = dev.alloc(w.size)
+    ops.repack_to_split(d_split, d_w, nblocks, True, stream=dev.stream)
+    d_x = dev.htod_sync_copy(to_storage(x, DTYPE_BF16))
+    d_y = dev.alloc(M * N * 2)
+    for flag in (0, UB_QMATMUL_WEIGHTS_FRESH):
+        d_w2 = dev.alloc_zeros(w.size)
+        dev.synchronize()
+        ops.repack_to_interleaved(d_w2, d_split, nblocks, True, stream=dev.stream)
+        ops.qmatmul(d_y, d_x, d_w2, M, N, K, is_q4k=True, x_dtype=DTYPE_BF16, out_dtype=DTYPE_BF16 | flag,
+                    stream=dev.stream)
+        assert o.rel_l2(fetch(dev, d_y, DTYPE_BF16, (M, N)), want) < 5e-3
 
 
 @pytest.mark.parametrize("x_dtype", [DTYPE_F32, DTYPE_BF16])

@@ -266,7 +266,7 @@ struct TcShared {
 // tensor memory are set up before the dependency wait, every access to global memory comes after it.
 template <int TOK, int STAGES, int MODE, int CTAS, int WST, int FMT, int SETS, int KS>
 __global__ void __launch_bounds__(tc_threads(SETS), CTAS)
-qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err_word,
+qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int early, int* err_word,
                     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                     const TcGroup grp) {
   if (KS > 1) {
@@ -390,8 +390,11 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = sh.tmem_base;
-  // everything below reads what the previous kernel may have written or writes what it may still read
-  if (KS > 1) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Everything below reads what the previous kernel may have written or writes what it may still read; only the
+  // thread that issues the copies first requests its first packed weight tiles (early: nothing on the stream
+  // writes the weights), whose way from memory is the longest wait of a launch.
+  const bool copy_warp = warp > 4 + kTcProducerWarps * SETS;
+  if (KS > 1 && !(early && copy_warp)) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ MMA issuer
@@ -764,6 +767,7 @@ qgemm_q4k_tc_kernel(__nv_bfloat16* __restrict__ y, int M, int N, int K, int* err
         }
       };
       for (int i = 0; i < kWStages - 1 && wq_next < total_sb && ok; i++) issue_w();
+      if (KS > 1 && early) asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int q = 0; q < total_sb && ok; q++) {
         if (wq_next < total_sb) issue_w();
         if (!ok) break;
@@ -824,7 +828,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 template <int TOK, int STAGES, int MODE, int CTAS = 1, int WST = 0, int FMT = 0, int SETS = 1, int KS = 1>
 int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const TcGroup& grp, int w_rows_total,
-              cudaStream_t s) {
+              cudaStream_t s, int early = 0) {
   constexpr size_t smem = tc_smem_bytes(TOK, STAGES, CTAS, WST, FMT, KS);
   static_assert(smem <= 227 * 1024 / CTAS, "shared memory plan");
   const int sms = ub::num_sms();
@@ -877,15 +881,16 @@ int launch_tc(void* y, const void* x, const void* wq, int M, int N, int K, const
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr, cfg.numAttrs = 2;
-    e = cudaLaunchKernelEx(&cfg, kernel, static_cast<__nv_bfloat16*>(y), M, N, K, ub::device_error_word(), map, wmap, grp);
+    e = cudaLaunchKernelEx(&cfg, kernel, static_cast<__nv_bfloat16*>(y), M, N, K, early, ub::device_error_word(), map, wmap,
+                           grp);
     if (e != cudaSuccess) {
       ub::set_cuda_error(e);
       return ub::fail(UB_ERR_CUDA);
     }
     return ub::check_launch();
   }
-  kernel<<<grid, tc_threads(SETS), smem, s>>>(static_cast<__nv_bfloat16*>(y), M, N, K, ub::device_error_word(), map, wmap,
-                                        grp);
+  kernel<<<grid, tc_threads(SETS), smem, s>>>(static_cast<__nv_bfloat16*>(y), M, N, K, 0, ub::device_error_word(), map,
+                                        wmap, grp);
   return ub::check_launch();
 }
 
@@ -914,19 +919,20 @@ void* tensor_map_encoder() { return reinterpret_cast<void*>(encode_tiled_fn()); 
 
 // y (bf16) [M,N] = x (bf16) [M,K] . dequant(Wq)^T on tcgen05; K % 256 == 0, pointers 16-byte aligned.
 // Returns UB_ERR_UNSUPPORTED when the driver offers no tensor-map encoder (the caller falls back).
-int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
+int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, bool fresh, cudaStream_t s) {
   const TcGroup none = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
   if (M <= 64) {
     // few tokens: K split over clusters, two CTAs per SM; the widest split that still fills one round of CTA slots
     const int tiles = (N + 127) / 128, slots = 2 * ub::num_sms(), nsb = K / UB_QK_K;
+    const int early = fresh ? 0 : 1;
     // Measured on B200 at 16 tokens: 14336x4096 27.4 us unsplit, 23.1 us in two; 4096x4096 26.4 / 19.3 / 12.7 / 11.3 us
     // unsplit / in two / four / eight.
     int ks = 1;
     while (ks < 8 && tiles * (2 * ks) <= slots && nsb % (2 * ks) == 0 && nsb / (2 * ks) >= 2) ks *= 2;
     if (ks == 1 && nsb % 2 == 0) ks = 2;
-    if (ks == 8) return launch_tc<64, 4, 0, 2, 0, 0, 1, 8>(y, x, wq, M, N, K, none, N, s);
-    if (ks == 4) return launch_tc<64, 4, 0, 2, 0, 0, 1, 4>(y, x, wq, M, N, K, none, N, s);
-    if (ks == 2) return launch_tc<64, 4, 0, 2, 0, 0, 1, 2>(y, x, wq, M, N, K, none, N, s);
+    if (ks == 8) return launch_tc<64, 4, 0, 2, 0, 0, 1, 8>(y, x, wq, M, N, K, none, N, s, early);
+    if (ks == 4) return launch_tc<64, 4, 0, 2, 0, 0, 1, 4>(y, x, wq, M, N, K, none, N, s, early);
+    if (ks == 2) return launch_tc<64, 4, 0, 2, 0, 0, 1, 2>(y, x, wq, M, N, K, none, N, s, early);
     return launch_tc<64, 6, 0>(y, x, wq, M, N, K, none, N, s);
   }
   if (M <= 128) return launch_tc<128, 6, 0>(y, x, wq, M, N, K, none, N, s);
@@ -938,16 +944,17 @@ int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cud
 // packed ring leave room for four token stages at 256 tokens.  Measured on B200, 4096x4096 with 512 tokens
 // (64 tiles of 256 tokens on 148 SMs): 505 TFLOP/s; with 128-token tiles (128 tiles) 400: the producers'
 // work per flop doubles, which costs more than the idle SMs.
-int q8_0_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s) {
+int q8_0_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, bool fresh, cudaStream_t s) {
   if (K % UB_QK_K || (reinterpret_cast<uintptr_t>(wq) & 15)) return UB_ERR_UNSUPPORTED;
   const TcGroup none = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
   if (M <= 64) {
     const int tiles = (N + 127) / 128, slots = ub::num_sms(), nsb = K / UB_QK_K;
+    const int early = fresh ? 0 : 1;
     int ks = 1;
     while (ks < 8 && tiles * (2 * ks) <= slots && nsb % (2 * ks) == 0 && nsb / (2 * ks) >= 2) ks *= 2;
-    if (ks == 8) return launch_tc<64, 6, 0, 1, 0, 1, 1, 8>(y, x, wq, M, N, K, none, N, s);
-    if (ks == 4) return launch_tc<64, 6, 0, 1, 0, 1, 1, 4>(y, x, wq, M, N, K, none, N, s);
-    if (ks == 2) return launch_tc<64, 6, 0, 1, 0, 1, 1, 2>(y, x, wq, M, N, K, none, N, s);
+    if (ks == 8) return launch_tc<64, 6, 0, 1, 0, 1, 1, 8>(y, x, wq, M, N, K, none, N, s, early);
+    if (ks == 4) return launch_tc<64, 6, 0, 1, 0, 1, 1, 4>(y, x, wq, M, N, K, none, N, s, early);
+    if (ks == 2) return launch_tc<64, 6, 0, 1, 0, 1, 1, 2>(y, x, wq, M, N, K, none, N, s, early);
     return launch_tc<64, 6, 0, 1, 0, 1>(y, x, wq, M, N, K, none, N, s);
   }
   if (M <= 128) return launch_tc<128, 6, 0, 1, 2, 1>(y, x, wq, M, N, K, none, N, s);

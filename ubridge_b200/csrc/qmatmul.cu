@@ -33,8 +33,8 @@ int q4k_gemv_m1x(const void* wq, const XT* x, void* y, int N, int K, int y_dtype
 int q4k_gemm_mma(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
 uint32_t oneshot_spin_limit();
 void* tensor_map_encoder();
-int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
-int q8_0_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, cudaStream_t s);
+int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, bool fresh, cudaStream_t s);
+int q8_0_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, bool fresh, cudaStream_t s);
 bool q4k_gemv_mc_supported(int M, int K);
 }  // namespace ub
 
@@ -113,7 +113,7 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
 
   if (is_q4k && M > kDecodeOnePassM && M <= kDecodeMaxM && x_dtype == UB_DTYPE_BF16 && out_dtype == UB_DTYPE_BF16 &&
       !ub::q4k_gemv_mc_supported(M, K)) {
-    const int st = ub::q4k_gemm_tc(y, x, wq, M, N, K, s);
+    const int st = ub::q4k_gemm_tc(y, x, wq, M, N, K, fresh, s);
     if (st != UB_ERR_UNSUPPORTED) return st;  // unsupported shape or driver: the decode kernel below
   }
   auto decode = [&]() {
@@ -146,7 +146,7 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
     xin = xb;
   }
   if (conv_out) yout = ws + align_up(static_cast<size_t>(M) * K * 2, 256);
-  int st = is_q4k ? ub::q4k_gemm_tc(yout, xin, wq, M, N, K, s) : ub::q8_0_gemm_tc(yout, xin, wq, M, N, K, s);
+  int st = is_q4k ? ub::q4k_gemm_tc(yout, xin, wq, M, N, K, fresh, s) : ub::q8_0_gemm_tc(yout, xin, wq, M, N, K, fresh, s);
   // no tensor-map encoder in this driver: the mma.sync kernel computes the same product
   if (st == UB_ERR_UNSUPPORTED && is_q4k) st = ub::q4k_gemm_mma(yout, xin, wq, M, N, K, s);
   if (st != UB_OK) return st;
