@@ -82,6 +82,44 @@ def test_matmul_odd_shapes(dev, x_dtype, M, N, K):
     assert o.rel_l2(got, want) < 1e-5  # f32 products of exact weights: only the summation order differs
 
 
+@pytest.mark.parametrize("x_dtype,out_dtype", [(DTYPE_BF16, DTYPE_F32), (DTYPE_F32, DTYPE_F32), (DTYPE_BF16, DTYPE_BF16),
+                                               (DTYPE_F32, DTYPE_F16)])
+@pytest.mark.parametrize("N,K", [(1, 4096), (9, 2048), (17, 4096), (4747, 4096), (2369, 2048), (30000, 4096), (20000, 2048)])
+def test_single_token_staged_kernel(dev, x_dtype, out_dtype, N, K):
+    """One token at K = 2048 / 4096: rows staged by bulk copies, 15-bit fixed-point activations.  Fewer rows than
+    CTAs, row ranges of unequal length, more stages per CTA than the ring has slots (30000 rows), a last stage of
+    fewer than eight rows."""
+    rng = np.random.default_rng(N + K)
+    w = o.gen_q6k_weight(rng, N, K)
+    x = o.gen_activation(rng, 1, K, x_dtype == DTYPE_BF16)
+    want = o.qmatmul_exact(x, o.dequant_q6k(w).reshape(N, K))
+    got = _matmul(dev, w, x, 1, N, K, x_dtype, out_dtype)
+    if out_dtype == DTYPE_F32:
+        assert o.rel_l2(got, want) < (1e-4 if N >= 1000 else TOL_DECODE)
+        assert np.array_equal(got, _matmul(dev, w, x, 1, N, K, x_dtype, out_dtype))  # fixed summation order
+    else:
+        assert np.array_equal(got, _expect(_matmul(dev, w, x, 1, N, K, x_dtype, DTYPE_F32), out_dtype))
+
+
+def test_single_token_staged_kernel_extreme_blocks(dev):
+    """Every bit pattern of ql, qh and the int8 scales (among them -128 and 127), zero and large activations."""
+    rng = np.random.default_rng(66)
+    N, K = 520, 4096
+    raw = rng.integers(0, 256, size=(N, K // 256, o.Q6K_BYTES), dtype=np.uint8)
+    raw[:, :, 208:210] = rng.uniform(-0.05, 0.05, size=(N, K // 256)).astype(np.float16).view(np.uint8).reshape(N, K // 256, 2)
+    raw[0, 0, 192:208] = 0x80  # scales of -128
+    raw[1, 0, 192:208] = 0x7F
+    raw[2, :, :192] = 0xFF     # q = 63 everywhere
+    raw[3, :, :192] = 0x00     # q = 0 everywhere
+    x = o.gen_activation(rng, 1, K, True)
+    x[0, :256] = 0.0
+    x[0, 256:512] *= 8192.0
+    got = _matmul(dev, raw, x, 1, N, K, DTYPE_BF16, DTYPE_F32)
+    want = o.qmatmul_exact(x, o.dequant_q6k(raw).reshape(N, K))
+    assert o.rel_l2(got, want) < 1e-4
+    assert np.allclose(got[0, :4], want[0, :4], rtol=2e-4, atol=1e-3 * np.abs(want).max())
+
+
 def test_matmul_weights_on_a_two_byte_boundary(dev):
     """GGUF tensors inside a mapped file need not start on a 4-byte boundary: the kernel's 16-bit-load path."""
     rng = np.random.default_rng(21)

@@ -7,9 +7,17 @@
 // ql[64h + 32(j & 1) + l] (upper half of the byte for j >= 2) and its top two bits at bit 2j of qh[32h + l];
 // y = (d * scales[i / 16]) * (q - 32).
 //
-// A block is 210 bytes, so nothing in it is better than 2-byte aligned: all weight loads are 16-bit ones, and
-// consecutive lanes read consecutive bytes.  The dequantisation kernel gives a lane two neighbouring l of one
-// half (eight weights), the matmul kernel four (sixteen weights).
+// A block is 210 bytes, so nothing in it is better than 2-byte aligned: all weight loads from global memory are
+// 16-bit ones, and consecutive lanes read consecutive bytes.  The dequantisation kernel gives a lane two
+// neighbouring l of one half (eight weights), the matmul kernels four (sixteen weights).
+//
+// One token with rows of 2048 or 4096 values (qgemv_q6k_m1_kernel) does not load weights through the load-store
+// unit at all: a row of K / 256 blocks is a multiple of 16 bytes there, so up to eight consecutive rows come into
+// shared memory as ONE bulk copy (cp.async.bulk, mbarrier ring, two CTAs per SM, programmatic dependent launch as
+// in the Q4_K one-token kernel), are read with aligned 32-bit shared loads (plus a funnel shift in the odd
+// blocks) and meet 15-bit block-fixed-point activations in dp4a.
+#include <string.h>
+
 #include "common.cuh"
 
 #define UB_Q6K_BYTES 210
@@ -159,8 +167,241 @@ __global__ void __launch_bounds__(256) qgemv_q6k_kernel(const uint8_t* __restric
   }
 }
 
+// ----------------------------------------------------------------------------------------------------------------
+// One token, K = 2048 or 4096.  A CTA owns a contiguous range of rows (ranges differ by at most one row) and walks
+// it in stages of up to eight rows = one bulk copy; warp w takes row w of the stage, all its super-blocks, two per
+// step (lanes 0-15 the even one, 16-31 the odd one; inside a super-block a lane owns four neighbouring l of one
+// 128-value half and all four j, i.e. 16 weights).  The four 6-bit values of a word become signed bytes 4 (q - 32)
+// without a subtraction: ql nibble << 2 | qh bits << 6, top bit flipped.  Activations are quantised once per CTA to
+// 15-bit block fixed point per 256 values (q = 254 hi + lo, two signed bytes) and stored so that a lane's sixteen
+// values are one 16-byte read per limb.  Per (row, super-block, j): two dp4a, one integer multiply-add, then the
+// int8 scale in float; d and the activation scale once per super-block.  A row's sum is added across the warp by
+// shuffles in a fixed order.
+constexpr int kQ6W = 8;            // warps per CTA = rows per stage
+constexpr int kQ6MaxStages = 4;
+constexpr uint32_t kQ6Spin = 400000;
+constexpr float kQ6XQMax = 32258.f;  // 127 * 254
+constexpr size_t kQ6DynBudget = 104 * 1024;  // two CTAs per SM
+
+__device__ __forceinline__ bool q6_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool q6_wait(uint32_t bar, uint32_t parity) {
+  if (q6_try(bar, parity)) return true;
+  for (uint32_t i = 0; i < kQ6Spin; i++) {
+    if (q6_try(bar, parity)) return true;
+    if (i >= 2) __nanosleep(40);
+  }
+  return false;
+}
+__device__ __forceinline__ uint32_t q6_pack4(int a, int b, int c, int d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+// four values from x + k (k a multiple of 4)
+__device__ __forceinline__ void q6_load4(const float* x, int k, float (&v)[4]) {
+  const float4 q = __ldg(reinterpret_cast<const float4*>(x + k));
+  v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+}
+__device__ __forceinline__ void q6_load4(const __nv_bfloat16* x, int k, float (&v)[4]) {
+  const uint2 q = __ldg(reinterpret_cast<const uint2*>(x + k));
+  v[0] = __uint_as_float(q.x << 16), v[1] = __uint_as_float(q.x & 0xFFFF0000u);
+  v[2] = __uint_as_float(q.y << 16), v[3] = __uint_as_float(q.y & 0xFFFF0000u);
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(kQ6W * 32, 2)
+qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void* __restrict__ y, int y_dtype, int N,
+                    int K, int S, int early, int* err_word) {
+  extern __shared__ __align__(128) unsigned char q6_smem[];
+  __shared__ __align__(8) unsigned long long bars[2 * kQ6MaxStages];  // full[S], empty[S]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nsb = K / UB_QK_K;
+  const uint32_t row_bytes = static_cast<uint32_t>(nsb) * UB_Q6K_BYTES, stage_bytes = kQ6W * row_bytes;
+  unsigned char* const ring = q6_smem;
+  uint4* const xhi = reinterpret_cast<uint4*>(q6_smem + static_cast<size_t>(S) * stage_bytes);  // [K / 16]
+  uint4* const xlo = xhi + K / 16;
+  float* const xsc = reinterpret_cast<float*>(xlo + K / 16);  // [nsb]
+  const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+  const uint32_t bars_s = static_cast<uint32_t>(__cvta_generic_to_shared(bars));
+  // rows of this CTA
+  const int base = N / static_cast<int>(gridDim.x), extra = N % static_cast<int>(gridDim.x);
+  const int bx = static_cast<int>(blockIdx.x);
+  const int r0 = bx * base + (bx < extra ? bx : extra), nrows = base + (bx < extra ? 1 : 0);
+  const int nst = (nrows + kQ6W - 1) / kQ6W;
+
+  // The next kernel in the stream may start as soon as every CTA of this grid has passed this point.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars_s + 8 * s), "r"(1) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars_s + 8 * (kQ6MaxStages + s)), "r"(kQ6W) : "memory");
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // stage n of this CTA = rows r0 + 8 n .. of the range -> ring slot n % S, one bulk copy
+  auto issue = [&](int n) {
+    const int rows = min(kQ6W, nrows - kQ6W * n);
+    const uint32_t bytes = static_cast<uint32_t>(rows) * row_bytes, full = bars_s + 8 * (n % S);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     ring_s + (n % S) * stage_bytes),
+                 "l"(wq + static_cast<size_t>(r0 + kQ6W * n) * row_bytes), "r"(bytes), "r"(full)
+                 : "memory");
+  };
+  const int n_early = min(min(early, S), nst);
+  if (threadIdx.x == 0)
+    for (int n = 0; n < n_early; n++) issue(n);
+
+  // everything below reads what the previous kernel may have written (x) or writes what it may still read (y)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- activations -> 15-bit block fixed point in shared memory; slot = 16 sb + 8 h + l / 4 holds the sixteen
+  // values 256 sb + 128 h + 32 j + l .. l + 3 (j = 0..3), one word per j and limb ----
+  for (int slot0 = 0; slot0 < K / 16; slot0 += kQ6W * 32) {
+    const int slot = slot0 + threadIdx.x;  // whole half-warps are inside or outside (K / 16 is a multiple of 16)
+    float v[4][4];
+    if (slot < K / 16) {
+      const int k0 = (slot >> 4) * UB_QK_K + ((slot >> 3) & 1) * 128 + (slot & 7) * 4;
+#pragma unroll
+      for (int j = 0; j < 4; j++) q6_load4(x, k0 + 32 * j, v[j]);
+    }
+    if (slot0 == 0 && threadIdx.x == 0)  // the rest of the ring goes out right behind the activation loads
+      for (int n = n_early; n < min(S, nst); n++) issue(n);
+    if (slot < K / 16) {
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) amax = fmaxf(amax, fabsf(v[j][e]));
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));  // the super-block
+      const float inv = amax > 0.f ? kQ6XQMax / amax : 0.f, inv254 = inv * (1.f / 254.f);
+      uint32_t wh[4], wl[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        int hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {  // rounding through the mantissa of 1.5 * 2^23; |lo| <= 127 either way
+          const int q = __float_as_int(fmaf(v[j][e], inv, 12582912.f)) - 0x4B400000;
+          hi[e] = __float_as_int(fmaf(v[j][e], inv254, 12582912.f)) - 0x4B400000;
+          lo[e] = q - 254 * hi[e];
+        }
+        wh[j] = q6_pack4(hi[0], hi[1], hi[2], hi[3]);
+        wl[j] = q6_pack4(lo[0], lo[1], lo[2], lo[3]);
+      }
+      xhi[slot] = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+      xlo[slot] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+      if ((slot & 15) == 0) xsc[slot >> 4] = amax * (1.f / kQ6XQMax);
+    }
+  }
+  __syncthreads();
+
+  const int sub = lane >> 4, h = (lane >> 3) & 1, lg = lane & 7;
+  bool ok = true;
+  int slot = 0, round = 0;
+#pragma unroll 1
+  for (int n = 0; n < nst; n++) {
+    if (ok) ok = q6_wait(bars_s + 8 * slot, round & 1);
+    const int rows = min(kQ6W, nrows - kQ6W * n);
+    float acc = 0.f;
+    if (warp < rows) {
+      const unsigned char* rowp = ring + static_cast<size_t>(slot) * stage_bytes + static_cast<size_t>(warp) * row_bytes;
+#pragma unroll 2
+      for (int sb = sub; sb < nsb; sb += 2) {
+        // block sb starts 2 (sb & 1) bytes past a 4-byte boundary: two aligned words and a funnel shift
+        const unsigned char* blk = rowp + sb * UB_Q6K_BYTES;
+        const uint32_t* al = reinterpret_cast<const uint32_t*>(blk - 2 * sub);
+        const int sh = 16 * sub;
+        const int ia = 16 * h + lg, ib = ia + 8, ih = 32 + 8 * h + lg;
+        const uint32_t qa = __funnelshift_r(al[ia], al[ia + 1], sh);  // low nibbles: j = 0, high: j = 2
+        const uint32_t qb = __funnelshift_r(al[ib], al[ib + 1], sh);  // low nibbles: j = 1, high: j = 3
+        const uint32_t qh = __funnelshift_r(al[ih], al[ih + 1], sh);
+        const signed char* sc = reinterpret_cast<const signed char*>(blk + 192) + 8 * h + (lg >> 2);
+        const float d = half_bits_to_f32(*reinterpret_cast<const unsigned short*>(blk + 208));
+        const uint4 xh = xhi[16 * sb + 8 * h + lg], xl = xlo[16 * sb + 8 * h + lg];
+        // signed bytes 4 (q - 32): six bits in bits 2-7, top bit flipped
+        const uint32_t w0 = (((qa << 2) & 0x3C3C3C3Cu) | ((qh << 6) & 0xC0C0C0C0u)) ^ 0x80808080u;
+        const uint32_t w1 = (((qb << 2) & 0x3C3C3C3Cu) | ((qh << 4) & 0xC0C0C0C0u)) ^ 0x80808080u;
+        const uint32_t w2 = (((qa >> 2) & 0x3C3C3C3Cu) | ((qh << 2) & 0xC0C0C0C0u)) ^ 0x80808080u;
+        const uint32_t w3 = (((qb >> 2) & 0x3C3C3C3Cu) | (qh & 0xC0C0C0C0u)) ^ 0x80808080u;
+        const int t0 = __dp4a(static_cast<int>(w0), static_cast<int>(xh.x), 0) * 254 + __dp4a(static_cast<int>(w0), static_cast<int>(xl.x), 0);
+        const int t1 = __dp4a(static_cast<int>(w1), static_cast<int>(xh.y), 0) * 254 + __dp4a(static_cast<int>(w1), static_cast<int>(xl.y), 0);
+        const int t2 = __dp4a(static_cast<int>(w2), static_cast<int>(xh.z), 0) * 254 + __dp4a(static_cast<int>(w2), static_cast<int>(xl.z), 0);
+        const int t3 = __dp4a(static_cast<int>(w3), static_cast<int>(xh.w), 0) * 254 + __dp4a(static_cast<int>(w3), static_cast<int>(xl.w), 0);
+        float f = static_cast<float>(t0) * static_cast<float>(sc[0]);
+        f = fmaf(static_cast<float>(t1), static_cast<float>(sc[2]), f);
+        f = fmaf(static_cast<float>(t2), static_cast<float>(sc[4]), f);
+        f = fmaf(static_cast<float>(t3), static_cast<float>(sc[6]), f);
+        acc = fmaf(f, d * (0.25f * xsc[sb]), acc);
+      }
+    }
+    // everything this warp needs from the stage has been read: hand the slot back
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bars_s + 8 * (kQ6MaxStages + slot)) : "memory");
+    if ((n & (kQ6W - 1)) == warp && n + S < nst) {
+      if (ok) ok = q6_wait(bars_s + 8 * (kQ6MaxStages + slot), round & 1);
+      if (ok && lane == 0) issue(n + S);
+    }
+    if (warp < rows) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+      if (lane == 0) {
+        const size_t at = static_cast<size_t>(r0 + kQ6W * n + warp);
+        if (y_dtype == UB_DTYPE_F32) static_cast<float*>(y)[at] = acc;
+        else if (y_dtype == UB_DTYPE_BF16) static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(acc);
+        else static_cast<__half*>(y)[at] = __float2half_rn(acc);
+      }
+    }
+    if (++slot == S) slot = 0, round++;
+  }
+  if (!ok && lane == 0) report_device_error(err_word, UB_ERR_TIMEOUT);
+}
+
+// One token at K = 2048 / 4096 with 16-byte aligned weights; UB_ERR_UNSUPPORTED for everything else.
+template <typename XT>
+int launch_q6k_m1(const uint8_t* w, const XT* x, void* y, int N, int K, int out_dtype, bool fresh, cudaStream_t s) {
+  if ((K != 2048 && K != 4096) || (reinterpret_cast<uintptr_t>(w) & 15)) return UB_ERR_UNSUPPORTED;
+  const size_t row_bytes = static_cast<size_t>(K / UB_QK_K) * UB_Q6K_BYTES, stage_bytes = kQ6W * row_bytes;
+  const size_t xbytes = static_cast<size_t>(K / 16) * 32 + static_cast<size_t>(K / UB_QK_K) * 4;
+  int S = static_cast<int>((kQ6DynBudget - xbytes) / stage_bytes);
+  if (S > kQ6MaxStages) S = kQ6MaxStages;
+  if (S < 2) return UB_ERR_UNSUPPORTED;
+  const size_t smem = static_cast<size_t>(S) * stage_bytes + xbytes;
+  auto kernel = qgemv_q6k_m1_kernel<XT>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  const int slots = 2 * ub::num_sms(), want = (N + kQ6W - 1) / kQ6W;
+  const int grid = want < slots ? want : slots;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kQ6W * 32), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, w, x, y, out_dtype, N, K, S, fresh ? 0 : 1, ub::device_error_word());
+  if (e != cudaSuccess) {
+    ub::set_cuda_error(e);
+    return ub::fail(UB_ERR_CUDA);
+  }
+  return ub::check_launch();
+}
+
 template <typename XT>
 int q6k_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int out_dtype, cudaStream_t s) {
+  // UB_QMATMUL_WEIGHTS_FRESH rides in the upper bits of out_dtype, as in ub_qmatmul_*
+  bool fresh = (out_dtype & UB_QMATMUL_WEIGHTS_FRESH) != 0;
+  out_dtype &= ~UB_QMATMUL_WEIGHTS_FRESH;
   if (M == 0 || N == 0) return ub::fail(UB_OK);
   if (!y || !x || !wq || M < 0 || N < 0 || K <= 0 || K % UB_QK_K) return ub::fail(UB_ERR_INVALID_ARG);
   if (out_dtype != UB_DTYPE_F32 && out_dtype != UB_DTYPE_BF16 && out_dtype != UB_DTYPE_F16)
@@ -170,6 +411,11 @@ int q6k_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int ou
   const int esz = out_dtype == UB_DTYPE_F32 ? 4 : 2;
   const int grid = (N + 8 * kQ6kRowsPerWarp - 1) / (8 * kQ6kRowsPerWarp);  // the CTA scheduler evens out the load
   const uint8_t* w = static_cast<const uint8_t*>(wq);
+  if (ub::take_weights_written(s)) fresh = true;
+  if (M == 1) {
+    const int st = launch_q6k_m1<XT>(w, x, y, N, K, out_dtype, fresh, s);
+    if (st != UB_ERR_UNSUPPORTED) return st;
+  }
   for (int m0 = 0; m0 < M;) {  // passes of up to four tokens: the weights are read once per pass
     const int left = M - m0;
     const XT* xp = x + static_cast<size_t>(m0) * K;
