@@ -54,7 +54,7 @@ sys.path.insert(0, ROOT)
 # dram__bytes_write of ONE launch) is what roofline.traffic reports; null where no capture has been summarised
 PROFILE_OF = {"c1": "qgemv_q8_0_m1_kernel__c1.md", "c2_m1": "qgemv_q4k_m1_kernel__c2_m1.md",
               "c2_m4": "qgemv_q4k_mt_kernel__c2_m4.md", "c3": "qgemm_q4k_tc_kernel__c3.md",
-              "c4": "qgemm_q4k_tc_kernel__c4.md", "q6k_m1": "qgemv_q6k_kernel__q6k_m1.md"}
+              "c4": "qgemm_q4k_tc_kernel__c4.md", "q6k_m1": "qgemv_q6k_m1_kernel__q6k_m1.md"}
 
 
 def profile_traffic(workload: str):
