@@ -155,7 +155,10 @@ int ub_repack_to_interleaved(void* interleaved, const void* split, size_t nblock
  * output and embedding matrices in it.  Blocks are interleaved as in a .gguf file, 2-byte aligned.
  * ub_dequant_q6k: the f32 value (d*scale)*(q-32) rounded once to out_dtype, bit-exact.
  * ub_qmatmul_q6k_*: y[M,N] = x[M,K] . W^T with W = N rows of K/256 blocks, f32 accumulation, a
- * weight-streaming decode kernel that takes the tokens four at a time (any M, no workspace). */
+ * weight-streaming decode kernel that takes the tokens four at a time (any M, no workspace).  One token
+ * with K = 2048 or 4096 and 16-byte aligned wq runs a kernel that stages whole rows by bulk copies and requests
+ * its first rows before it waits for the kernel in front of it on the stream: the precondition on the weights and
+ * UB_QMATMUL_WEIGHTS_FRESH (below, ORed into out_dtype) apply to it as to ub_qmatmul_*. */
 int ub_dequant_q6k(void* out, const void* blocks, size_t numel, int out_dtype, void* stream);
 int ub_qmatmul_q6k_f32(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* stream);
 int ub_qmatmul_q6k_bf16(void* y, const void* x, const void* wq, int M, int N, int K, int out_dtype, void* stream);
@@ -167,13 +170,14 @@ int ub_qmatmul_q6k_bf16(void* y, const void* x, const void* wq, int M, int N, in
  * matmul_* (kernels/matmul.cpp:1143-1184; small-M shape in
  * kernels/third_party/matmul_decoding.h:12-570).  The suffix names the activation type;
  * out_dtype is UB_DTYPE_F32 / UB_DTYPE_BF16 / UB_DTYPE_F16.  M <= 16 runs the
- * bandwidth-bound decode kernel (Q4_K with bf16 activations and bf16 output: M <= 8), larger M
- * the tensor-core kernel — see ub_qmatmul_workspace_bytes for the scratch it needs when the
+ * bandwidth-bound decode kernels (Q4_K with bf16 activations and bf16 output: M <= 8 at K = 2048 / 4096 / 8192,
+ * M <= 4 otherwise), larger M the tensor-core kernel — see ub_qmatmul_workspace_bytes for the scratch it needs when the
  * activation or output type is not bf16 (0 whenever M <= 16).  Q8_0 takes the tensor-core kernel when
  * K % 256 == 0 and wq is 16-byte aligned; otherwise, or when called without the scratch, it runs the
  * decode kernel in passes of eight tokens (same result within the matmul tolerance, slower).
  *
- * Precondition on the weights.  The decode kernels (M <= 16) are launched with programmatic dependent launch
+ * Precondition on the weights.  The decode kernels (M <= 16) and the tensor-core kernel up to 64 tokens are
+ * launched with programmatic dependent launch
  * and request their first weight tiles BEFORE they wait for the kernel in front of them on the stream.  The
  * weight bytes must therefore be complete before that preceding kernel starts: uploaded by a copy, written
  * by a kernel that is followed by an event / synchronisation / any non-kernel operation, or simply written
