@@ -294,9 +294,9 @@ def test_q4k_two_to_four_tokens_rows_differ(dev):
 @pytest.mark.parametrize("M,N,K", [(5, 1, 4096), (5, 17, 2048), (8, 4747, 4096), (6, 4736, 2048), (7, 30000, 4096),
                                    (8, 20000, 2048), (8, 14336, 4096), (7, 5000, 8192), (8, 130, 8192), (6, 63, 4096)])
 def test_q4k_five_to_eight_tokens(dev, x_dtype, out_dtype, M, N, K):
-    """Tokens in the columns of the integer MMA, activation fragments shared by clusters of four CTAs: fewer tiles than
-    CTAs (CTAs without a tile still quantise their share), ragged last tile, more tiles per CTA than ring stages
-    (30000 rows), 8192-value rows."""
+    """Tokens in the columns of the integer MMA, activation fragments shared by the CTAs of a cluster: fewer tiles
+    than CTAs (CTAs without a tile still quantise their share), ragged last tile, more tiles per CTA than ring
+    stages (30000 rows), 8192-value rows."""
     rng = np.random.default_rng(M + N + K)
     w = o.gen_q4k_weight(rng, N, K)
     x = o.gen_activation(rng, M, K, x_dtype == DTYPE_BF16)

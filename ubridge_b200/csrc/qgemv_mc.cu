@@ -21,19 +21,21 @@
 // copy), warp w takes super-block w % 8 of every stage and there the 64-value groups 2 (w / 8), 2 (w / 8) + 1.
 // The activation fragments of all tokens (2 bytes per value, 64 KB for eight tokens of 4096 values) stay in shared
 // memory for the whole launch.
-// Quantising them in every CTA would cost several microseconds, so the CTAs of a cluster of four share the work:
-// each quantises the super-blocks of one quarter of K into its own shared memory, and after a cluster barrier
-// sends that contiguous piece to the other three with one bulk copy each (cp.async.bulk shared::cta ->
-// shared::cluster, counted on a barrier of the receiver); then every CTA runs on its own.  (Scattered
-// st.shared::cluster stores into all four memories took 2.7 us.)
+// Quantising them in every CTA would cost several microseconds, so the CTAs of a cluster of two share the work:
+// each quantises the super-blocks of one half of K into its own shared memory and sends that contiguous piece to
+// the other with one bulk copy (cp.async.bulk shared::cta -> shared::cluster, counted on a barrier of the
+// receiver); then every CTA runs on its own.  (Scattered st.shared::cluster stores into four memories took 2.7 us.)
+// Partial sums of the warps meet in shared memory once per tile; the addition (fixed order) is deferred until the
+// first stage of the next tile has been consumed, so nobody waits for the slowest warp.  Programmatic dependent
+// launch with the first stages requested ahead of the dependency wait, every mbarrier wait bounded, as in the
+// one-token kernel.
 //
-// Measured on B200, 14336 x 4096: 18.7 us for five to eight tokens (the tcgen05 kernel with its K split: 23 us; the
-// token-pair kernel 11.5 us at four tokens, which is why this one starts at five).  The main loop runs at the rate
-// mma.sync delivers here, 5-6 ns per m16n8k32 and SM; the same layout with two token groups took 25.5 us for nine to
-// sixteen tokens, no better than tcgen05, and was not kept.  Partial sums of the warps meet in shared memory once per tile;
-// the addition (fixed order) is deferred until the first stage of the next tile has been consumed, so nobody waits
-// for the slowest warp.  Programmatic dependent launch with the first stages requested ahead of the dependency
-// wait, every mbarrier wait bounded, as in the one-token kernel.
+// Measured on B200, 14336 x 4096: 16.4 us for five to eight tokens (the tcgen05 kernel with its K split: 20.8 us; the
+// token-pair kernel 11.5 us at four tokens, which is why this one starts at five).  Clusters of four (a quarter of
+// K each) fit only 33 at a time, 132 of 148 SMs, and took 17.6 us; with a release / acquire cluster barrier
+// between quantisation and exchange 18.9 us.  The launch is bound by instruction issue (597 warp instructions per
+// 16 rows x 256 weights, tensor pipe 11 % busy); the same layout with two token groups took 25.5 us for nine to
+// sixteen tokens, no better than tcgen05, and was not kept.
 #include <cuda.h>  // CUtensorMap type and enums only; the encoder is resolved at run time
 
 #include <string.h>
@@ -51,7 +53,7 @@ using namespace ub;
 constexpr int kW = 16;  // warps per CTA, all of them compute
 constexpr int kThreads = kW * 32;
 constexpr int kMaxStages = 8;
-constexpr int kCluster = 4;  // CTAs that share the quantisation of the activations
+constexpr int kCluster = 2;  // CTAs that share the quantisation of the activations
 constexpr uint32_t kSpin = 400000;
 constexpr float kXQMax = 32258.f;  // 127 * 254
 constexpr int kRowStride = 8 * UB_Q4K_BYTES;  // 1152 = 9 lines of 128 bytes
@@ -169,7 +171,7 @@ qgemv_q4k_mc_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, int N
                     int* err_word, const __grid_constant__ CUtensorMap w_map) {
   constexpr int K = 2048 * NCH;
   constexpr int MT = 8;     // token slots
-  constexpr int CPW = NCH;  // (token, super-block) chunks of 256 values a warp quantises
+  constexpr int CPW = 4 * NCH / kCluster;  // (token, super-block) chunks of 256 values a warp quantises
   constexpr int NG = 2;     // 64-value groups of its super-block a warp multiplies
   static_assert(MT * 8 * NCH == kCluster * kW * CPW, "every chunk has a warp");
   extern __shared__ __align__(128) unsigned char mc_smem_raw[];
@@ -207,6 +209,8 @@ qgemv_q4k_mc_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, int N
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // "this CTA runs and its barriers exist": the others wait for it before they send their fragments here
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
   // item n of this CTA = (tile n / NCH, stage n % NCH) -> ring slot n % S; rows past N arrive as zeros
   auto issue_item = [&](int n) {
@@ -286,12 +290,13 @@ qgemv_q4k_mc_kernel(const XT* __restrict__ x, void* __restrict__ y, int M, int N
       if (lane == 0) *reinterpret_cast<float*>(frag + sb_off + kFragLimbs + kFragMin + col * 4) = xs;
     }
   }
-  // This CTA's piece (its 2 NCH super-blocks: contiguous) is complete; the bulk copies below read
-  // it through the asynchronous proxy.  After the cluster barrier every CTA of the cluster runs, has initialised
-  // its barriers and has its piece ready.
+  // This CTA's piece (its 8 NCH / kCluster super-blocks: contiguous) is complete; the bulk copies below read it
+  // through the asynchronous proxy.  The cluster barrier only says that every CTA of the cluster runs and has
+  // initialised its barriers (they arrived long ago); a piece arrives wherever it is sent whenever it is ready.
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-  constexpr uint32_t kPiece = 2 * NCH * kFragSB;
+  __syncthreads();
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+  constexpr uint32_t kPiece = 8 * NCH / kCluster * kFragSB;
   static_assert(kPiece % 16 == 0, "bulk copy size");
   if (threadIdx.x == 0) {
     mb_expect_tx(fragfull_s, (kCluster - 1) * kPiece);
@@ -471,7 +476,8 @@ int launch_mc(const uint8_t* wq, const XT* x, void* y, int M, int N, int y_dtype
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = 1;
   // Clusters that run at once: a cluster lives inside one processor cluster of the chip, so fewer CTAs than SMs
-  // fit (128 of 148 on B200); a grid larger than that would run its last clusters after all the others.
+  // may fit (132 of 148 with clusters of four on B200); a grid larger than that would run its last clusters after
+  // all the others.
   static int max_clusters = 0;  // per instantiation; the same on every device of a node
   if (max_clusters == 0) {
     int n = 0;
