@@ -79,16 +79,20 @@ def test_matmul_odd_shapes(dev, x_dtype, M, N, K):
     want = o.qmatmul_exact(x, o.dequant_q6k(w).reshape(N, K))
     got = _matmul(dev, w, x, M, N, K, x_dtype, DTYPE_F32)
     assert o.rel_l2(got, want) < TOL_DECODE
-    assert o.rel_l2(got, want) < 1e-5  # f32 products of exact weights: only the summation order differs
+    if M > 1 or K % 2048:
+        assert o.rel_l2(got, want) < 1e-5  # f32 products of exact weights: only the summation order differs
+    else:
+        assert o.rel_l2(got, want) < 1e-4  # one token at K % 2048 == 0: 15-bit fixed-point activations
 
 
 @pytest.mark.parametrize("x_dtype,out_dtype", [(DTYPE_BF16, DTYPE_F32), (DTYPE_F32, DTYPE_F32), (DTYPE_BF16, DTYPE_BF16),
                                                (DTYPE_F32, DTYPE_F16)])
-@pytest.mark.parametrize("N,K", [(1, 4096), (9, 2048), (17, 4096), (4747, 4096), (2369, 2048), (30000, 4096), (20000, 2048)])
+@pytest.mark.parametrize("N,K", [(1, 4096), (9, 2048), (17, 4096), (4747, 4096), (2369, 2048), (30000, 4096), (20000, 2048),
+                                 (3001, 8192), (2000, 14336), (700, 6144)])
 def test_single_token_staged_kernel(dev, x_dtype, out_dtype, N, K):
-    """One token at K = 2048 / 4096: rows staged by bulk copies, 15-bit fixed-point activations.  Fewer rows than
-    CTAs, row ranges of unequal length, more stages per CTA than the ring has slots (30000 rows), a last stage of
-    fewer than eight rows."""
+    """One token at K a multiple of 2048: rows staged by bulk copies, 15-bit fixed-point activations.  Fewer rows
+    than CTAs, row ranges of unequal length, more stages per CTA than the ring has slots (30000 rows), a last stage
+    of fewer than eight rows; rows of 6144 to 14336 values run one CTA per SM."""
     rng = np.random.default_rng(N + K)
     w = o.gen_q6k_weight(rng, N, K)
     x = o.gen_activation(rng, 1, K, x_dtype == DTYPE_BF16)

@@ -11,8 +11,8 @@
 // 16-bit ones, and consecutive lanes read consecutive bytes.  The dequantisation kernel gives a lane two
 // neighbouring l of one half (eight weights), the matmul kernels four (sixteen weights).
 //
-// One token with rows of 2048 or 4096 values (qgemv_q6k_m1_kernel) does not load weights through the load-store
-// unit at all: a row of K / 256 blocks is a multiple of 16 bytes there, so up to eight consecutive rows come into
+// One token with rows of a multiple of 2048 values up to 14336 (qgemv_q6k_m1_kernel) does not load weights through
+// the load-store unit at all: a row of K / 256 blocks is a multiple of 16 bytes there, so up to eight consecutive rows come into
 // shared memory as ONE bulk copy (cp.async.bulk, mbarrier ring, two CTAs per SM, programmatic dependent launch as
 // in the Q4_K one-token kernel), are read with aligned 32-bit shared loads (plus a funnel shift in the odd
 // blocks) and meet 15-bit block-fixed-point activations in dp4a.
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256) qgemv_q6k_kernel(const uint8_t* __restric
 }
 
 // ----------------------------------------------------------------------------------------------------------------
-// One token, K = 2048 or 4096.  A CTA owns a contiguous range of rows (ranges differ by at most one row) and walks
+// One token, K a multiple of 2048.  A CTA owns a contiguous range of rows (ranges differ by at most one row) and walks
 // it in stages of up to eight rows = one bulk copy; warp w takes row w of the stage, all its super-blocks, two per
 // step (lanes 0-15 the even one, 16-31 the odd one; inside a super-block a lane owns four neighbouring l of one
 // 128-value half and all four j, i.e. 16 weights).  The four 6-bit values of a word become signed bytes 4 (q - 32)
@@ -183,7 +183,8 @@ constexpr int kQ6W = 8;            // warps per CTA = rows per stage
 constexpr int kQ6MaxStages = 4;
 constexpr uint32_t kQ6Spin = 400000;
 constexpr float kQ6XQMax = 32258.f;  // 127 * 254
-constexpr size_t kQ6DynBudget = 104 * 1024;  // two CTAs per SM
+constexpr size_t kQ6DynBudget = 104 * 1024;     // two CTAs per SM
+constexpr size_t kQ6DynBudgetOne = 222 * 1024;  // one CTA per SM
 
 __device__ __forceinline__ bool q6_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -375,13 +376,20 @@ qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, vo
   if (!ok && lane == 0) report_device_error(err_word, UB_ERR_TIMEOUT);
 }
 
-// One token at K = 2048 / 4096 with 16-byte aligned weights; UB_ERR_UNSUPPORTED for everything else.
+// One token, K a multiple of 2048 (rows are then whole 16-byte pieces) up to 14336, 16-byte aligned weights;
+// UB_ERR_UNSUPPORTED for everything else.  Two CTAs per SM while two stages of eight rows fit beside the activation
+// limbs in half an SM's shared memory (K <= 4096), one CTA per SM with the whole of it beyond.
 template <typename XT>
 int launch_q6k_m1(const uint8_t* w, const XT* x, void* y, int N, int K, int out_dtype, bool fresh, cudaStream_t s) {
-  if ((K != 2048 && K != 4096) || (reinterpret_cast<uintptr_t>(w) & 15)) return UB_ERR_UNSUPPORTED;
+  if (K % 2048 || (reinterpret_cast<uintptr_t>(w) & 15)) return UB_ERR_UNSUPPORTED;
   const size_t row_bytes = static_cast<size_t>(K / UB_QK_K) * UB_Q6K_BYTES, stage_bytes = kQ6W * row_bytes;
   const size_t xbytes = static_cast<size_t>(K / 16) * 32 + static_cast<size_t>(K / UB_QK_K) * 4;
-  int S = static_cast<int>((kQ6DynBudget - xbytes) / stage_bytes);
+  int ctas = 2;
+  int S = xbytes + 2 * stage_bytes <= kQ6DynBudget ? static_cast<int>((kQ6DynBudget - xbytes) / stage_bytes) : 0;
+  if (S < 2) {
+    ctas = 1;
+    S = xbytes + 2 * stage_bytes <= kQ6DynBudgetOne ? static_cast<int>((kQ6DynBudgetOne - xbytes) / stage_bytes) : 0;
+  }
   if (S > kQ6MaxStages) S = kQ6MaxStages;
   if (S < 2) return UB_ERR_UNSUPPORTED;
   const size_t smem = static_cast<size_t>(S) * stage_bytes + xbytes;
@@ -391,7 +399,7 @@ int launch_q6k_m1(const uint8_t* w, const XT* x, void* y, int N, int K, int out_
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
   }
-  const int slots = 2 * ub::num_sms(), want = (N + kQ6W - 1) / kQ6W;
+  const int slots = ctas * ub::num_sms(), want = (N + kQ6W - 1) / kQ6W;
   const int grid = want < slots ? want : slots;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));

@@ -40,6 +40,8 @@
 
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace ub {
@@ -478,7 +480,8 @@ int launch_mc(const uint8_t* wq, const XT* x, void* y, int M, int N, int y_dtype
   // Clusters that run at once: a cluster lives inside one processor cluster of the chip, so fewer CTAs than SMs
   // may fit (132 of 148 with clusters of four on B200); a grid larger than that would run its last clusters after
   // all the others.
-  static int max_clusters = 0;  // per instantiation; the same on every device of a node
+  static std::atomic<int> cached_clusters{0};  // per instantiation; the same on every device of a node
+  int max_clusters = cached_clusters.load(std::memory_order_relaxed);
   if (max_clusters == 0) {
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
@@ -486,6 +489,7 @@ int launch_mc(const uint8_t* wq, const XT* x, void* y, int M, int N, int y_dtype
       return UB_ERR_UNSUPPORTED;
     }
     max_clusters = n;
+    cached_clusters.store(n, std::memory_order_relaxed);
   }
   // whole clusters: CTAs without a tile still quantise their share of the activations
   const int tiles = (N + 15) / 16;
