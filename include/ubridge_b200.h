@@ -155,8 +155,8 @@ int ub_repack_to_interleaved(void* interleaved, const void* split, size_t nblock
  * output and embedding matrices in it.  Blocks are interleaved as in a .gguf file, 2-byte aligned.
  * ub_dequant_q6k: the f32 value (d*scale)*(q-32) rounded once to out_dtype, bit-exact.
  * ub_qmatmul_q6k_*: y[M,N] = x[M,K] . W^T with W = N rows of K/256 blocks, f32 accumulation, a
- * weight-streaming decode kernel that takes the tokens four at a time (any M, no workspace).  One token
- * with K a multiple of 2048 up to 14336 and 16-byte aligned wq runs a kernel that stages whole rows by bulk copies and requests
+ * weight-streaming decode kernel that takes the tokens four at a time (any M, no workspace).  With K a multiple of
+ * 2048 (up to 14336 for one token) and 16-byte aligned wq each pass runs a kernel that stages whole rows by bulk copies and requests
  * its first rows before it waits for the kernel in front of it on the stream: the precondition on the weights and
  * UB_QMATMUL_WEIGHTS_FRESH (below, ORed into out_dtype) apply to it as to ub_qmatmul_*. */
 int ub_dequant_q6k(void* out, const void* blocks, size_t numel, int out_dtype, void* stream);

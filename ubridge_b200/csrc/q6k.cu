@@ -11,8 +11,8 @@
 // 16-bit ones, and consecutive lanes read consecutive bytes.  The dequantisation kernel gives a lane two
 // neighbouring l of one half (eight weights), the matmul kernels four (sixteen weights).
 //
-// One token with rows of a multiple of 2048 values up to 14336 (qgemv_q6k_m1_kernel) does not load weights through
-// the load-store unit at all: a row of K / 256 blocks is a multiple of 16 bytes there, so up to eight consecutive rows come into
+// One to four tokens with rows of a multiple of 2048 values up to 14336 (qgemv_q6k_m1_kernel) do not load weights
+// through the load-store unit at all: a row of K / 256 blocks is a multiple of 16 bytes there, so up to eight consecutive rows come into
 // shared memory as ONE bulk copy (cp.async.bulk, mbarrier ring, two CTAs per SM, programmatic dependent launch as
 // in the Q4_K one-token kernel), are read with aligned 32-bit shared loads (plus a funnel shift in the odd
 // blocks) and meet 15-bit block-fixed-point activations in dp4a.
@@ -217,19 +217,21 @@ __device__ __forceinline__ void q6_load4(const __nv_bfloat16* x, int k, float (&
   v[2] = __uint_as_float(q.y << 16), v[3] = __uint_as_float(q.y & 0xFFFF0000u);
 }
 
-template <typename XT>
+// MT: token slots (1, 2 or 4; M <= MT tokens are real, the others are not computed).  The weights of a step are
+// unpacked once and meet every token's limbs.
+template <typename XT, int MT>
 __global__ void __launch_bounds__(kQ6W * 32, 2)
-qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void* __restrict__ y, int y_dtype, int N,
-                    int K, int S, int early, int* err_word) {
+qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void* __restrict__ y, int y_dtype, int M,
+                    int N, int K, int S, int early, int* err_word) {
   extern __shared__ __align__(128) unsigned char q6_smem[];
   __shared__ __align__(8) unsigned long long bars[2 * kQ6MaxStages];  // full[S], empty[S]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nsb = K / UB_QK_K;
   const uint32_t row_bytes = static_cast<uint32_t>(nsb) * UB_Q6K_BYTES, stage_bytes = kQ6W * row_bytes;
   unsigned char* const ring = q6_smem;
-  uint4* const xhi = reinterpret_cast<uint4*>(q6_smem + static_cast<size_t>(S) * stage_bytes);  // [K / 16]
-  uint4* const xlo = xhi + K / 16;
-  float* const xsc = reinterpret_cast<float*>(xlo + K / 16);  // [nsb]
+  uint4* const xhi = reinterpret_cast<uint4*>(q6_smem + static_cast<size_t>(S) * stage_bytes);  // [MT][K / 16]
+  uint4* const xlo = xhi + MT * (K / 16);
+  float* const xsc = reinterpret_cast<float*>(xlo + MT * (K / 16));  // [MT][nsb]
   const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
   const uint32_t bars_s = static_cast<uint32_t>(__cvta_generic_to_shared(bars));
   // rows of this CTA
@@ -267,17 +269,18 @@ qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, vo
 
   // ---- activations -> 15-bit block fixed point in shared memory; slot = 16 sb + 8 h + l / 4 holds the sixteen
   // values 256 sb + 128 h + 32 j + l .. l + 3 (j = 0..3), one word per j and limb ----
-  for (int slot0 = 0; slot0 < K / 16; slot0 += kQ6W * 32) {
-    const int slot = slot0 + threadIdx.x;  // whole half-warps are inside or outside (K / 16 is a multiple of 16)
+  for (int slot0 = 0; slot0 < M * (K / 16); slot0 += kQ6W * 32) {
+    // whole half-warps are inside or outside (K / 16 is a multiple of 16); tok: the token, slot: inside its row
+    const int gslot = slot0 + threadIdx.x, tok = gslot / (K / 16), slot = gslot - tok * (K / 16);
     float v[4][4];
-    if (slot < K / 16) {
+    if (gslot < M * (K / 16)) {
       const int k0 = (slot >> 4) * UB_QK_K + ((slot >> 3) & 1) * 128 + (slot & 7) * 4;
 #pragma unroll
-      for (int j = 0; j < 4; j++) q6_load4(x, k0 + 32 * j, v[j]);
+      for (int j = 0; j < 4; j++) q6_load4(x + static_cast<size_t>(tok) * K, k0 + 32 * j, v[j]);
     }
     if (slot0 == 0 && threadIdx.x == 0)  // the rest of the ring goes out right behind the activation loads
       for (int n = n_early; n < min(S, nst); n++) issue(n);
-    if (slot < K / 16) {
+    if (gslot < M * (K / 16)) {
       float amax = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; j++)
@@ -299,9 +302,9 @@ qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, vo
         wh[j] = q6_pack4(hi[0], hi[1], hi[2], hi[3]);
         wl[j] = q6_pack4(lo[0], lo[1], lo[2], lo[3]);
       }
-      xhi[slot] = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-      xlo[slot] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
-      if ((slot & 15) == 0) xsc[slot >> 4] = amax * (1.f / kQ6XQMax);
+      xhi[gslot] = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+      xlo[gslot] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+      if ((slot & 15) == 0) xsc[tok * nsb + (slot >> 4)] = amax * (1.f / kQ6XQMax);
     }
   }
   __syncthreads();
@@ -313,7 +316,9 @@ qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, vo
   for (int n = 0; n < nst; n++) {
     if (ok) ok = q6_wait(bars_s + 8 * slot, round & 1);
     const int rows = min(kQ6W, nrows - kQ6W * n);
-    float acc = 0.f;
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) acc[m] = 0.f;
     if (warp < rows) {
       const unsigned char* rowp = ring + static_cast<size_t>(slot) * stage_bytes + static_cast<size_t>(warp) * row_bytes;
       // even super-blocks first, then the odd ones: a block starts 2 (sb & 1) bytes past a 4-byte boundary, and with
@@ -334,7 +339,6 @@ qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, vo
         }
         const signed char* sc = reinterpret_cast<const signed char*>(blk + 192) + 8 * h + (lg >> 2);
         const float d = half_bits_to_f32(*reinterpret_cast<const unsigned short*>(blk + 208));
-        const uint4 xh = xhi[16 * sb + 8 * h + lg], xl = xlo[16 * sb + 8 * h + lg];
         // signed bytes 4 (q - 32): six bits in bits 2-7, top bit flipped
         const uint32_t w0 = (((qa << 2) & 0x3C3C3C3Cu) | ((qh << 6) & 0xC0C0C0C0u)) ^ 0x80808080u;
         const uint32_t w1 = (((qb << 2) & 0x3C3C3C3Cu) | ((qh << 4) & 0xC0C0C0C0u)) ^ 0x80808080u;
@@ -342,16 +346,22 @@ qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, vo
         const uint32_t w3 = (((qb >> 2) & 0x3C3C3C3Cu) | (qh & 0xC0C0C0C0u)) ^ 0x80808080u;
         // the int8 scales meet the limb dots in integers (|scale * dot| < 2^23 each), one conversion per limb
         const int s0 = sc[0], s1 = sc[2], s2 = sc[4], s3 = sc[6];
-        const int H = s0 * __dp4a(static_cast<int>(w0), static_cast<int>(xh.x), 0) +
-                      s1 * __dp4a(static_cast<int>(w1), static_cast<int>(xh.y), 0) +
-                      s2 * __dp4a(static_cast<int>(w2), static_cast<int>(xh.z), 0) +
-                      s3 * __dp4a(static_cast<int>(w3), static_cast<int>(xh.w), 0);
-        const int L = s0 * __dp4a(static_cast<int>(w0), static_cast<int>(xl.x), 0) +
-                      s1 * __dp4a(static_cast<int>(w1), static_cast<int>(xl.y), 0) +
-                      s2 * __dp4a(static_cast<int>(w2), static_cast<int>(xl.z), 0) +
-                      s3 * __dp4a(static_cast<int>(w3), static_cast<int>(xl.w), 0);
-        const float f = fmaf(static_cast<float>(H), 254.f, static_cast<float>(L));
-        acc = fmaf(f, d * (0.25f * xsc[sb]), acc);
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+          if (m < 3 || M > 3) {  // only the fourth slot can be empty (one, two or four slots for M = 1, 2, 3-4)
+            const uint4 xh = xhi[m * (K / 16) + 16 * sb + 8 * h + lg], xl = xlo[m * (K / 16) + 16 * sb + 8 * h + lg];
+            const int H = s0 * __dp4a(static_cast<int>(w0), static_cast<int>(xh.x), 0) +
+                          s1 * __dp4a(static_cast<int>(w1), static_cast<int>(xh.y), 0) +
+                          s2 * __dp4a(static_cast<int>(w2), static_cast<int>(xh.z), 0) +
+                          s3 * __dp4a(static_cast<int>(w3), static_cast<int>(xh.w), 0);
+            const int L = s0 * __dp4a(static_cast<int>(w0), static_cast<int>(xl.x), 0) +
+                          s1 * __dp4a(static_cast<int>(w1), static_cast<int>(xl.y), 0) +
+                          s2 * __dp4a(static_cast<int>(w2), static_cast<int>(xl.z), 0) +
+                          s3 * __dp4a(static_cast<int>(w3), static_cast<int>(xl.w), 0);
+            const float f = fmaf(static_cast<float>(H), 254.f, static_cast<float>(L));
+            acc[m] = fmaf(f, d * (0.25f * xsc[m * nsb + sb]), acc[m]);
+          }
+        }
       }
     }
     // everything this warp needs from the stage has been read: hand the slot back
@@ -363,12 +373,16 @@ qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, vo
     }
     if (warp < rows) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-      if (lane == 0) {
-        const size_t at = static_cast<size_t>(r0 + kQ6W * n + warp);
-        if (y_dtype == UB_DTYPE_F32) static_cast<float*>(y)[at] = acc;
-        else if (y_dtype == UB_DTYPE_BF16) static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(acc);
-        else static_cast<__half*>(y)[at] = __float2half_rn(acc);
+      for (int m = 0; m < MT; m++) {
+        float v = acc[m];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        if (lane == 0 && (m < 3 || M > 3)) {
+          const size_t at = static_cast<size_t>(m) * N + static_cast<size_t>(r0 + kQ6W * n + warp);
+          if (y_dtype == UB_DTYPE_F32) static_cast<float*>(y)[at] = v;
+          else if (y_dtype == UB_DTYPE_BF16) static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(v);
+          else static_cast<__half*>(y)[at] = __float2half_rn(v);
+        }
       }
     }
     if (++slot == S) slot = 0, round++;
@@ -376,14 +390,15 @@ qgemv_q6k_m1_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, vo
   if (!ok && lane == 0) report_device_error(err_word, UB_ERR_TIMEOUT);
 }
 
-// One token, K a multiple of 2048 (rows are then whole 16-byte pieces) up to 14336, 16-byte aligned weights;
-// UB_ERR_UNSUPPORTED for everything else.  Two CTAs per SM while two stages of eight rows fit beside the activation
+// One to four tokens, K a multiple of 2048 (rows are then whole 16-byte pieces) while two stages fit beside the
+// tokens' limbs (one token: up to 14336), 16-byte aligned weights; UB_ERR_UNSUPPORTED for everything else.  Two CTAs per SM while two stages of eight rows fit beside the activation
 // limbs in half an SM's shared memory (K <= 4096), one CTA per SM with the whole of it beyond.
-template <typename XT>
-int launch_q6k_m1(const uint8_t* w, const XT* x, void* y, int N, int K, int out_dtype, bool fresh, cudaStream_t s) {
+template <typename XT, int MT>
+int launch_q6k_m1(const uint8_t* w, const XT* x, void* y, int M, int N, int K, int out_dtype, bool fresh,
+                  cudaStream_t s) {
   if (K % 2048 || (reinterpret_cast<uintptr_t>(w) & 15)) return UB_ERR_UNSUPPORTED;
   const size_t row_bytes = static_cast<size_t>(K / UB_QK_K) * UB_Q6K_BYTES, stage_bytes = kQ6W * row_bytes;
-  const size_t xbytes = static_cast<size_t>(K / 16) * 32 + static_cast<size_t>(K / UB_QK_K) * 4;
+  const size_t xbytes = MT * (static_cast<size_t>(K / 16) * 32 + static_cast<size_t>(K / UB_QK_K) * 4);
   int ctas = 2;
   int S = xbytes + 2 * stage_bytes <= kQ6DynBudget ? static_cast<int>((kQ6DynBudget - xbytes) / stage_bytes) : 0;
   if (S < 2) {
@@ -393,7 +408,7 @@ int launch_q6k_m1(const uint8_t* w, const XT* x, void* y, int N, int K, int out_
   if (S > kQ6MaxStages) S = kQ6MaxStages;
   if (S < 2) return UB_ERR_UNSUPPORTED;
   const size_t smem = static_cast<size_t>(S) * stage_bytes + xbytes;
-  auto kernel = qgemv_q6k_m1_kernel<XT>;
+  auto kernel = qgemv_q6k_m1_kernel<XT, MT>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
@@ -408,7 +423,7 @@ int launch_q6k_m1(const uint8_t* w, const XT* x, void* y, int N, int K, int out_
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, w, x, y, out_dtype, N, K, S, fresh ? 0 : 1, ub::device_error_word());
+  e = cudaLaunchKernelEx(&cfg, kernel, w, x, y, out_dtype, M, N, K, S, fresh ? 0 : 1, ub::device_error_word());
   if (e != cudaSuccess) {
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
@@ -431,14 +446,21 @@ int q6k_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int ou
   const int grid = (N + 8 * kQ6kRowsPerWarp - 1) / (8 * kQ6kRowsPerWarp);  // the CTA scheduler evens out the load
   const uint8_t* w = static_cast<const uint8_t*>(wq);
   if (ub::take_weights_written(s)) fresh = true;
-  if (M == 1) {
-    const int st = launch_q6k_m1<XT>(w, x, y, N, K, out_dtype, fresh, s);
-    if (st != UB_ERR_UNSUPPORTED) return st;
-  }
   for (int m0 = 0; m0 < M;) {  // passes of up to four tokens: the weights are read once per pass
     const int left = M - m0;
     const XT* xp = x + static_cast<size_t>(m0) * K;
     void* yp = static_cast<char*>(y) + static_cast<size_t>(m0) * N * esz;
+    {  // rows staged by bulk copies where the shape allows (the output rows of a pass are N apart there as well)
+      const int mt = left >= 4 ? 4 : left;
+      const int st = mt == 1   ? launch_q6k_m1<XT, 1>(w, xp, yp, mt, N, K, out_dtype, fresh, s)
+                     : mt == 2 ? launch_q6k_m1<XT, 2>(w, xp, yp, mt, N, K, out_dtype, fresh, s)
+                               : launch_q6k_m1<XT, 4>(w, xp, yp, mt, N, K, out_dtype, fresh, s);
+      if (st == UB_OK) {
+        m0 += mt;
+        continue;
+      }
+      if (st != UB_ERR_UNSUPPORTED) return st;
+    }
     if (left >= 4) {
       qgemv_q6k_kernel<XT, 4><<<grid, 256, 0, s>>>(w, xp, yp, out_dtype, N, K, N);
       m0 += 4;
