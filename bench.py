@@ -53,7 +53,8 @@ sys.path.insert(0, ROOT)
 # ncu summary of the workload's dominant kernel: its line `dram_bytes_per_launch = <n>` (dram__bytes_read +
 # dram__bytes_write of ONE launch) is what roofline.traffic reports; null where no capture has been summarised
 PROFILE_OF = {"c1": "qgemv_q8_0_m1_kernel__c1.md", "c2_m1": "qgemv_q4k_m1_kernel__c2_m1.md",
-              "c2_m4": "qgemv_q4k_mt_kernel__c2_m4.md", "c3": "qgemm_q4k_tc_kernel__c3.md",
+              "c2_m4": "qgemv_q4k_mt_kernel__c2_m4.md", "c2_m8": "qgemv_q4k_mc_kernel__c2_m8.md",
+              "c2_m16": "qgemm_q4k_tc_kernel__c2_m16.md", "c3": "qgemm_q4k_tc_kernel__c3.md",
               "c4": "qgemm_q4k_tc_kernel__c4.md", "q6k_m1": "qgemv_q6k_m1_kernel__q6k_m1.md"}
 
 
