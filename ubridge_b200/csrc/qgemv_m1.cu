@@ -434,32 +434,63 @@ int launch_m1(const uint8_t* wq, const XT* x, void* y, int N, int K, int y_dtype
   if (!enc) return UB_ERR_UNSUPPORTED;
   constexpr int kRowStride = 8 * SBW * UB_Q4K_BYTES;
   constexpr int kStageBytes = 16 * kRowStride;
-  // rows as lines of 128 bytes: {128 bytes, lines per row, N rows}; box = one 16-row tile
-  CUtensorMap wmap;
-  const cuuint64_t row_bytes = static_cast<cuuint64_t>(K / UB_QK_K) * UB_Q4K_BYTES;
-  const cuuint64_t dims[3] = {128, row_bytes / 128, static_cast<cuuint64_t>(N)};
-  const cuuint64_t strides[2] = {128, row_bytes};
-  const cuuint32_t box[3] = {128, static_cast<cuuint32_t>(kRowStride / 128), 16};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(wq), dims, strides, box, estr,
-          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return UB_ERR_UNSUPPORTED;
-  // the same rows through a box of eight: the halves of the tiles left over after the full rounds
-  CUtensorMap wmap8;
-  const cuuint32_t box8[3] = {128, static_cast<cuuint32_t>(kRowStride / 128), 8};
-  if (enc(&wmap8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(wq), dims, strides, box8, estr,
-          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return UB_ERR_UNSUPPORTED;
+  // A decode step calls this once per weight matrix and token, and the host side of a call costs about as much
+  // as the launch runs on the GPU (5-7 us against 6.6 us at 14336 x 4096): the two tensor maps of a matrix depend
+  // on its address and shape only and are kept per thread, and the kernel's shared-memory attribute is set once
+  // per device.
+  struct MapEntry {
+    const uint8_t* wq;
+    int N, K;
+    CUtensorMap m16, m8;
+  };
+  static thread_local MapEntry cache[8];
+  static thread_local int cache_next = 0;
+  const MapEntry* hit = nullptr;
+  for (int i = 0; i < 8; i++)
+    if (cache[i].wq == wq && cache[i].N == N && cache[i].K == K) hit = &cache[i];
+  if (!hit) {
+    MapEntry ent;
+    ent.wq = wq, ent.N = N, ent.K = K;
+    // rows as lines of 128 bytes: {128 bytes, lines per row, N rows}; box = one 16-row tile
+    const cuuint64_t row_bytes = static_cast<cuuint64_t>(K / UB_QK_K) * UB_Q4K_BYTES;
+    const cuuint64_t dims[3] = {128, row_bytes / 128, static_cast<cuuint64_t>(N)};
+    const cuuint64_t strides[2] = {128, row_bytes};
+    const cuuint32_t box[3] = {128, static_cast<cuuint32_t>(kRowStride / 128), 16};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    if (enc(&ent.m16, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(wq), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return UB_ERR_UNSUPPORTED;
+    // the same rows through a box of eight: the halves of the tiles left over after the full rounds
+    const cuuint32_t box8[3] = {128, static_cast<cuuint32_t>(kRowStride / 128), 8};
+    if (enc(&ent.m8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(wq), dims, strides, box8, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return UB_ERR_UNSUPPORTED;
+    cache[cache_next] = ent;
+    hit = &cache[cache_next];
+    cache_next = (cache_next + 1) & 7;
+  }
+  const CUtensorMap& wmap = hit->m16;
+  const CUtensorMap& wmap8 = hit->m8;
   int S = static_cast<int>(kRingBudget / kStageBytes);
   if (S > kMaxStagesM1) S = kMaxStagesM1;
   const size_t smem = static_cast<size_t>(S) * kStageBytes + 1024;
   auto kernel = qgemv_q4k_m1_kernel<XT, SBW>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  if (e != cudaSuccess) {
-    ub::set_cuda_error(e);
-    return ub::fail(UB_ERR_CUDA);
+  cudaError_t e;
+  {
+    static std::atomic<unsigned long long> attr_set{0};  // bit d: done on device d (this instantiation)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned long long bit = (dev >= 0 && dev < 64) ? 1ull << dev : 0;
+    if (!(attr_set.load(std::memory_order_relaxed) & bit) || !bit) {
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) {
+        ub::set_cuda_error(e);
+        return ub::fail(UB_ERR_CUDA);
+      }
+      attr_set.fetch_or(bit, std::memory_order_relaxed);
+    }
   }
   const int tiles = (N + 15) / 16;
   const int slots = 2 * ub::num_sms();

@@ -15,19 +15,19 @@ _SUFFIX = {DTYPE_F32: "f32", DTYPE_F16: "f16", DTYPE_BF16: "bf16"}
 
 
 def _p(buf):
-    if buf is None:
-        return None
-    if hasattr(buf, "ptr"):
-        return ctypes.c_void_p(buf.ptr)
-    if isinstance(buf, ctypes.c_void_p):
+    # every pointer parameter is declared c_void_p, which takes None, an int or a c_void_p as it is: no object is
+    # made per call (a decode step makes hundreds of these calls)
+    if buf is None or type(buf) is int or isinstance(buf, ctypes.c_void_p):
         return buf
-    return ctypes.c_void_p(int(buf))
+    if hasattr(buf, "ptr"):
+        return buf.ptr
+    return int(buf)
 
 
 def _s(stream):
-    if stream is None or isinstance(stream, ctypes.c_void_p):
+    if stream is None or type(stream) is int or isinstance(stream, ctypes.c_void_p):
         return stream
-    return ctypes.c_void_p(int(stream))
+    return int(stream)
 
 
 # ----------------------------------------------------------------------------- GGUF blocks
@@ -84,6 +84,9 @@ def qmatmul_gguf(y, x, blob, ggml_type: int, M: int, N: int, K: int, *, x_dtype:
 
 
 # ----------------------------------------------------------------------------- quantized matmul
+_QMATMUL = {}  # (is_q4k, x_dtype) -> (function, name): looked up once
+
+
 def qmatmul_workspace_bytes(M: int, N: int, K: int, is_q4k: bool) -> int:
     return lib().ub_qmatmul_workspace_bytes(M, N, K, int(is_q4k))
 
@@ -93,8 +96,13 @@ def qmatmul(y, x, wq, M: int, N: int, K: int, *, is_q4k: bool, x_dtype: int, out
     """y[M,N] = x[M,K] . W^T with W given as interleaved GGUF blocks (Q4_K when is_q4k else Q8_0)."""
     if x_dtype not in (DTYPE_F32, DTYPE_BF16):
         raise _lib.UbridgeError(_lib.UB_ERR_INVALID_ARG, "qmatmul: activations must be f32 or bf16")
-    name = "ub_qmatmul_%s_%s" % ("q4k" if is_q4k else "q8_0", _SUFFIX[x_dtype])
-    check(getattr(lib(), name)(_p(y), _p(x), _p(wq), M, N, K, out_dtype, _p(workspace), ws_bytes, _s(stream)), name)
+    fn = _QMATMUL.get((is_q4k, x_dtype))
+    if fn is None:
+        name = "ub_qmatmul_%s_%s" % ("q4k" if is_q4k else "q8_0", _SUFFIX[x_dtype])
+        fn = _QMATMUL[(is_q4k, x_dtype)] = (getattr(lib(), name), name)
+    st = fn[0](_p(y), _p(x), _p(wq), M, N, K, out_dtype, _p(workspace), ws_bytes, _s(stream))
+    if st:
+        check(st, fn[1])
 
 
 def qmatmul_q4k_gate_up_workspace_bytes(M: int, I: int, K: int) -> int:
