@@ -227,7 +227,11 @@ int ub_qmatmul_q4k_f32_static(void* y, const void* x, const void* wq, int M, int
  * bytes as they lie in the file and dispatch on the tag.  The reference declares the block structs of the family
  * (kernels/quant.cpp:64-185) and ships kernels for Q8_0 and Q4_K; taken here: Q4_0 (2), Q8_0 (8), Q4_K (12),
  * Q5_K (13), Q6_K (14); other tags return UB_ERR_UNSUPPORTED.  x_dtype f32 / bf16; Q4_K with more than 16 tokens
- * and non-bf16 types needs ub_qmatmul_gguf_workspace_bytes of workspace, the other formats none. */
+ * and non-bf16 types needs ub_qmatmul_gguf_workspace_bytes of workspace, the other formats none.  Q4_0, Q5_K and
+ * Q6_K with rows of whole 2048 values and 16-byte aligned blob and activations run, up to four tokens per pass,
+ * kernels that stage whole rows by bulk copies and request their first rows before they wait for the kernel in
+ * front of them on the stream: the precondition on the weights and UB_QMATMUL_WEIGHTS_FRESH (ORed into out_dtype)
+ * apply to them as to ub_qmatmul_*. */
 int ub_gguf_block_values(int ggml_type);
 int ub_gguf_block_bytes(int ggml_type);
 size_t ub_gguf_tensor_bytes(int ggml_type, size_t numel);

@@ -21,6 +21,13 @@
 // GGML type tags (the values GGUF files carry)
 enum { GGML_Q4_0 = 2, GGML_Q8_0 = 8, GGML_Q4_K = 12, GGML_Q5_K = 13, GGML_Q6_K = 14 };
 
+namespace ub {
+template <typename XT>
+int q5k_gemv_staged(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+template <typename XT>
+int q4_0_gemv_staged(const void* wq, const XT* x, void* y, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s);
+}
+
 namespace {
 
 using namespace ub;
@@ -173,7 +180,7 @@ int launch_gguf_gemv(const uint8_t* wq, const XT* x, void* y, int M, int N, int 
 }
 
 template <typename XT, int FMT>
-int gguf_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, cudaStream_t s) {
+int gguf_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int y_dtype, bool fresh, cudaStream_t s) {
   const uint8_t* w = static_cast<const uint8_t*>(wq);
   const size_t esz = y_dtype == UB_DTYPE_F32 ? 4 : 2;
   for (int m0 = 0; m0 < M;) {
@@ -181,6 +188,16 @@ int gguf_matmul(void* y, const XT* x, const void* wq, int M, int N, int K, int y
     const XT* xp = x + static_cast<size_t>(m0) * K;
     void* yp = static_cast<char*>(y) + static_cast<size_t>(m0) * N * esz;
     int st, step;
+    {  // rows of whole 2048 values: staged by bulk copies, dp4a on fixed-point activations
+      step = left < 4 ? left : 4;
+      st = FMT == 1 ? ub::q5k_gemv_staged<XT>(w, xp, yp, step, N, K, y_dtype, fresh, s)
+                    : ub::q4_0_gemv_staged<XT>(w, xp, yp, step, N, K, y_dtype, fresh, s);
+      if (st == UB_OK) {
+        m0 += step;
+        continue;
+      }
+      if (st != UB_ERR_UNSUPPORTED) return st;
+    }
     // tokens per pass: as many as the activations' f32 copy leaves room for in shared memory
     if (left >= 4 && static_cast<size_t>(4) * K * 4 <= 200 * 1024) {
       step = left < 4 ? left : 4;
@@ -291,6 +308,9 @@ int ub_qmatmul_gguf(void* y, const void* x, const void* blob, int ggml_type, int
     default: break;
   }
   if (ggml_type != GGML_Q4_0 && ggml_type != GGML_Q5_K) return ub::fail(UB_ERR_UNSUPPORTED);
+  // UB_QMATMUL_WEIGHTS_FRESH rides in the upper bits of out_dtype, as in ub_qmatmul_*
+  bool fresh = (out_dtype & UB_QMATMUL_WEIGHTS_FRESH) != 0;
+  out_dtype &= ~UB_QMATMUL_WEIGHTS_FRESH;
   if (M == 0 || N == 0) return ub::fail(UB_OK);
   const int per = ub_gguf_block_values(ggml_type);
   if (!y || !x || !blob || M < 0 || N < 0 || K <= 0 || K % per) return ub::fail(UB_ERR_INVALID_ARG);
@@ -298,11 +318,12 @@ int ub_qmatmul_gguf(void* y, const void* x, const void* blob, int ggml_type, int
     return ub::fail(UB_ERR_INVALID_ARG);
   if (reinterpret_cast<uintptr_t>(blob) & (ggml_type == GGML_Q5_K ? 15 : 1)) return ub::fail(UB_ERR_INVALID_ARG);
   cudaStream_t s = ub::as_stream(stream);
+  if (ub::take_weights_written(s)) fresh = true;
   if (ggml_type == GGML_Q4_0)
-    return f32 ? gguf_matmul<float, 0>(y, static_cast<const float*>(x), blob, M, N, K, out_dtype, s)
-               : gguf_matmul<__nv_bfloat16, 0>(y, static_cast<const __nv_bfloat16*>(x), blob, M, N, K, out_dtype, s);
-  return f32 ? gguf_matmul<float, 1>(y, static_cast<const float*>(x), blob, M, N, K, out_dtype, s)
-             : gguf_matmul<__nv_bfloat16, 1>(y, static_cast<const __nv_bfloat16*>(x), blob, M, N, K, out_dtype, s);
+    return f32 ? gguf_matmul<float, 0>(y, static_cast<const float*>(x), blob, M, N, K, out_dtype, fresh, s)
+               : gguf_matmul<__nv_bfloat16, 0>(y, static_cast<const __nv_bfloat16*>(x), blob, M, N, K, out_dtype, fresh, s);
+  return f32 ? gguf_matmul<float, 1>(y, static_cast<const float*>(x), blob, M, N, K, out_dtype, fresh, s)
+             : gguf_matmul<__nv_bfloat16, 1>(y, static_cast<const __nv_bfloat16*>(x), blob, M, N, K, out_dtype, fresh, s);
 }
 
 }  // extern "C"
