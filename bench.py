@@ -28,7 +28,7 @@ Printed JSON (one line, rank 0):
 `--impl reference` times that CPU path alone (the reference's own kernels need the vendor toolchain
 and device, so the CPU restatement is the only reference arm that can run).
 
-Other workloads (c1, c2_m4, c2_m8, c2_m16, c3, c4, c5_m1, c5_m512; q6k_m1 for the Q6_K decode kernel) print the same
+Other workloads (c1, c2_m4, c2_m8, c2_m16, c3, c4, c5_m1, c5_m512; q6k_m1, q5k_m1, q4_0_m1 for the decode kernels of the other GGUF formats) print the same
 line for the other configurations.  The linear workloads run one replica per GPU (weak scaling); c4 (MoE layer) and c5
 (70B-shaped linear stack) shard over the ranks (expert / tensor parallel, strong scaling) with NCCL
 all-reduces through the eccl entry points.
@@ -74,15 +74,24 @@ def profile_traffic(workload: str):
 Q4K_ROW_BYTES = lambda K: K // 256 * 144  # noqa: E731
 Q8_ROW_BYTES = lambda K: K // 32 * 34  # noqa: E731
 Q6K_ROW_BYTES = lambda K: K // 256 * 210  # noqa: E731
+Q5K_ROW_BYTES = lambda K: K // 256 * 176  # noqa: E731
+Q4_0_ROW_BYTES = lambda K: K // 32 * 18   # noqa: E731
+
+
+def GEN_WEIGHT(o):
+    """Synthetic weight generators by format name (o: the module that holds them)."""
+    return {"Q8_0": o.gen_q8_0_weight, "Q4_K": o.gen_q4k_weight, "Q6_K": o.gen_q6k_weight, "Q5_K": o.gen_q5k_weight,
+            "Q4_0": o.gen_q4_0_weight}
 
 
 def wl_format(wl) -> str:
-    """"Q8_0", "Q4_K" or "Q6_K" (key ``fmt`` overrides the is_q4k flag)."""
+    """"Q8_0", "Q4_K", "Q6_K", "Q5_K" or "Q4_0" (key ``fmt`` overrides the is_q4k flag)."""
     return wl.get("fmt", "Q4_K" if wl["is_q4k"] else "Q8_0")
 
 
 def wl_row_bytes(wl) -> int:
-    return {"Q8_0": Q8_ROW_BYTES, "Q4_K": Q4K_ROW_BYTES, "Q6_K": Q6K_ROW_BYTES}[wl_format(wl)](wl["K"])
+    return {"Q8_0": Q8_ROW_BYTES, "Q4_K": Q4K_ROW_BYTES, "Q6_K": Q6K_ROW_BYTES, "Q5_K": Q5K_ROW_BYTES,
+            "Q4_0": Q4_0_ROW_BYTES}[wl_format(wl)](wl["K"])
 
 
 def measured_peaks():
@@ -198,8 +207,9 @@ class CpuArm:
         N, K, M, is_q4k = workload["N"], workload["K"], workload["M"], workload["is_q4k"]
         rng = np.random.default_rng(workload["seed"])
         fmt = wl_format(workload)
-        self.w = {"Q8_0": o.gen_q8_0_weight, "Q4_K": o.gen_q4k_weight, "Q6_K": o.gen_q6k_weight}[fmt](rng, N, K)
-        self.fmt_code = {"Q8_0": o.FMT_Q8_0, "Q4_K": o.FMT_Q4K, "Q6_K": o.FMT_Q6K}[fmt]
+        self.w = GEN_WEIGHT(o)[fmt](rng, N, K)
+        self.fmt_code = {"Q8_0": o.FMT_Q8_0, "Q4_K": o.FMT_Q4K, "Q6_K": o.FMT_Q6K, "Q5_K": o.FMT_Q5K,
+                         "Q4_0": o.FMT_Q4_0}[fmt]
         self.Ms = min(M, workload.get("cpu_rows", M))
         self.x = o.gen_activation(rng, self.Ms, K, workload["x_bf16"])
         self.y = np.empty((self.Ms, N), dtype=np.float32)
@@ -251,6 +261,10 @@ WORKLOADS = {
                    desc="Q4_K 14336x4096 small-batch decode, M=16"),
     "q6k_m1": dict(N=14336, K=4096, M=1, is_q4k=False, fmt="Q6_K", x_bf16=True, unit="GB/s", seed=1006, copies=16,
                    passes=4, desc="Q6_K 14336x4096 decode GEMV, bf16 activations, M=1"),
+    "q5k_m1": dict(N=14336, K=4096, M=1, is_q4k=False, fmt="Q5_K", x_bf16=True, unit="GB/s", seed=1007, copies=16,
+                   passes=4, desc="Q5_K 14336x4096 decode GEMV, bf16 activations, M=1"),
+    "q4_0_m1": dict(N=14336, K=4096, M=1, is_q4k=False, fmt="Q4_0", x_bf16=True, unit="GB/s", seed=1008, copies=32,
+                    passes=4, desc="Q4_0 14336x4096 decode GEMV, bf16 activations, M=1"),
     "c3": dict(N=14336, K=4096, M=2048, is_q4k=True, x_bf16=True, unit="TFLOP/s", seed=1002, copies=2, cpu_rows=64,
                desc="Q4_K 14336x4096 prefill GEMM, M=2048"),
     "c3_m1024": dict(N=14336, K=4096, M=1024, is_q4k=True, x_bf16=True, unit="TFLOP/s", seed=1002, copies=2,
@@ -289,7 +303,7 @@ def run_linear(wl_name, wl, steps, warmup, min_seconds, rank, world, torch, with
     N, K, M, is_q4k = wl["N"], wl["K"], wl["M"], wl["is_q4k"]
     rng = np.random.default_rng(wl["seed"] + rank)
     fmt = wl_format(wl)
-    w_host = {"Q8_0": o.gen_q8_0_weight, "Q4_K": o.gen_q4k_weight, "Q6_K": o.gen_q6k_weight}[fmt](rng, N, K).reshape(-1)
+    w_host = np.ascontiguousarray(GEN_WEIGHT(o)[fmt](rng, N, K)).reshape(-1)
     w_bytes = w_host.nbytes
     copies = wl["copies"]
     x_dtype = ub.DTYPE_BF16 if wl["x_bf16"] else ub.DTYPE_F32
@@ -307,10 +321,13 @@ def run_linear(wl_name, wl, steps, warmup, min_seconds, rank, world, torch, with
     del base
     x_dev = torch.from_numpy(x_host.view(np.uint8).reshape(-1).copy()).cuda()
     y_dev = torch.empty((M * N * esz,), dtype=torch.uint8, device="cuda")
-    ws_bytes = 0 if fmt == "Q6_K" else ops.qmatmul_workspace_bytes(M, N, K, is_q4k)
+    ws_bytes = 0 if fmt in ("Q6_K", "Q5_K", "Q4_0") else ops.qmatmul_workspace_bytes(M, N, K, is_q4k)
+    gguf_tag = {"Q5_K": 13, "Q4_0": 2}.get(fmt)  # GGML type tags of the formats that only the blob entry takes
 
     def matmul(y, x, w, workspace, stream):
-        if fmt == "Q6_K":
+        if gguf_tag is not None:
+            ops.qmatmul_gguf(y, x, w, gguf_tag, M, N, K, x_dtype=x_dtype, out_dtype=y_dtype, stream=stream)
+        elif fmt == "Q6_K":
             ops.qmatmul_q6k(y, x, w, M, N, K, x_dtype=x_dtype, out_dtype=y_dtype, stream=stream)
         else:
             ops.qmatmul(y, x, w, M, N, K, is_q4k=is_q4k, x_dtype=x_dtype, out_dtype=y_dtype, workspace=workspace,
@@ -472,7 +489,8 @@ def run_linear(wl_name, wl, steps, warmup, min_seconds, rank, world, torch, with
     return dict(value=value, ms_per_step=ms_step, launches=launches, e2e=e2e, e2e_per_call=e2e_call, roofline=roof,
                 clocks=clocks, replays_per_step=k, timed_seconds=ms_total * 1e-3,
                 dtype={"Q4_K": "u4+f16 scales -> f32 accumulate", "Q8_0": "i8+f16 scales -> f32 accumulate",
-                       "Q6_K": "u6+i8 scales+f16 -> f32 accumulate"}[fmt])
+                       "Q6_K": "u6+i8 scales+f16 -> f32 accumulate", "Q5_K": "u5+f16 scales -> f32 accumulate",
+                       "Q4_0": "u4+f16 scale -> f32 accumulate"}[fmt])
 
 
 class ShardedContext:

@@ -591,7 +591,8 @@ def c_dequant(blocks: np.ndarray, is_q4k: bool) -> np.ndarray:
     return out
 
 
-FMT_Q8_0, FMT_Q4K, FMT_Q6K = 0, 1, 2  # format codes of the C restatement's matmuls (bool is_q4k = 0 / 1)
+# format codes of the C restatement's matmuls (bool is_q4k = 0 / 1)
+FMT_Q8_0, FMT_Q4K, FMT_Q6K, FMT_Q5K, FMT_Q4_0 = 0, 1, 2, 3, 4
 
 
 def c_dequant_q6k(blocks: np.ndarray) -> np.ndarray:

@@ -233,16 +233,64 @@ static void dequant_block_q6k(const uint8_t* blk, float* y) {
     }
 }
 
-/* Format codes of the functions below: 0 = Q8_0, 1 = Q4_K, 2 = Q6_K. */
-static int fmt_per(int fmt) { return fmt == 0 ? QK8_0 : QK_K; }
-static int fmt_bytes(int fmt) { return fmt == 0 ? Q8_0_BYTES : (fmt == 1 ? Q4K_BYTES : Q6K_BYTES); }
+/* One interleaved 176-byte Q5_K super-block -> 256 floats (layout declared at kernels/quant.cpp:154-161: f16 d,
+ * f16 dmin, twelve scale bytes packed as in Q4_K, qh[32], qs[128]; the reference has no kernel for it, the
+ * arithmetic is the published GGML one).  64-value group g: values 0..31 = low nibbles of qs[32g..] + 16 * bit 2g
+ * of qh[l] with pair 2g, values 32..63 = high nibbles + 16 * bit 2g+1 with pair 2g+1; y = (d*sc)*q - dmin*m. */
+#define Q5K_BYTES 176
+static void dequant_block_q5k(const uint8_t* blk, float* y) {
+  uint16_t dh, mh;
+  memcpy(&dh, blk, 2);
+  memcpy(&mh, blk + 2, 2);
+  const float d = f16_to_f32(dh);
+  const float dmin = f16_to_f32(mh);
+  const uint8_t* scales = blk + 4;
+  const uint8_t* qh = blk + 16;
+  const uint8_t* qs = blk + 48;
+  for (int g = 0; g < 4; g++) {
+    uint8_t sc, m;
+    scale_min_k4(2 * g, scales, &sc, &m);
+    const float d1 = d * (float)sc, m1 = dmin * (float)m;
+    scale_min_k4(2 * g + 1, scales, &sc, &m);
+    const float d2 = d * (float)sc, m2 = dmin * (float)m;
+    for (int l = 0; l < 32; l++) {
+      const int q1 = (qs[32 * g + l] & 0xF) + (((qh[l] >> (2 * g)) & 1) << 4);
+      const int q2 = (qs[32 * g + l] >> 4) + (((qh[l] >> (2 * g + 1)) & 1) << 4);
+      y[64 * g + l] = d1 * (float)q1 - m1;
+      y[64 * g + 32 + l] = d2 * (float)q2 - m2;
+    }
+  }
+}
+
+/* One interleaved 18-byte Q4_0 block -> 32 floats (kernels/quant.cpp:64-69: f16 d and sixteen bytes; value i in
+ * the low nibble of byte i, value 16 + i in its high nibble); y = d * (q - 8). */
+#define Q4_0_BYTES 18
+static void dequant_block_q4_0(const uint8_t* blk, float* y) {
+  uint16_t dh;
+  memcpy(&dh, blk, 2);
+  const float d = f16_to_f32(dh);
+  for (int i = 0; i < 16; i++) {
+    y[i] = d * (float)((int)(blk[2 + i] & 0xF) - 8);
+    y[16 + i] = d * (float)((int)(blk[2 + i] >> 4) - 8);
+  }
+}
+
+/* Format codes of the functions below: 0 = Q8_0, 1 = Q4_K, 2 = Q6_K, 3 = Q5_K, 4 = Q4_0. */
+static int fmt_per(int fmt) { return (fmt == 0 || fmt == 4) ? QK8_0 : QK_K; }
+static int fmt_bytes(int fmt) {
+  return fmt == 0 ? Q8_0_BYTES : fmt == 1 ? Q4K_BYTES : fmt == 2 ? Q6K_BYTES : fmt == 3 ? Q5K_BYTES : Q4_0_BYTES;
+}
 static void dequant_block(int fmt, const uint8_t* blk, float* y) {
   if (fmt == 0)
     dequant_block_q8_0(blk, y);
   else if (fmt == 1)
     dequant_block_q4k(blk, y);
-  else
+  else if (fmt == 2)
     dequant_block_q6k(blk, y);
+  else if (fmt == 3)
+    dequant_block_q5k(blk, y);
+  else
+    dequant_block_q4_0(blk, y);
 }
 
 void ub_oracle_dequant_q6k(const uint8_t* blocks, float* out, size_t nblocks) {
@@ -319,7 +367,7 @@ void ub_oracle_quantize_q8_0(const float* x, uint8_t* blocks, size_t nblocks) {
  * dequantised to f32 exactly as above, products and sums in double, one rounding
  * to f32 at the end.  This is the parity oracle (not a timed path). */
 void ub_oracle_qmatmul_exact(const float* x, const uint8_t* wq, float* y, int M, int N, int K, int is_q4k) {
-  const int per = fmt_per(is_q4k), bytes = fmt_bytes(is_q4k);  /* is_q4k is the format code (2 = Q6_K) */
+  const int per = fmt_per(is_q4k), bytes = fmt_bytes(is_q4k);  /* is_q4k is the format code (0 .. 4) */
   const int nb = K / per;
 #pragma omp parallel for schedule(static)
   for (int n = 0; n < N; n++) {
@@ -343,7 +391,7 @@ void ub_oracle_qmatmul_exact(const float* x, const uint8_t* wq, float* y, int M,
  * first and scaled once, the usual CPU formulation of a GGML-style vec-dot with a
  * floating-point activation row. */
 void ub_oracle_qmatmul_f32(const float* x, const uint8_t* wq, float* y, int M, int N, int K, int is_q4k) {
-  const int per = fmt_per(is_q4k), bytes = fmt_bytes(is_q4k);  /* is_q4k is the format code (2 = Q6_K) */
+  const int per = fmt_per(is_q4k), bytes = fmt_bytes(is_q4k);  /* is_q4k is the format code (0 .. 4) */
   const int nb = K / per;
 #pragma omp parallel for schedule(static)
   for (int n = 0; n < N; n++) {

@@ -72,6 +72,25 @@ def gen_q4k_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
     return pack_q4k(d, dm, sc, mn, q)
 
 
+def gen_q4_0_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    """Q4_0: d f16 uniform in [1e-3, 1e-2], every nibble pattern -> bytes [N * K / 32 * 18] (f16 d, sixteen bytes;
+    value i in the low nibble of byte i, value 16 + i in its high nibble)."""
+    nb = N * K // 32
+    b = rng.integers(0, 256, size=(nb, 18), dtype=np.uint8)
+    b[:, :2] = rng.uniform(1e-3, 1e-2, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    return b.reshape(-1)
+
+
+def gen_q5k_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
+    """Q5_K: d, dmin f16 uniform in [1e-4, 1e-2], every pattern of the packed 6-bit scales and mins, the fifth bits
+    and the nibbles -> bytes [N * K / 256 * 176] (d, dmin, scales[12], qh[32], qs[128])."""
+    nb = N * K // QK_K
+    b = rng.integers(0, 256, size=(nb, 176), dtype=np.uint8)
+    b[:, 0:2] = rng.uniform(1e-4, 1e-2, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    b[:, 2:4] = rng.uniform(1e-4, 1e-2, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    return b.reshape(-1)
+
+
 def gen_q6k_weight(rng: np.random.Generator, N: int, K: int) -> np.ndarray:
     """d f16 uniform in [1e-4, 1e-3]; int8 scales uniform in [-128, 127]; 6-bit quants uniform in [0, 63]
     -> bytes [N, K/256, 210] = ql[128] (low nibbles), qh[64] (upper two bits), scales[16], d.  Position
