@@ -5,9 +5,11 @@
 // The reference declares the block (kernels/quant.cpp:64-70: f16 d and sixteen bytes of nibbles, 18 bytes per 32
 // values; value i in the low half of byte i, value 16 + i in the high half; w = d * (q - 8)) and ships no kernel for
 // it.  Same structure as the Q5_K and Q6_K kernels (qgemv_q5k.cu, q6k.cu): a CTA (two per SM, eight warps) owns a
-// contiguous, balanced range of rows and walks it in stages of up to eight rows = ONE bulk copy (cp.async.bulk,
+// contiguous, balanced range of rows and walks it in stages of up to sixteen rows = ONE bulk copy (cp.async.bulk,
 // mbarrier ring, programmatic dependent launch with the first stage requested ahead of the dependency wait); warp
-// w takes row w of the stage, a lane one block per step.  Blocks are 18 bytes apart, so the even ones start on a
+// w takes rows w and w + 8 of a stage of sixteen (the two rows share every read of the activation limbs, which at 2
+// bytes per value against 0.56 of the weights are most of what the shared-memory pipe moves), a lane one block of
+// each per step.  Blocks are 18 bytes apart, so the even ones start on a
 // 4-byte boundary and the odd ones two bytes later: a step takes blocks of one parity in all lanes (2 lane + p),
 // five aligned words each, and the nibble words are a funnel shift (even) or the words themselves (odd).  The
 // nibbles are unsigned bytes and meet 15-bit block-fixed-point activations (q = 254 hi + lo, one scale per 256
@@ -23,7 +25,9 @@ namespace {
 
 using namespace ub;
 
-constexpr int kW = 8;  // warps per CTA = rows per stage
+constexpr int kW = 8;          // warps per CTA
+constexpr int kR = 2;          // rows per warp and stage: the two rows share every read of the activation limbs
+constexpr int kRows = kW * kR; // rows per stage
 constexpr int kMaxStages = 4;
 constexpr uint32_t kSpin = 400000;
 constexpr float kXQMax = 32258.f;                // 127 * 254
@@ -83,7 +87,7 @@ qgemv_q4_0_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStages];  // full[S], empty[S]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nsb = K / UB_QK_K, nb = K / 32;
-  const uint32_t row_bytes = static_cast<uint32_t>(nb) * UB_Q4_0_BYTES, stage_bytes = kW * row_bytes;
+  const uint32_t row_bytes = static_cast<uint32_t>(nb) * UB_Q4_0_BYTES, stage_bytes = kRows * row_bytes;
   unsigned char* const ring = q40_smem;
   XSlot* const xq = reinterpret_cast<XSlot*>(q40_smem + static_cast<size_t>(S) * stage_bytes);  // [MT][K / 32]
   float* const xsc = reinterpret_cast<float*>(xq + MT * nb);                                     // [MT][nsb]
@@ -93,7 +97,7 @@ qgemv_q4_0_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void
   const int base = N / static_cast<int>(gridDim.x), extra = N % static_cast<int>(gridDim.x);
   const int bx = static_cast<int>(blockIdx.x);
   const int r0 = bx * base + (bx < extra ? bx : extra), nrows = base + (bx < extra ? 1 : 0);
-  const int nst = (nrows + kW - 1) / kW;
+  const int nst = (nrows + kRows - 1) / kRows;
 
   // The next kernel in the stream may start as soon as every CTA of this grid has passed this point.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -107,12 +111,12 @@ qgemv_q4_0_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void
   __syncthreads();
   // stage n of this CTA = rows r0 + 8 n .. of the range -> ring slot n % S, one bulk copy
   auto issue = [&](int n) {
-    const int rows = min(kW, nrows - kW * n);
+    const int rows = min(kRows, nrows - kRows * n);
     const uint32_t bytes = static_cast<uint32_t>(rows) * row_bytes, full = bars_s + 8 * (n % S);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(bytes) : "memory");
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                      ring_s + (n % S) * stage_bytes),
-                 "l"(wq + static_cast<size_t>(r0 + kW * n) * row_bytes), "r"(bytes), "r"(full)
+                 "l"(wq + static_cast<size_t>(r0 + kRows * n) * row_bytes), "r"(bytes), "r"(full)
                  : "memory");
   };
   const int n_early = min(min(early, S), nst);
@@ -173,11 +177,14 @@ qgemv_q4_0_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void
 #pragma unroll 1
   for (int n = 0; n < nst; n++) {
     if (ok) ok = mb_wait(bars_s + 8 * slot, round & 1);
-    const int rows = min(kW, nrows - kW * n);
-    float acc[MT];
+    const int rows = min(kRows, nrows - kRows * n);
+    float acc[kR][MT];
 #pragma unroll
-    for (int m = 0; m < MT; m++) acc[m] = 0.f;
+    for (int r = 0; r < kR; r++)
+#pragma unroll
+      for (int m = 0; m < MT; m++) acc[r][m] = 0.f;
     if (warp < rows) {
+      const bool two = warp + kW < rows;  // the warp's second row (row warp + 8 of the stage) exists
       const unsigned char* rowp = ring + static_cast<size_t>(slot) * stage_bytes + static_cast<size_t>(warp) * row_bytes;
 #pragma unroll
       for (int par = 0; par < 2; par++)
@@ -185,26 +192,43 @@ qgemv_q4_0_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void
         for (int b = 2 * lane + par; b < nb; b += 64) {
           // even block: starts on a word, d in its low half, the nibbles from its high half on; odd block: starts two
           // bytes into a word, d in that word's high half, the nibbles in the four words that follow
-          const uint32_t* al = reinterpret_cast<const uint32_t*>(rowp + b * UB_Q4_0_BYTES - 2 * par);
-          const uint32_t w0 = al[0], w1 = al[1], w2 = al[2], w3 = al[3], w4 = al[4];
-          const float d = half_bits_to_f32(par ? w0 >> 16 : w0);
-          const uint32_t q0 = par ? w1 : __funnelshift_r(w0, w1, 16), q1 = par ? w2 : __funnelshift_r(w1, w2, 16);
-          const uint32_t q2 = par ? w3 : __funnelshift_r(w2, w3, 16), q3 = par ? w4 : __funnelshift_r(w3, w4, 16);
-          const uint32_t l0 = q0 & 0x0F0F0F0Fu, l1 = q1 & 0x0F0F0F0Fu, l2 = q2 & 0x0F0F0F0Fu, l3 = q3 & 0x0F0F0F0Fu;
-          const uint32_t h0 = (q0 >> 4) & 0x0F0F0F0Fu, h1 = (q1 >> 4) & 0x0F0F0F0Fu, h2 = (q2 >> 4) & 0x0F0F0F0Fu,
-                         h3 = (q3 >> 4) & 0x0F0F0F0Fu;
+          uint32_t lo4[kR][4], hi4[kR][4];
+          float d[kR];
+#pragma unroll
+          for (int r = 0; r < kR; r++) {
+            if (r == 0 || two) {
+              const uint32_t* al = reinterpret_cast<const uint32_t*>(rowp + static_cast<size_t>(r) * kW * row_bytes +
+                                                                     b * UB_Q4_0_BYTES - 2 * par);
+              const uint32_t w0 = al[0], w1 = al[1], w2 = al[2], w3 = al[3], w4 = al[4];
+              d[r] = half_bits_to_f32(par ? w0 >> 16 : w0);
+              const uint32_t q0 = par ? w1 : __funnelshift_r(w0, w1, 16), q1 = par ? w2 : __funnelshift_r(w1, w2, 16);
+              const uint32_t q2 = par ? w3 : __funnelshift_r(w2, w3, 16), q3 = par ? w4 : __funnelshift_r(w3, w4, 16);
+              lo4[r][0] = q0 & 0x0F0F0F0Fu, lo4[r][1] = q1 & 0x0F0F0F0Fu, lo4[r][2] = q2 & 0x0F0F0F0Fu, lo4[r][3] = q3 & 0x0F0F0F0Fu;
+              hi4[r][0] = (q0 >> 4) & 0x0F0F0F0Fu, hi4[r][1] = (q1 >> 4) & 0x0F0F0F0Fu;
+              hi4[r][2] = (q2 >> 4) & 0x0F0F0F0Fu, hi4[r][3] = (q3 >> 4) & 0x0F0F0F0Fu;
+            } else {
+              d[r] = 0.f;
+#pragma unroll
+              for (int i = 0; i < 4; i++) lo4[r][i] = hi4[r][i] = 0;
+            }
+          }
 #pragma unroll
           for (int m = 0; m < MT; m++) {
             if (m < 3 || M > 3) {  // only the fourth slot can be empty (one, two or four slots for M = 1, 2, 3-4)
               const XSlot& xs = xq[m * nb + b];
               const uint4 xa = xs.hi[0], xb = xs.hi[1], ya = xs.lo[0], yb = xs.lo[1];
-              const int H = dp4a_us(h3, xb.w, dp4a_us(h2, xb.z, dp4a_us(h1, xb.y, dp4a_us(h0, xb.x,
-                            dp4a_us(l3, xa.w, dp4a_us(l2, xa.z, dp4a_us(l1, xa.y, dp4a_us(l0, xa.x, 0))))))));
-              const int L = dp4a_us(h3, yb.w, dp4a_us(h2, yb.z, dp4a_us(h1, yb.y, dp4a_us(h0, yb.x,
-                            dp4a_us(l3, ya.w, dp4a_us(l2, ya.z, dp4a_us(l1, ya.y, dp4a_us(l0, ya.x, 0))))))));
-              // sum (q - 8) xq = 254 H + L - 8 sum(xq): < 2^25
-              const int t = 254 * H + L - 8 * xs.sum;
-              acc[m] = fmaf(static_cast<float>(t), d * xsc[m * nsb + (b >> 3)], acc[m]);
+              const int s8 = 8 * xs.sum;
+              const float xsv = xsc[m * nsb + (b >> 3)];
+#pragma unroll
+              for (int r = 0; r < kR; r++) {
+                const int H = dp4a_us(hi4[r][3], xb.w, dp4a_us(hi4[r][2], xb.z, dp4a_us(hi4[r][1], xb.y, dp4a_us(hi4[r][0], xb.x,
+                              dp4a_us(lo4[r][3], xa.w, dp4a_us(lo4[r][2], xa.z, dp4a_us(lo4[r][1], xa.y, dp4a_us(lo4[r][0], xa.x, 0))))))));
+                const int L = dp4a_us(hi4[r][3], yb.w, dp4a_us(hi4[r][2], yb.z, dp4a_us(hi4[r][1], yb.y, dp4a_us(hi4[r][0], yb.x,
+                              dp4a_us(lo4[r][3], ya.w, dp4a_us(lo4[r][2], ya.z, dp4a_us(lo4[r][1], ya.y, dp4a_us(lo4[r][0], ya.x, 0))))))));
+                // sum (q - 8) xq = 254 H + L - 8 sum(xq): < 2^25
+                const int t = 254 * H + L - s8;
+                acc[r][m] = fmaf(static_cast<float>(t), d[r] * xsv, acc[r][m]);
+              }
             }
           }
         }
@@ -216,17 +240,20 @@ qgemv_q4_0_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void
       if (ok) ok = mb_wait(bars_s + 8 * (kMaxStages + slot), round & 1);
       if (ok && lane == 0) issue(n + S);
     }
-    if (warp < rows) {
 #pragma unroll
-      for (int m = 0; m < MT; m++) {
-        float v = acc[m];
+    for (int r = 0; r < kR; r++) {
+      if (warp + kW * r < rows) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-        if (lane == 0 && (m < 3 || M > 3)) {
-          const size_t at = static_cast<size_t>(m) * N + static_cast<size_t>(r0 + kW * n + warp);
-          if (y_dtype == UB_DTYPE_F32) static_cast<float*>(y)[at] = v;
-          else if (y_dtype == UB_DTYPE_BF16) static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(v);
-          else static_cast<__half*>(y)[at] = __float2half_rn(v);
+        for (int m = 0; m < MT; m++) {
+          float v = acc[r][m];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+          if (lane == 0 && (m < 3 || M > 3)) {
+            const size_t at = static_cast<size_t>(m) * N + static_cast<size_t>(r0 + kRows * n + warp + kW * r);
+            if (y_dtype == UB_DTYPE_F32) static_cast<float*>(y)[at] = v;
+            else if (y_dtype == UB_DTYPE_BF16) static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(v);
+            else static_cast<__half*>(y)[at] = __float2half_rn(v);
+          }
         }
       }
     }
@@ -237,7 +264,7 @@ qgemv_q4_0_kernel(const uint8_t* __restrict__ wq, const XT* __restrict__ x, void
 
 template <typename XT, int MT>
 int launch_q4_0(const uint8_t* w, const XT* x, void* y, int M, int N, int K, int out_dtype, bool fresh, cudaStream_t s) {
-  const size_t row_bytes = static_cast<size_t>(K / 32) * UB_Q4_0_BYTES, stage_bytes = kW * row_bytes;
+  const size_t row_bytes = static_cast<size_t>(K / 32) * UB_Q4_0_BYTES, stage_bytes = kRows * row_bytes;
   const size_t xbytes = MT * (static_cast<size_t>(K / 32) * sizeof(XSlot) + static_cast<size_t>(K / UB_QK_K) * 4);
   int ctas = 2;
   int S = xbytes + 2 * stage_bytes <= kDynBudget ? static_cast<int>((kDynBudget - xbytes) / stage_bytes) : 0;
@@ -254,7 +281,7 @@ int launch_q4_0(const uint8_t* w, const XT* x, void* y, int M, int N, int K, int
     ub::set_cuda_error(e);
     return ub::fail(UB_ERR_CUDA);
   }
-  const int slots = ctas * ub::num_sms(), want = (N + kW - 1) / kW;
+  const int slots = ctas * ub::num_sms(), want = (N + kRows - 1) / kRows;
   const int grid = want < slots ? want : slots;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
