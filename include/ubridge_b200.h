@@ -170,8 +170,8 @@ int ub_qmatmul_q6k_bf16(void* y, const void* x, const void* wq, int M, int N, in
  * matmul_* (kernels/matmul.cpp:1143-1184; small-M shape in
  * kernels/third_party/matmul_decoding.h:12-570).  The suffix names the activation type;
  * out_dtype is UB_DTYPE_F32 / UB_DTYPE_BF16 / UB_DTYPE_F16.  M <= 16 runs the
- * bandwidth-bound decode kernels (Q4_K with bf16 activations and bf16 output: M <= 8 at K = 2048 / 4096 / 8192,
- * M <= 4 otherwise), larger M the tensor-core kernel — see ub_qmatmul_workspace_bytes for the scratch it needs when the
+ * bandwidth-bound decode kernels (Q4_K with bf16 activations and bf16 output: M <= 8), larger M
+ * the tensor-core kernel — see ub_qmatmul_workspace_bytes for the scratch it needs when the
  * activation or output type is not bf16 (0 whenever M <= 16).  Q8_0 takes the tensor-core kernel when
  * K % 256 == 0 and wq is 16-byte aligned; otherwise, or when called without the scratch, it runs the
  * decode kernel in passes of eight tokens (same result within the matmul tolerance, slower).

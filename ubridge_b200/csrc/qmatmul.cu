@@ -35,7 +35,6 @@ uint32_t oneshot_spin_limit();
 void* tensor_map_encoder();
 int q4k_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, bool fresh, cudaStream_t s);
 int q8_0_gemm_tc(void* y, const void* x, const void* wq, int M, int N, int K, bool fresh, cudaStream_t s);
-bool q4k_gemv_mc_supported(int M, int K);
 }  // namespace ub
 
 namespace {
@@ -111,8 +110,7 @@ int qmatmul(bool is_q4k, int x_dtype, void* y, const void* x, const void* wq, in
   cudaStream_t s = ub::as_stream(stream);
   if (ub::take_weights_written(s)) fresh = true;
 
-  if (is_q4k && M > kDecodeOnePassM && M <= kDecodeMaxM && x_dtype == UB_DTYPE_BF16 && out_dtype == UB_DTYPE_BF16 &&
-      !ub::q4k_gemv_mc_supported(M, K)) {
+  if (is_q4k && M > kDecodeOnePassM && M <= kDecodeMaxM && x_dtype == UB_DTYPE_BF16 && out_dtype == UB_DTYPE_BF16) {
     const int st = ub::q4k_gemm_tc(y, x, wq, M, N, K, fresh, s);
     if (st != UB_ERR_UNSUPPORTED) return st;  // unsupported shape or driver: the decode kernel below
   }
